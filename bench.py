@@ -1,0 +1,283 @@
+#!/usr/bin/env python
+"""Benchmark of the ChebyKAN layer forward (configuration 3: 65536 x 1024 -> 1024, degree 8).
+
+    python bench.py --gpus N --steps K --warmup W [--mode bf16|tf32|fp32]
+    python bench.py --impl reference ...        # the reference's CPU path on the host cores
+
+One "step" is one forward pass of the layer over one batch of synthetic input.
+With N > 1 (launched by torch.distributed.run, one rank per GPU) every rank
+runs the full configuration-3 batch on its own GPU with replicated
+coefficients: rows are independent, so inference has no collective
+("weak" scaling; value = rows of all ranks / max-over-ranks time).
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+METRIC = "chebykan_layer_fwd_samples_per_s"
+UNIT = "samples/s"
+CFG = dict(workload="cfg3: ChebyKANLayer fwd, batch 65536 per GPU, in=1024, out=1024, degree=8, x~N(0,1) fp32",
+           batch_per_gpu=65536, input_dim=1024, output_dim=1024, degree=8)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained"), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self.nv is not None:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+
+    def stop(self):
+        if self._thr is not None:
+            self._stop.set()
+            self._thr.join()
+        med = statistics.median(self.samples) if self.samples else None
+        return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def cpu_reference_throughput(rows: int, repeats: int, seed: int = 1003):
+    """The reference's CPU path for this layer, restated op for op (torch CPU kernels), all host threads."""
+    from oracle import chebykan_oracle as o
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(rows, CFG["input_dim"], generator=g)
+    torch.manual_seed(seed)
+    coeffs = o.init_coeffs(CFG["input_dim"], CFG["output_dim"], CFG["degree"])
+    o.forward(x[:256], coeffs)  # warm the thread pool
+    best = float("inf")
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        o.forward(x, coeffs)
+        dt = time.perf_counter() - t0
+        times.append(dt)
+        best = min(best, dt)
+    return rows / best, torch.get_num_threads(), times
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = 4096
+    from oracle import chebykan_oracle as o
+    torch.set_num_threads(os.cpu_count() or 1)
+    g = torch.Generator().manual_seed(1003)
+    x = torch.randn(rows, CFG["input_dim"], generator=g)
+    torch.manual_seed(1003)
+    coeffs = o.init_coeffs(CFG["input_dim"], CFG["output_dim"], CFG["degree"])
+    for _ in range(args.warmup):
+        o.forward(x, coeffs)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        o.forward(x, coeffs)
+    dt = time.perf_counter() - t0
+    value = rows * args.steps / dt
+    sample = f"{rows} of 65536 rows per step (closed-form basis + einsum, torch CPU fp32)"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": dict(CFG, rows_per_step=rows),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    import kan_b200
+    from kan_b200 import ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, n_in, n_out, deg = CFG["batch_per_gpu"], CFG["input_dim"], CFG["output_dim"], CFG["degree"]
+    mode = args.mode
+    torch.manual_seed(1003)
+    layer = kan_b200.ChebyKANLayer(n_in, n_out, deg, math_mode=mode).to(dev)
+    for p in layer.parameters():
+        p.requires_grad_(False)
+    g = torch.Generator().manual_seed(1003 + rank)
+    x_host = torch.randn(B, n_in, generator=g).pin_memory()
+    y_host = torch.empty(B, n_out, dtype=torch.float32).pin_memory()
+    x = x_host.to(dev)
+    packed = ops.pack_coeffs(layer.cheby_coeffs.detach(), mode)
+    y = torch.empty(B, n_out, dtype=torch.float32, device=dev)
+
+    def step():
+        ops.forward(x, packed, n_in, n_out, deg, mode, out=y)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ops.check_status()
+    ms_total = ev0.elapsed_time(ev1)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = world * B / (ms_step * 1e-3)
+
+    # end to end through the layer's public call with host buffers: H2D of x, forward, D2H of y
+    e2e_steps = max(3, min(args.steps, 10))
+
+    def e2e_step():
+        xd = x_host.to(dev, non_blocking=True)
+        yd = layer(xd)
+        y_host.copy_(yd, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_value = world * B / (float(te.item()) / e2e_steps * 1e-3)
+    ops.check_status()
+
+    if rank == 0:
+        peaks = measured_peaks()
+        flops = 2.0 * B * n_in * (deg + 1) * n_out
+        achieved = flops / (ms_step * 1e-3) / 1e12
+        if mode == "fp32":
+            peak, peak_note = 148 * 128 * 2 * 1.965e9 / 1e12, "nominal FFMA peak (148 SM x 128 lanes x 2 x 1.965 GHz)"
+        elif mode == "tf32":
+            peak, peak_note = peaks["bf16_tflops"] / 2, f"half of the {peaks['source']} bf16 burst peak"
+        else:
+            peak, peak_note = peaks["bf16_tflops"], f"{peaks['source']} cuBLAS bf16 burst peak"
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode],
+            "data": "synthetic",
+            "config": dict(CFG, global_batch=world * B, parallelism=f"dp{world} (rows sharded, no collective)",
+                           l2_policy="inputs larger than L2 (x 268 MB + y 268 MB per step vs 126 MB L2)",
+                           math_mode=mode),
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": TRAFFIC_BYTES.get(mode), "peak_note": peak_note,
+                         "flops_per_launch": flops},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 4,
+                    "d2h_bytes_per_step": y_host.numel() * 4, "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            v, cores, times = cpu_reference_throughput(8192, 3)
+            line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"8192 of 65536 rows, best of 3 ({sum(times):.1f} s of CPU work)"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one forward launch taken from an ncu capture; None until one exists.
+TRAFFIC_BYTES = {"bf16": None, "tf32": None, "fp32": None}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

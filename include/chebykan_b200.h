@@ -1,0 +1,137 @@
+/*
+ * chebykan_b200 — C ABI of the B200 (sm_100a) ChebyKAN layer hot path.
+ *
+ * The layer computes  y[b,o] = sum_i sum_d C[i,o,d] * T_d(tanh(x[b,i]))
+ * (T_d = Chebyshev polynomial of the first kind) and its gradients.  The
+ * reference project (0xEodum/KAN) implements this path in Python on top of
+ * PyTorch; it has no FFI of its own, so every entry point below cites the
+ * reference lines whose work it replaces (paths inside that project).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - x, y, dy, dx are row-major fp32: x[B][in], y[B][out];
+ *   - coeffs / dcoeffs use the parameter's own layout [in][out][deg+1] fp32;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = default stream);
+ *   - all launches are asynchronous on `stream`; nothing synchronises;
+ *   - return value: 0 on success, a negative CHEBYKAN_E* code otherwise
+ *     (no exception ever crosses this boundary);
+ *   - the library allocates no device memory: callers own every buffer
+ *     (sizes from chebykan_packed_bytes / chebykan_workspace_bytes).
+ */
+#ifndef CHEBYKAN_B200_H_
+#define CHEBYKAN_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CHEBYKAN_ABI_VERSION 1
+
+/* error codes */
+#define CHEBYKAN_OK            0
+#define CHEBYKAN_EINVAL       -1  /* bad shape / null pointer / bad enum            */
+#define CHEBYKAN_EALIGN       -2  /* pointer not 16-byte aligned                    */
+#define CHEBYKAN_EUNSUPPORTED -3  /* shape outside what this mode's kernel handles  */
+#define CHEBYKAN_ECUDA        -4  /* CUDA runtime error (see chebykan_last_cuda_error) */
+#define CHEBYKAN_ETIMEOUT     -5  /* a bounded device-side wait gave up             */
+#define CHEBYKAN_EWORKSPACE   -6  /* workspace / packed buffer too small            */
+#define CHEBYKAN_EDEVICE      -7  /* current device is not compute capability 10.x  */
+
+/* arithmetic mode of the contraction */
+#define CHEBYKAN_MODE_FP32 0  /* fp32 FFMA on CUDA cores, correctly rounded tanh   */
+#define CHEBYKAN_MODE_TF32 1  /* tcgen05 kind::tf32, fp32 accumulate in TMEM       */
+#define CHEBYKAN_MODE_BF16 2  /* tcgen05 kind::f16 (bf16 x bf16), fp32 accumulate  */
+
+/* operations that may need a caller-provided workspace */
+#define CHEBYKAN_OP_FWD        0
+#define CHEBYKAN_OP_BWD_DCOEFF 1
+#define CHEBYKAN_OP_BWD_DX     2
+
+int         chebykan_abi_version(void);
+const char* chebykan_strerror(int code);
+/* cudaError_t of the most recent CHEBYKAN_ECUDA on the calling thread */
+int         chebykan_last_cuda_error(void);
+
+/*
+ * Packed coefficient matrix for one mode.
+ * Replaces the permute + copy that torch.einsum performs on the coefficient
+ * tensor before its bmm (kan/basis/chebyshev.py:101).  The packed layout is
+ * private to the library; it is rebuilt after every optimizer step.
+ */
+int64_t chebykan_packed_bytes(int64_t in, int64_t out, int64_t deg, int mode);
+int chebykan_pack_coeffs(const float* coeffs, void* packed,
+                         int64_t in, int64_t out, int64_t deg, int mode,
+                         void* stream);
+
+/* bytes of caller-owned workspace an operation needs (0 = none, <0 = error) */
+int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out,
+                                 int64_t deg, int mode);
+
+/*
+ * Forward.  Replaces ChebyKANLayer.forward -> ChebyshevBasis.forward
+ * (kan/layers/chebykan.py:53-67, kan/basis/chebyshev.py:80-145): tanh,
+ * basis expansion and einsum('bid,iod->bo') in one fused kernel; the basis
+ * tensor never exists in device memory.  `packed` comes from
+ * chebykan_pack_coeffs with the same (in, out, deg, mode).
+ * `status` is a device int32 the kernel sets non-zero if a bounded wait gave
+ * up (tensor-core modes; may be NULL in FP32 mode).
+ */
+int chebykan_fwd(const float* x, const void* packed, float* y,
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
+                 int32_t* status, void* stream);
+
+/*
+ * Coefficient gradient dC[i,o,d] = sum_b T_d(tanh x[b,i]) * dY[b,o].
+ * Replaces the dW half of autograd's BmmBackward plus the permute back to
+ * [in,out,deg+1] (backward of kan/basis/chebyshev.py:101,119-145).
+ * accumulate != 0 adds into dcoeffs, otherwise dcoeffs is overwritten.
+ */
+int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs,
+                        void* workspace, int64_t workspace_bytes,
+                        int64_t B, int64_t in, int64_t out, int64_t deg,
+                        int mode, int accumulate, int32_t* status, void* stream);
+
+/*
+ * Input gradient dx[b,i] = (1-t^2) * sum_d T_d'(t) * sum_o dY[b,o] C[i,o,d],
+ * t = tanh x[b,i].  Replaces the dPhi half of BmmBackward and the
+ * Cos/Mul/Acos/Clamp/Tanh backward chain (backward of
+ * kan/basis/chebyshev.py:78,136-145).  Where tanh saturates to exactly +-1
+ * the reference produces NaN (0 * inf); this library returns 0 there.
+ * Reads the coefficients in their own [in][out][deg+1] layout.
+ */
+int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs,
+                    float* dx, int64_t B, int64_t in, int64_t out, int64_t deg,
+                    int mode, int32_t* status, void* stream);
+
+/*
+ * Optimizer updates on a flat fp32 parameter of n elements.  Replace
+ * torch.optim.SGD(lr) / torch.optim.Adam(lr) as called by the reference's
+ * training loop (README.md:59-66).  grad_scale multiplies the gradient first
+ * (1/world_size after a sum all-reduce).  `step` is 1-based.
+ */
+int chebykan_sgd_step(float* param, const float* grad, int64_t n, float lr,
+                      float grad_scale, void* stream);
+int chebykan_adam_step(float* param, const float* grad, float* exp_avg,
+                       float* exp_avg_sq, int64_t n, float lr, float beta1,
+                       float beta2, float eps, int64_t step, float grad_scale,
+                       void* stream);
+
+/*
+ * Forward with HOST buffers: copies x and the coefficients to the device,
+ * packs, runs chebykan_fwd and copies y back; synchronous.  The caller lends
+ * device scratch of at least chebykan_fwd_host_scratch_bytes(...) bytes.
+ * Same replaced reference lines as chebykan_fwd.
+ */
+int64_t chebykan_fwd_host_scratch_bytes(int64_t B, int64_t in, int64_t out,
+                                        int64_t deg, int mode);
+int chebykan_fwd_host(const float* x_host, const float* coeffs_host,
+                      float* y_host, void* device_scratch,
+                      int64_t scratch_bytes, int64_t B, int64_t in,
+                      int64_t out, int64_t deg, int mode, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CHEBYKAN_B200_H_ */

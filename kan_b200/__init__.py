@@ -1,0 +1,14 @@
+"""kan_b200 — the ChebyKAN layer hot path of 0xEodum/KAN on NVIDIA B200 (sm_100a).
+
+Public surface: ``ChebyKANLayer`` (drop-in for kan.layers.chebykan.ChebyKANLayer),
+``install_into_reference`` (swap it into the reference's layer registry), the
+functional ``ops``, the kernel-backed ``optim.SGD`` / ``optim.Adam`` and the
+data-parallel helpers in ``dp``.  Everything computes in hand-written CUDA
+behind the C ABI of ``include/chebykan_b200.h``; there is no CPU fallback.
+"""
+from .layer import ChebyKANLayer, ChebyshevBasis, KANLayer, chebykan_apply, install_into_reference
+from . import ops, optim, dp, workloads
+
+__all__ = ["ChebyKANLayer", "ChebyshevBasis", "KANLayer", "chebykan_apply", "install_into_reference",
+           "ops", "optim", "dp", "workloads"]
+__version__ = "0.1.0"

@@ -1,0 +1,191 @@
+// C ABI of the library: argument validation and dispatch to the kernels.
+#include <math.h>
+#include "common.cuh"
+
+namespace chebykan {
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(int e) { g_last_cuda_error = e; }
+
+// 0 = unknown, 1 = compute capability 10.x, -1 = anything else (per device ordinal)
+static int g_cc_ok[64] = {0};
+
+static int check_device() {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) { set_last_cuda_error((int)e); return CHEBYKAN_ECUDA; }
+    if (dev < 0 || dev >= 64) return CHEBYKAN_EDEVICE;
+    if (g_cc_ok[dev] == 0) {
+        int major = 0;
+        e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+        if (e != cudaSuccess) { set_last_cuda_error((int)e); return CHEBYKAN_ECUDA; }
+        g_cc_ok[dev] = (major == 10) ? 1 : -1;
+    }
+    return g_cc_ok[dev] == 1 ? CHEBYKAN_OK : CHEBYKAN_EDEVICE;
+}
+
+static bool shape_ok(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    // 32-bit tile arithmetic inside the kernels; deg+1 <= 128 slots per tile
+    return B >= 0 && in >= 1 && out >= 1 && deg >= 0 && deg <= 127 &&
+           in <= (1 << 20) && out <= (1 << 20) && B <= (int64_t)1 << 31 &&
+           in * (deg + 1) <= (int64_t)1 << 24;
+}
+static bool mode_ok(int mode) {
+    return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16;
+}
+}  // namespace chebykan
+
+using namespace chebykan;
+
+extern "C" {
+
+int chebykan_abi_version(void) { return CHEBYKAN_ABI_VERSION; }
+
+const char* chebykan_strerror(int code) {
+    switch (code) {
+        case CHEBYKAN_OK: return "ok";
+        case CHEBYKAN_EINVAL: return "invalid argument (shape, null pointer or enum)";
+        case CHEBYKAN_EALIGN: return "pointer is not 16-byte aligned";
+        case CHEBYKAN_EUNSUPPORTED: return "shape not supported in this mode";
+        case CHEBYKAN_ECUDA: return "CUDA runtime error";
+        case CHEBYKAN_ETIMEOUT: return "a bounded device-side wait gave up";
+        case CHEBYKAN_EWORKSPACE: return "workspace or packed buffer too small";
+        case CHEBYKAN_EDEVICE: return "current device is not compute capability 10.x (B200)";
+        default: return "unknown error code";
+    }
+}
+
+int chebykan_last_cuda_error(void) { return g_last_cuda_error; }
+
+int64_t chebykan_packed_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
+    if (!shape_ok(0, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
+    const PackedDims p = packed_dims(in, out, deg, mode);
+    return p.k_pad * p.n_pad * p.elem;
+}
+
+int chebykan_pack_coeffs(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg,
+                         int mode, void* stream) {
+    if (!shape_ok(0, in, out, deg) || !mode_ok(mode) || !coeffs || !packed) return CHEBYKAN_EINVAL;
+    if (!aligned16(coeffs) || !aligned16(packed)) return CHEBYKAN_EALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_pack(coeffs, packed, in, out, deg, mode, (cudaStream_t)stream);
+}
+
+int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
+    switch (op) {
+        case CHEBYKAN_OP_FWD: return 0;
+        case CHEBYKAN_OP_BWD_DCOEFF: return B == 0 ? 0 : dcoeff_workspace_bytes(B, in, out, deg, mode);
+        case CHEBYKAN_OP_BWD_DX: return 0;
+        default: return CHEBYKAN_EINVAL;
+    }
+}
+
+int chebykan_fwd(const float* x, const void* packed, float* y, int64_t B, int64_t in, int64_t out,
+                 int64_t deg, int mode, int32_t* status, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !packed) return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x || !y) return CHEBYKAN_EINVAL;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(packed)) return CHEBYKAN_EALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    if (mode == CHEBYKAN_MODE_FP32)
+        return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg,
+                               (cudaStream_t)stream);
+    if (!status) return CHEBYKAN_EINVAL;
+    return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream);
+}
+
+int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* workspace,
+                        int64_t workspace_bytes, int64_t B, int64_t in, int64_t out, int64_t deg,
+                        int mode, int accumulate, int32_t* /*status*/, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !dcoeffs) return CHEBYKAN_EINVAL;
+    if (!aligned16(dcoeffs) || !aligned16(workspace)) return CHEBYKAN_EALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (B == 0) {
+        if (!accumulate) return check_cuda(cudaMemsetAsync(dcoeffs, 0, in * out * (deg + 1) * 4, s));
+        return CHEBYKAN_OK;
+    }
+    if (!x || !dy) return CHEBYKAN_EINVAL;
+    if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
+    // every mode currently accumulates dC in fp32 on the FFMA pipe
+    return launch_dcoeff_ffma(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg,
+                              accumulate, s);
+}
+
+int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
+                    int64_t in, int64_t out, int64_t deg, int mode, int32_t* /*status*/,
+                    void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !coeffs) return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x || !dy || !dx) return CHEBYKAN_EINVAL;
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(coeffs)) return CHEBYKAN_EALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream);
+}
+
+int chebykan_sgd_step(float* param, const float* grad, int64_t n, float lr, float grad_scale,
+                      void* stream) {
+    if (n < 0 || !param || !grad) return CHEBYKAN_EINVAL;
+    if (!aligned16(param) || !aligned16(grad)) return CHEBYKAN_EALIGN;
+    if (n == 0) return CHEBYKAN_OK;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_sgd(param, grad, n, lr, grad_scale, (cudaStream_t)stream);
+}
+
+int chebykan_adam_step(float* param, const float* grad, float* exp_avg, float* exp_avg_sq,
+                       int64_t n, float lr, float beta1, float beta2, float eps, int64_t step,
+                       float grad_scale, void* stream) {
+    if (n < 0 || step < 1 || !param || !grad || !exp_avg || !exp_avg_sq) return CHEBYKAN_EINVAL;
+    if (!aligned16(param) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq))
+        return CHEBYKAN_EALIGN;
+    if (n == 0) return CHEBYKAN_OK;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_adam(param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, step,
+                       grad_scale, (cudaStream_t)stream);
+}
+
+// ---- host-buffer forward ------------------------------------------------------------
+static int64_t a256(int64_t v) { return round_up(v, 256); }
+
+int64_t chebykan_fwd_host_scratch_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
+    return a256(B * in * 4) + a256(in * out * (deg + 1) * 4) +
+           a256(chebykan_packed_bytes(in, out, deg, mode)) + a256(B * out * 4) + 256;
+}
+
+int chebykan_fwd_host(const float* x_host, const float* coeffs_host, float* y_host,
+                      void* device_scratch, int64_t scratch_bytes, int64_t B, int64_t in,
+                      int64_t out, int64_t deg, int mode, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !coeffs_host || !device_scratch)
+        return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x_host || !y_host) return CHEBYKAN_EINVAL;
+    if (!aligned16(device_scratch)) return CHEBYKAN_EALIGN;
+    if (scratch_bytes < chebykan_fwd_host_scratch_bytes(B, in, out, deg, mode)) return CHEBYKAN_EWORKSPACE;
+    cudaStream_t s = (cudaStream_t)stream;
+    char* base = reinterpret_cast<char*>(device_scratch);
+    float* xd = reinterpret_cast<float*>(base);            base += a256(B * in * 4);
+    float* cd = reinterpret_cast<float*>(base);            base += a256(in * out * (deg + 1) * 4);
+    void* pk = base;                                       base += a256(chebykan_packed_bytes(in, out, deg, mode));
+    float* yd = reinterpret_cast<float*>(base);            base += a256(B * out * 4);
+    int32_t* st = reinterpret_cast<int32_t*>(base);
+    int rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(xd, x_host, B * in * 4, cudaMemcpyHostToDevice, s)))) return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(cd, coeffs_host, in * out * (deg + 1) * 4, cudaMemcpyHostToDevice, s)))) return rc;
+    if ((rc = check_cuda(cudaMemsetAsync(st, 0, 4, s)))) return rc;
+    if ((rc = chebykan_pack_coeffs(cd, pk, in, out, deg, mode, stream))) return rc;
+    if ((rc = chebykan_fwd(xd, pk, yd, B, in, out, deg, mode, st, stream))) return rc;
+    if ((rc = check_cuda(cudaMemcpyAsync(y_host, yd, B * out * 4, cudaMemcpyDeviceToHost, s)))) return rc;
+    int32_t st_host = 0;
+    if ((rc = check_cuda(cudaMemcpyAsync(&st_host, st, 4, cudaMemcpyDeviceToHost, s)))) return rc;
+    if ((rc = check_cuda(cudaStreamSynchronize(s)))) return rc;
+    return st_host ? CHEBYKAN_ETIMEOUT : CHEBYKAN_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,94 @@
+// Shared helpers for the ChebyKAN sm_100a kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include "../../include/chebykan_b200.h"
+
+namespace chebykan {
+
+__host__ __device__ constexpr int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+__host__ __device__ constexpr int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+// ---- packed coefficient layouts ------------------------------------------
+// FP32 mode:  Wf[K_pad][N_pad] fp32, N contiguous.
+//   k = (i / 8) * (deg+1) * 8 + d * 8 + (i % 8)           (degree-major inside
+//   blocks of 8 inputs), in padded to a multiple of 8, out to a multiple of 64.
+// BF16 mode:  Wt[N_pad][K_pad] bf16, K contiguous (K-major B operand).
+//   k = (i / 64) * (deg+1) * 64 + d * 64 + (i % 64), in padded to a multiple of
+//   64, out to a multiple of 128.  One 64-wide K block (= one 128-byte swizzle
+//   row) holds one degree of 64 consecutive inputs.
+// TF32 mode:  Wt[N_pad][K_pad] fp32 (rounded to tf32), blocks of 32 inputs.
+constexpr int FP32_IB = 8;
+constexpr int BF16_IB = 64;
+constexpr int TF32_IB = 32;
+constexpr int FP32_NPAD = 64;
+constexpr int TC_NPAD = 128;
+
+struct PackedDims {
+    int64_t ib;      // inputs per K block
+    int64_t in_pad;  // inputs padded to a multiple of ib
+    int64_t k_pad;   // in_pad * (deg+1)
+    int64_t n_pad;   // padded outputs
+    int64_t elem;    // bytes per element
+    bool    k_major; // true: [N_pad][K_pad]; false: [K_pad][N_pad]
+};
+
+inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64_t deg, int mode) {
+    PackedDims p{};
+    if (mode == CHEBYKAN_MODE_FP32) {
+        p.ib = FP32_IB; p.elem = 4; p.k_major = false; p.n_pad = round_up(out, FP32_NPAD);
+    } else if (mode == CHEBYKAN_MODE_BF16) {
+        p.ib = BF16_IB; p.elem = 2; p.k_major = true; p.n_pad = round_up(out, TC_NPAD);
+    } else {
+        p.ib = TF32_IB; p.elem = 4; p.k_major = true; p.n_pad = round_up(out, TC_NPAD);
+    }
+    p.in_pad = round_up(in, p.ib);
+    p.k_pad = p.in_pad * (deg + 1);
+    return p;
+}
+
+// ---- tanh ------------------------------------------------------------------
+// FP32 mode: tanh evaluated in double and rounded once, i.e. the correctly
+// rounded fp32 value (high-degree T_d amplifies an error in t by up to d^2, so
+// a 2-ulp tanh alone would spend the whole 1e-5 budget at degree 32).
+__device__ __forceinline__ float tanh_exact(float x) { return (float)tanh((double)x); }
+
+// Tensor-core modes: 1 - 2/(1+2^(2x log2 e)) with the approximate ex2 and rcp
+// units; absolute error about 2e-7, far below bf16/tf32 operand rounding.
+__device__ __forceinline__ float tanh_fast(float x) {
+    float e, r;
+    float z = x * 2.885390081777927f;  // 2*log2(e)
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(z));
+    float den = e + 1.0f;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(den));
+    return fmaf(-2.0f, r, 1.0f);
+}
+
+// thread-local record of the last CUDA error seen by an entry point
+void set_last_cuda_error(int e);
+inline int check_cuda(cudaError_t e) {
+    if (e == cudaSuccess) return CHEBYKAN_OK;
+    set_last_cuda_error((int)e);
+    return CHEBYKAN_ECUDA;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// ---- launchers implemented in the .cu files ------------------------------------
+int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, int mode,
+                cudaStream_t s);
+int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
+                    int64_t deg, cudaStream_t s);
+int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s);
+int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
+int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
+                       int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
+                       cudaStream_t s);
+int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
+                   int64_t in, int64_t out, int64_t deg, cudaStream_t s);
+int launch_sgd(float* p, const float* g, int64_t n, float lr, float gs, cudaStream_t s);
+int launch_adam(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1,
+                float b2, float eps, int64_t step, float gs, cudaStream_t s);
+
+}  // namespace chebykan

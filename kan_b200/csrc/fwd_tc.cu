@@ -1,0 +1,448 @@
+// Tensor-core forward for sm_100a:  Y[B, out] = Phi[B, K] * W[K, out],
+// K = in*(deg+1), with the basis tile Phi generated on chip.
+//
+// Replaces reference kan/basis/chebyshev.py:92-101,119-145 (tanh, basis
+// expansion, einsum) with one persistent, warp-specialised kernel:
+//
+//   warps 0-7   producers: coalesced x loads -> tanh -> three-term recurrence
+//               T_d = 2t T_{d-1} - T_{d-2} held in registers -> bf16 (or tf32)
+//               -> 128-byte-swizzled K-major A tile in shared memory.  One K
+//               block is one degree d of IB consecutive inputs, so a thread
+//               advances its recurrence by one step per K block.
+//   warp  8     TMA: cp.async.bulk.tensor loads of the packed coefficient tile
+//               Wt[N][K] (B operand, K-major, 128B swizzle), no multicast.
+//   warp  9     MMA: one elected lane issues tcgen05.mma (cta_group::1,
+//               M=128, N=BN) into one of two TMEM accumulators, and
+//               tcgen05.commit releases shared-memory stages / publishes the
+//               accumulator.
+//   warps 10-13 epilogue: tcgen05.ld TMEM -> registers -> y, overlapped with
+//               the next tile's main loop through the second accumulator.
+//
+// Phi never reaches device memory.  Every mbarrier wait is bounded: when one
+// gives up the kernel raises an abort flag, records a code in *status, drains
+// what it has in flight, frees its TMEM and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include "common.cuh"
+
+namespace chebykan {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int NUM_PRODUCER_WARPS = 8;
+constexpr int NUM_PRODUCERS = NUM_PRODUCER_WARPS * 32;
+constexpr int TMA_WARP = 8;
+constexpr int MMA_WARP = 9;
+constexpr int NUM_THREADS = 14 * 32;
+constexpr int A_STAGE_BYTES = BM * 128;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false when another role already aborted or when this
+// wait itself ran out of time (it then raises the abort flag and records `code`).
+__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                       int32_t* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = globaltimer_ns();
+    for (uint32_t it = 1;; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+                *abort_flag = 1;
+                atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile, 128-byte rows, 128B swizzle, 8-row groups 1024 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);  // start address
+    d |= (uint64_t)1 << 16;                   // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;         // stride byte offset between 8-row groups
+    d |= (uint64_t)1 << 46;                   // descriptor version (sm_100)
+    d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
+    return d;
+}
+template <int MODE>
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                     uint32_t accumulate) {
+    if (MODE == CHEBYKAN_MODE_BF16) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+            ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+    }
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* tmap, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(tmap), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// status codes recorded by a wait that gave up
+enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_FULL = 3, ST_MMA_ACC = 4, ST_EPILOGUE = 5, ST_DRAIN = 6 };
+
+template <int BN>
+struct Smem {
+    static constexpr int B_STAGE_BYTES = BN * 128;
+    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+    static constexpr int NS = (BN == 256) ? 4 : 6;
+    static constexpr int BAR_OFFSET = NS * STAGE_BYTES;
+    // barriers: full[NS], empty[NS], acc_full[2], acc_empty[2], drain; then tmem slot + abort flag
+    static constexpr int NUM_BARS = 2 * NS + 5;
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024 alignment slack
+};
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ x,
+              float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
+              int64_t num_tiles, int32_t* status) {
+    using L = Smem<BN>;
+    constexpr int NS = L::NS;
+    constexpr int IB = (MODE == CHEBYKAN_MODE_BF16) ? 64 : 32;  // inputs per K block
+    constexpr int CH = (MODE == CHEBYKAN_MODE_BF16) ? 8 : 4;    // elements per 16-byte chunk
+    constexpr uint32_t FMT = (MODE == CHEBYKAN_MODE_BF16) ? 1u : 2u;
+    constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BN >> 3) << 17) |
+                               ((uint32_t)(BM >> 4) << 24);
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + L::BAR_OFFSET;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NS + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NS + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * NS + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_iblk = (in + IB - 1) / IB;
+    const int nkb = n_iblk * dp1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), NUM_PRODUCERS + 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4 * 32); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < NUM_PRODUCER_WARPS) {
+        // ------------------------------ producers ------------------------------
+        const int p = threadIdx.x;
+        const int c = p & 7;      // 16-byte chunk inside the 128-byte row
+        const int r0 = p >> 3;    // rows r0, r0+32, r0+64, r0+96
+        const bool vec = (in & 3) == 0;
+        float tt[4][CH], tm1[4][CH], tm2[4][CH];
+        int s = 0; uint32_t ph = 0;
+        bool alive = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            const int64_t m0 = (tile / n_tiles) * BM;
+            for (int ib = 0; ib < n_iblk && alive; ++ib) {
+                const int i_base = ib * IB + c * CH;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t row = m0 + r0 + 32 * j;
+                    float v[CH];
+#pragma unroll
+                    for (int e = 0; e < CH; ++e) v[e] = 0.f;
+                    if (row < B) {
+                        const float* src = x + row * in + i_base;
+                        if (vec) {
+#pragma unroll
+                            for (int q = 0; q < CH / 4; ++q)
+                                if (i_base + 4 * q < in) {
+                                    const float4 f = __ldg(reinterpret_cast<const float4*>(src) + q);
+                                    v[4 * q] = f.x; v[4 * q + 1] = f.y; v[4 * q + 2] = f.z; v[4 * q + 3] = f.w;
+                                }
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < CH; ++e)
+                                if (i_base + e < in) v[e] = __ldg(src + e);
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < CH; ++e) {
+                        const float t = tanh_fast(v[e]);
+                        tt[j][e] = 2.f * t; tm1[j][e] = 1.f; tm2[j][e] = t;  // T_0 = 1, T_{-1} = t
+                    }
+                }
+                for (int d = 0; d < dp1; ++d) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) { alive = false; break; }
+                    const uint32_t a_stage = smem_base + s * L::STAGE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float phi[CH];
+                        if (d == 0) {
+#pragma unroll
+                            for (int e = 0; e < CH; ++e) phi[e] = 1.f;
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < CH; ++e) {
+                                phi[e] = fmaf(tt[j][e], tm1[j][e], -tm2[j][e]);
+                                tm2[j][e] = tm1[j][e]; tm1[j][e] = phi[e];
+                            }
+                        }
+                        uint32_t w[4];
+                        if (MODE == CHEBYKAN_MODE_BF16) {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const __nv_bfloat162 h = __floats2bfloat162_rn(phi[(2 * q) % CH], phi[(2 * q + 1) % CH]);
+                                w[q] = *reinterpret_cast<const uint32_t*>(&h);
+                            }
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[q]) : "f"(phi[q % CH]));
+                        }
+                        const int row = r0 + 32 * j;
+                        const uint32_t dst = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                    }
+                    fence_proxy_async_smem();
+                    mbar_arrive(full_bar(s));
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == TMA_WARP) {
+        // ------------------------------ coefficient loads ------------------------------
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool alive = true;
+            int64_t issued = 0;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                const int n0 = (int)(tile % n_tiles) * BN;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), L::B_STAGE_BYTES);
+                    tma_load_2d(smem_base + s * L::STAGE_BYTES + A_STAGE_BYTES, &tmap_w, kb * IB, n0, full_bar(s));
+                    ++issued;
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!alive) {
+                // let the copies already issued land before the CTA gives up its shared memory
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000ull) { }
+            }
+        }
+    } else if (warp == MMA_WARP) {
+        // ------------------------------ MMA issue ------------------------------
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, status, ST_MMA_FULL)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
+                    const uint64_t a_desc = make_smem_desc(a_addr);
+                    const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)   // 4 x 32 bytes of K per 128-byte row
+                        umma<MODE>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (uint32_t)((kb | k) != 0));
+                    umma_commit(empty_bar(s));
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+                if (alive) umma_commit(acc_full_bar(acc));
+                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+            }
+            if (!alive) {
+                // wait (bounded) until the MMAs already issued have retired
+                umma_commit(drain_bar);
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        int acc = 0; uint32_t acc_ph = 0;
+        bool alive = true;
+        const bool vec = (out & 3) == 0;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            const int64_t row = (tile / n_tiles) * BM + q * 32 + lane;
+            const int n0 = (int)(tile % n_tiles) * BN;
+            // tcgen05.ld is warp-collective: leave the loop only as a whole warp
+            const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, ST_EPILOGUE);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                tmem_ld_wait();
+                if (row < B) {
+                    float* dst = y + row * out + n0 + c0;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        const int col = n0 + c0 + 4 * g;
+                        if (vec && col + 3 < out) {
+                            *reinterpret_cast<float4*>(dst + 4 * g) =
+                                make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                            __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < out) dst[4 * g + e] = __uint_as_float(r[4 * g + e]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(acc_empty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+        return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+    return fn;
+}
+
+template <int MODE, int BN>
+int launch_one(const CUtensorMap& tmap, const float* x, float* y, int64_t B, int in, int out, int dp1,
+               int n_pad, int32_t* status, cudaStream_t s) {
+    using L = Smem<BN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN>,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int n_tiles = n_pad / BN;
+    const int64_t num_tiles = ceil_div(B, BM) * n_tiles;
+    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
+    fwd_tc_kernel<MODE, BN><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, x, y, B, in, out, dp1, n_tiles,
+                                                                num_tiles, status);
+    return check_cuda(cudaGetLastError());
+}
+
+}  // namespace
+
+int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s) {
+    const PackedDims p = packed_dims(in, out, deg, mode);
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return CHEBYKAN_ECUDA;
+    const int bn = (p.n_pad % 256 == 0) ? 256 : 128;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
+    const cuuint64_t strides[1] = {(cuuint64_t)(p.k_pad * p.elem)};
+    const cuuint32_t box[2] = {(cuuint32_t)p.ib, (cuuint32_t)bn};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = (mode == CHEBYKAN_MODE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    const CUresult r = encode(&tmap, dt, 2, const_cast<void*>(wt), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    const int dp1 = (int)deg + 1;
+    if (mode == CHEBYKAN_MODE_BF16) {
+        if (bn == 256) return launch_one<CHEBYKAN_MODE_BF16, 256>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+        return launch_one<CHEBYKAN_MODE_BF16, 128>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+    }
+    if (bn == 256) return launch_one<CHEBYKAN_MODE_TF32, 256>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+    return launch_one<CHEBYKAN_MODE_TF32, 128>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+}
+
+}  // namespace chebykan

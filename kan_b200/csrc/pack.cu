@@ -1,0 +1,53 @@
+// Coefficient packing: cheby_coeffs[in][out][deg+1] fp32 -> the per-mode GEMM
+// operand layouts described in common.cuh.  Takes the place of the permute +
+// copy torch.einsum does before its bmm (reference kan/basis/chebyshev.py:101).
+#include <cuda_bf16.h>
+#include "common.cuh"
+
+namespace chebykan {
+
+template <int MODE>
+__global__ void __launch_bounds__(256)
+pack_kernel(const float* __restrict__ c, void* __restrict__ packed, int in, int out, int dp1,
+            int ib, int64_t k_pad, int64_t n_pad) {
+    const int64_t total = k_pad * n_pad;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        int64_t k, n;
+        if (MODE == CHEBYKAN_MODE_FP32) { k = e / n_pad; n = e % n_pad; }
+        else                            { n = e / k_pad; k = e % k_pad; }
+        const int64_t blk = k / ((int64_t)ib * dp1);
+        const int64_t rem = k % ((int64_t)ib * dp1);
+        const int d = (int)(rem / ib);
+        const int64_t i = blk * ib + rem % ib;
+        float v = 0.f;
+        if (i < in && n < out) v = c[(i * out + n) * dp1 + d];
+        if (MODE == CHEBYKAN_MODE_FP32) {
+            reinterpret_cast<float*>(packed)[e] = v;
+        } else if (MODE == CHEBYKAN_MODE_TF32) {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+            reinterpret_cast<uint32_t*>(packed)[e] = r;
+        } else {
+            reinterpret_cast<__nv_bfloat16*>(packed)[e] = __float2bfloat16_rn(v);
+        }
+    }
+}
+
+int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, int mode,
+                cudaStream_t s) {
+    const PackedDims p = packed_dims(in, out, deg, mode);
+    const int64_t total = p.k_pad * p.n_pad;
+    int64_t blocks = ceil_div(total, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    const int dp1 = (int)deg + 1;
+    if (mode == CHEBYKAN_MODE_FP32)
+        pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+    else if (mode == CHEBYKAN_MODE_TF32)
+        pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+    else
+        pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+    return check_cuda(cudaGetLastError());
+}
+
+}  // namespace chebykan

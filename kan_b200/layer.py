@@ -1,0 +1,228 @@
+"""Drop-in ChebyKANLayer backed by the sm_100a kernels.
+
+Mirrors the reference's ``kan.layers.chebykan.ChebyKANLayer``
+(kan/layers/chebykan.py:10-101): same constructor, the same parameter
+``cheby_coeffs[in, out, deg+1]`` drawn from the global CPU RNG in the same
+way, the same ``state_dict``, ``forward`` flatten rule, ``get_coefficients``,
+``get_analytical_form`` and ``extra_repr``.  ``forward`` and its autograd
+backward run hand-written CUDA through the C ABI; there is no CPU path and no
+PyTorch fallback: a CPU input raises.
+"""
+from __future__ import annotations
+
+from abc import ABC, abstractmethod
+from typing import Any, Dict, Tuple
+
+import torch
+import torch.nn as nn
+
+from . import ops
+
+
+# ---------------------------------------------------------------------------
+# local stand-ins for the reference's abstract bases, used when the reference
+# package is not importable (kan/layers/base.py:11-141, kan/basis/base.py:7-94,
+# kan/basis/chebyshev.py:24-66)
+# ---------------------------------------------------------------------------
+class KANLayer(nn.Module, ABC):
+    """Same abstract surface as the reference's kan.layers.base.KANLayer."""
+
+    @abstractmethod
+    def __init__(self, input_dim: int, output_dim: int, basis_function, **kwargs):
+        super().__init__()
+        self.input_dim = input_dim
+        self.output_dim = output_dim
+        self.basis_function = basis_function
+
+    @abstractmethod
+    def forward(self, x: torch.Tensor) -> torch.Tensor: ...
+
+    @property
+    def basis(self):
+        return self.basis_function
+
+    @abstractmethod
+    def get_analytical_form(self) -> Dict[str, Any]: ...
+
+    @abstractmethod
+    def get_coefficients(self) -> torch.Tensor: ...
+
+
+class ChebyshevBasis:
+    """Descriptor of the Chebyshev basis (degree, name, domain).
+
+    Carries the attributes the reference's ChebyshevBasis exposes
+    (kan/basis/chebyshev.py:24-66).  ``forward`` evaluates the expansion with
+    the fused CUDA kernel; the [B, in, deg+1] basis tensor is never built.
+    """
+
+    def __init__(self, degree: int, domain: Tuple[float, float] = (-1, 1), use_recurrence: bool = False):
+        self.degree = degree
+        self._domain = domain
+        self.use_recurrence = use_recurrence
+        self.arange = torch.arange(0, degree + 1, dtype=torch.float32)
+
+    @property
+    def name(self) -> str:
+        return f"Chebyshev-{self.degree}"
+
+    @property
+    def domain(self) -> Tuple[float, float]:
+        return self._domain
+
+    def forward(self, x: torch.Tensor, coefficients: torch.Tensor) -> torch.Tensor:
+        x = x.view(-1, coefficients.shape[0])
+        return chebykan_apply(x, coefficients, "fp32", None)
+
+
+# ---------------------------------------------------------------------------
+# autograd glue
+# ---------------------------------------------------------------------------
+class _PackedCache:
+    """Packed coefficient buffers, one per math mode, rebuilt when the parameter changes."""
+
+    def __init__(self):
+        self._entries = {}
+
+    def get(self, coeffs: torch.Tensor, mode: str) -> torch.Tensor:
+        key = (coeffs.data_ptr(), coeffs._version, tuple(coeffs.shape))
+        ent = self._entries.get(mode)
+        if ent is None or ent[0] != key:
+            buf = ent[1] if ent is not None and ent[1].device == coeffs.device else None
+            try:
+                buf = ops.pack_coeffs(coeffs.detach(), mode, out=buf)
+            except RuntimeError:
+                buf = ops.pack_coeffs(coeffs.detach(), mode)
+            self._entries[mode] = (key, buf)
+            ent = self._entries[mode]
+        return ent[1]
+
+    def clear(self):
+        self._entries.clear()
+
+
+class _ChebyKANFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, coeffs, mode, cache):
+        n_in, n_out, dp1 = coeffs.shape
+        packed = cache.get(coeffs, mode) if cache is not None else ops.pack_coeffs(coeffs.detach(), mode)
+        y = ops.forward(x, packed, n_in, n_out, dp1 - 1, mode)
+        ctx.save_for_backward(x, coeffs)
+        ctx.mode = mode
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, coeffs = ctx.saved_tensors
+        n_in, n_out, dp1 = coeffs.shape
+        dy = dy.contiguous()
+        dx = dc = None
+        if ctx.needs_input_grad[1]:
+            dc = ops.bwd_dcoeff(x, dy, n_in, n_out, dp1 - 1, ctx.mode)
+        if ctx.needs_input_grad[0]:
+            dx = ops.bwd_dx(x, dy, coeffs.detach(), ctx.mode)
+        return dx, dc, None, None
+
+
+def chebykan_apply(x: torch.Tensor, coeffs: torch.Tensor, mode: str = "fp32", cache=None) -> torch.Tensor:
+    """y = sum_i sum_d coeffs[i,o,d] T_d(tanh x[b,i]) with autograd, x already [B, in]."""
+    if not x.is_cuda or not coeffs.is_cuda:
+        raise RuntimeError("kan_b200.ChebyKANLayer runs on CUDA (sm_100a) only: move the layer and its "
+                           "input to the GPU; there is no CPU path")
+    if x.dtype != torch.float32:
+        # the reference's einsum raises the same way on a dtype mismatch
+        raise RuntimeError(f"expected scalar type Float but found {str(x.dtype).replace('torch.', '').capitalize()}")
+    return _ChebyKANFunction.apply(x, coeffs, mode, cache)
+
+
+# ---------------------------------------------------------------------------
+# the layer
+# ---------------------------------------------------------------------------
+def make_chebykan_layer_class(base_cls, basis_cls, name: str = "ChebyKANLayer"):
+    """Build the layer class on a given (KANLayer base, ChebyshevBasis) pair.
+
+    Called once with the local stand-ins, and by ``install_into_reference``
+    with the reference's own classes so that ``isinstance(layer, kan.KANLayer)``
+    and ``isinstance(layer.basis_function, kan.ChebyshevBasis)`` hold.
+    """
+
+    class _Layer(base_cls):
+        __doc__ = ChebyKANLayerDoc
+
+        def __init__(self, input_dim: int, output_dim: int, degree: int,
+                     use_recurrence: bool = False, init_scale: float = None, *,
+                     math_mode: str = "fp32"):
+            if math_mode not in ops.MODES:
+                raise ValueError(f"math_mode must be one of {sorted(ops.MODES)}")
+            basis_function = basis_cls(degree=degree, use_recurrence=use_recurrence)
+            super().__init__(input_dim=input_dim, output_dim=output_dim, basis_function=basis_function)
+            self.degree = degree
+            self.math_mode = math_mode
+            # identical RNG consumption to kan/layers/chebykan.py:47-51
+            init_scale = init_scale or 1.0 / (input_dim * (degree + 1))
+            self.cheby_coeffs = nn.Parameter(torch.empty(input_dim, output_dim, degree + 1))
+            nn.init.normal_(self.cheby_coeffs, mean=0.0, std=init_scale)
+            self._packed = _PackedCache()
+
+        def forward(self, x: torch.Tensor) -> torch.Tensor:
+            x = x.view(-1, self.input_dim)   # kan/layers/chebykan.py:64
+            return chebykan_apply(x, self.cheby_coeffs, self.math_mode, self._packed)
+
+        def get_analytical_form(self) -> Dict[str, Any]:
+            return {
+                'type': 'ChebyKANLayer',
+                'input_dim': self.input_dim,
+                'output_dim': self.output_dim,
+                'degree': self.degree,
+                'basis': self.basis_function.name,
+                'coefficients': self.cheby_coeffs.detach().cpu().numpy(),
+            }
+
+        def get_coefficients(self) -> torch.Tensor:
+            return self.cheby_coeffs
+
+        def extra_repr(self) -> str:
+            return f'input_dim={self.input_dim}, output_dim={self.output_dim}, degree={self.degree}'
+
+        def _apply(self, fn, *args, **kwargs):
+            self._packed.clear()
+            return super()._apply(fn, *args, **kwargs)
+
+    _Layer.__name__ = name
+    _Layer.__qualname__ = name
+    return _Layer
+
+
+ChebyKANLayerDoc = """KAN layer on Chebyshev polynomials, computed by sm_100a CUDA kernels.
+
+    Args (as in the reference, kan/layers/chebykan.py:21-32):
+        input_dim, output_dim, degree, use_recurrence, init_scale
+    Keyword-only:
+        math_mode: 'fp32' (FFMA, rel-L2 <= 1e-5 to the reference), 'tf32' or
+                   'bf16' (tcgen05 tensor cores, rel-L2 <= 2e-3).
+    ``use_recurrence`` is kept for API compatibility; the kernels always use
+    the three-term recurrence, which agrees with the reference's closed form
+    to about 1e-6.
+"""
+
+ChebyKANLayer = make_chebykan_layer_class(KANLayer, ChebyshevBasis)
+
+
+def install_into_reference():
+    """Swap this layer into an importable reference package.
+
+    Builds the layer on the reference's own ``KANLayer`` / ``ChebyshevBasis``
+    and assigns it to ``kan.layers.LAYER_REGISTRY['chebykan']``
+    (kan/layers/__init__.py:18-27), ``kan.layers.ChebyKANLayer`` and
+    ``kan.ChebyKANLayer``.  The name inside the module ``kan.layers.chebykan``
+    is left alone: the reference class refers to itself through it in its own
+    ``super()`` call.  Returns the new class.
+    """
+    import kan  # the reference package; raises ImportError when absent
+    from kan.layers.base import KANLayer as RefKANLayer
+    from kan.basis.chebyshev import ChebyshevBasis as RefBasis
+    cls = make_chebykan_layer_class(RefKANLayer, RefBasis)
+    kan.layers.LAYER_REGISTRY['chebykan'] = cls
+    kan.layers.ChebyKANLayer = cls
+    kan.ChebyKANLayer = cls
+    return cls

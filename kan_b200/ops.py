@@ -1,0 +1,204 @@
+"""Functional wrappers: torch CUDA tensors in, C-ABI calls underneath.
+
+PyTorch provides device memory and streams only; all arithmetic happens in the
+sm_100a kernels of libchebykan_b200.so.  Nothing here computes on the CPU.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import MODES, OP_BWD_DCOEFF
+
+_status = {}  # device index -> int32[1] tensor the tensor-core kernels report into
+
+
+def _mode(mode) -> int:
+    if isinstance(mode, str):
+        if mode not in MODES:
+            raise ValueError(f"math_mode must be one of {sorted(MODES)}, got {mode!r}")
+        return MODES[mode]
+    return int(mode)
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _require(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor: kan_b200 has no CPU path")
+    if t.dtype != torch.float32:
+        raise RuntimeError(f"expected scalar type Float but found {str(t.dtype).replace('torch.', '')} for {name}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.data_ptr() % 16 != 0 and t.numel() > 0:
+        raise RuntimeError(f"{name} must be 16-byte aligned")
+
+
+def status_tensor(device) -> torch.Tensor:
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise if a tensor-core kernel reported a wait that gave up."""
+    devs = list(_status) if device is None else [torch.device(device).index or 0]
+    for idx in devs:
+        if idx in _status:
+            code = int(_status[idx].item())
+            if code:
+                _status[idx].zero_()
+                raise RuntimeError(f"chebykan kernel on cuda:{idx} gave up a bounded wait (role code {code})")
+
+
+def packed_bytes(in_dim: int, out_dim: int, degree: int, mode) -> int:
+    n = _lib.load().chebykan_packed_bytes(in_dim, out_dim, degree, _mode(mode))
+    _lib.check(n, "chebykan_packed_bytes")
+    return n
+
+
+def pack_coeffs(coeffs: torch.Tensor, mode, out: torch.Tensor | None = None) -> torch.Tensor:
+    """cheby_coeffs[in,out,deg+1] -> the library's private GEMM operand layout."""
+    _require(coeffs, "coeffs")
+    if coeffs.dim() != 3:
+        raise RuntimeError("coeffs must have shape [in, out, degree+1]")
+    n_in, n_out, dp1 = coeffs.shape
+    m = _mode(mode)
+    nbytes = packed_bytes(n_in, n_out, dp1 - 1, m)
+    if out is None:
+        out = torch.empty(nbytes, dtype=torch.uint8, device=coeffs.device)
+    elif out.numel() * out.element_size() < nbytes or out.device != coeffs.device:
+        raise RuntimeError("packed buffer too small or on another device")
+    with torch.cuda.device(coeffs.device):
+        rc = _lib.load().chebykan_pack_coeffs(coeffs.data_ptr(), out.data_ptr(), n_in, n_out, dp1 - 1, m,
+                                              _stream(coeffs))
+    _lib.check(rc, "chebykan_pack_coeffs")
+    return out
+
+
+def forward(x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, degree: int, mode,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[B,out] from x[B,in] and a packed coefficient buffer of the same mode."""
+    _require(x, "x")
+    if x.dim() != 2 or x.shape[1] != in_dim:
+        raise RuntimeError(f"x must have shape [B, {in_dim}]")
+    m = _mode(mode)
+    B = x.shape[0]
+    if out is None:
+        out = torch.empty(B, out_dim, dtype=torch.float32, device=x.device)
+    else:
+        _require(out, "out")
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_fwd(x.data_ptr(), packed.data_ptr(), out.data_ptr(), B, in_dim, out_dim,
+                                      degree, m, status_tensor(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "chebykan_fwd")
+    return out
+
+
+def bwd_dcoeff(x: torch.Tensor, dy: torch.Tensor, in_dim: int, out_dim: int, degree: int, mode,
+               out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """dC[in,out,deg+1] = sum_b T_d(tanh x[b,i]) dY[b,o]."""
+    _require(x, "x")
+    _require(dy, "dy")
+    B = x.shape[0]
+    if x.shape != (B, in_dim) or dy.shape != (B, out_dim):
+        raise RuntimeError("x must be [B, in] and dy [B, out]")
+    m = _mode(mode)
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty(in_dim, out_dim, degree + 1, dtype=torch.float32, device=x.device)
+        accumulate = False
+    else:
+        _require(out, "out")
+    ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DCOEFF, B, in_dim, out_dim, degree, m)
+    _lib.check(ws_bytes, "chebykan_workspace_bytes")
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = lib.chebykan_bwd_dcoeff(x.data_ptr(), dy.data_ptr(), out.data_ptr(), ws.data_ptr(), ws_bytes, B,
+                                     in_dim, out_dim, degree, m, int(accumulate),
+                                     status_tensor(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "chebykan_bwd_dcoeff")
+    return out
+
+
+def bwd_dx(x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor, mode,
+           out: torch.Tensor | None = None) -> torch.Tensor:
+    """dx[B,in] = (1-t^2) sum_d T_d'(t) sum_o dY[b,o] C[i,o,d]."""
+    _require(x, "x")
+    _require(dy, "dy")
+    _require(coeffs, "coeffs")
+    n_in, n_out, dp1 = coeffs.shape
+    B = x.shape[0]
+    if x.shape != (B, n_in) or dy.shape != (B, n_out):
+        raise RuntimeError("x must be [B, in] and dy [B, out]")
+    if out is None:
+        out = torch.empty_like(x)
+    else:
+        _require(out, "out")
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_bwd_dx(x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(), out.data_ptr(), B,
+                                         n_in, n_out, dp1 - 1, _mode(mode),
+                                         status_tensor(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "chebykan_bwd_dx")
+    return out
+
+
+def sgd_step(param: torch.Tensor, grad: torch.Tensor, lr: float, grad_scale: float = 1.0) -> None:
+    _require(param, "param")
+    _require(grad, "grad")
+    if grad.numel() != param.numel():
+        raise RuntimeError("grad and param sizes differ")
+    with torch.cuda.device(param.device):
+        rc = _lib.load().chebykan_sgd_step(param.data_ptr(), grad.data_ptr(), param.numel(), lr, grad_scale,
+                                           _stream(param))
+    _lib.check(rc, "chebykan_sgd_step")
+
+
+def adam_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+              step: int, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+              grad_scale: float = 1.0) -> None:
+    for t, n in ((param, "param"), (grad, "grad"), (exp_avg, "exp_avg"), (exp_avg_sq, "exp_avg_sq")):
+        _require(t, n)
+        if t.numel() != param.numel():
+            raise RuntimeError(f"{n} and param sizes differ")
+    with torch.cuda.device(param.device):
+        rc = _lib.load().chebykan_adam_step(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(),
+                                            exp_avg_sq.data_ptr(), param.numel(), lr, beta1, beta2, eps, step,
+                                            grad_scale, _stream(param))
+    _lib.check(rc, "chebykan_adam_step")
+
+
+def forward_host(x_host: torch.Tensor, coeffs_host: torch.Tensor, mode, scratch: torch.Tensor | None = None,
+                 out: torch.Tensor | None = None):
+    """Forward with HOST tensors through chebykan_fwd_host; returns (y_host, scratch).
+
+    x_host / coeffs_host / out are CPU fp32 tensors (pinned memory makes the
+    copies asynchronous DMA); `scratch` is a reusable device byte buffer.
+    """
+    if x_host.is_cuda or coeffs_host.is_cuda:
+        raise RuntimeError("forward_host takes host tensors")
+    if x_host.dtype != torch.float32 or coeffs_host.dtype != torch.float32:
+        raise RuntimeError("expected scalar type Float")
+    n_in, n_out, dp1 = coeffs_host.shape
+    x2 = x_host.view(-1, n_in)
+    B = x2.shape[0]
+    m = _mode(mode)
+    lib = _lib.load()
+    need = lib.chebykan_fwd_host_scratch_bytes(B, n_in, n_out, dp1 - 1, m)
+    _lib.check(need, "chebykan_fwd_host_scratch_bytes")
+    if scratch is None or scratch.numel() < need:
+        scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
+    if out is None:
+        out = torch.empty(B, n_out, dtype=torch.float32, pin_memory=True)
+    with torch.cuda.device(scratch.device):
+        rc = lib.chebykan_fwd_host(x2.data_ptr(), coeffs_host.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                   scratch.numel(), B, n_in, n_out, dp1 - 1, m,
+                                   torch.cuda.current_stream(scratch.device).cuda_stream)
+    _lib.check(rc, "chebykan_fwd_host")
+    return out, scratch

@@ -1,0 +1,74 @@
+"""SGD and Adam whose updates run in the library's CUDA kernels.
+
+Stand in for ``torch.optim.SGD(params, lr)`` and ``torch.optim.Adam(params,
+lr)`` as the reference's training loop uses them (README.md:59-66): no
+momentum / weight decay for SGD; Adam with betas (0.9, 0.999), eps 1e-8, bias
+correction, no weight decay, no amsgrad.  Works on any contiguous fp32 CUDA
+parameter (ChebyKAN coefficients, LayerNorm weights, ...).  ``grad_scale``
+multiplies every gradient first (1/world_size after a sum all-reduce).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import ops
+
+
+def _bump(p: torch.Tensor) -> None:
+    # the kernels write through the raw pointer; tell autograd the tensor changed
+    torch.autograd.graph.increment_version(p)
+
+
+class _Base:
+    def __init__(self, params, lr: float):
+        self.params = [p for p in params]
+        if not self.params:
+            raise ValueError("optimizer got an empty parameter list")
+        for p in self.params:
+            if not p.is_cuda or p.dtype != torch.float32 or not p.is_contiguous():
+                raise RuntimeError("kan_b200 optimizers need contiguous fp32 CUDA parameters")
+        self.lr = float(lr)
+        self.grad_scale = 1.0
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for p in self.params:
+            if p.grad is not None:
+                if set_to_none:
+                    p.grad = None
+                else:
+                    p.grad.zero_()
+
+
+class SGD(_Base):
+    def __init__(self, params, lr: float = 1e-3):
+        super().__init__(params, lr)
+
+    @torch.no_grad()
+    def step(self) -> None:
+        for p in self.params:
+            if p.grad is None:
+                continue
+            ops.sgd_step(p.data, p.grad.contiguous(), self.lr, self.grad_scale)
+            _bump(p)
+
+
+class Adam(_Base):
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8):
+        super().__init__(params, lr)
+        self.betas = (float(betas[0]), float(betas[1]))
+        self.eps = float(eps)
+        self.state = {}
+
+    @torch.no_grad()
+    def step(self) -> None:
+        for p in self.params:
+            if p.grad is None:
+                continue
+            st = self.state.get(p)
+            if st is None:
+                st = {"step": 0, "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+                self.state[p] = st
+            st["step"] += 1
+            ops.adam_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], st["step"], self.lr,
+                          self.betas[0], self.betas[1], self.eps, self.grad_scale)
+            _bump(p)

@@ -1,0 +1,223 @@
+"""GPU parity, fp32 FFMA mode: CUDA kernels through the C ABI vs the CPU oracle
+and vs the reference's golden vectors.  Tolerance: rel-L2 <= 1e-5."""
+import numpy as np
+import pytest
+import torch
+
+import kan_b200
+from kan_b200 import ops, workloads
+from oracle import chebykan_oracle as o
+from _util import FP32_TOL, OracleLayer, assert_guards_intact, guarded, make_case
+
+pytestmark = pytest.mark.gpu
+
+GOLDEN_CASES = ["tiny_d4", "mid_d8", "cfg1_shape", "deg32_uniform", "deg0", "deg1", "three_dim_input",
+                "recurrence_path", "sparse_784", "wide_out", "kat_points"]
+
+SHAPES = [
+    # B, in, out, deg, dist
+    (4096, 1024, 1024, 8, "normal"),     # configuration 3 at reduced batch
+    (256, 784, 64, 4, "sparse"),         # configuration 2, first layer
+    (256, 64, 10, 4, "normal"),          # configuration 2, second layer
+    (4096, 64, 64, 32, "uniform3"),      # configuration 5 layer
+    (1024, 2048, 2048, 4, "normal"),     # configuration 4 layer at reduced batch
+    (127, 13, 7, 3, "normal"),
+    (1, 5, 130, 2, "normal"),
+    (100, 1, 1, 8, "normal"),
+    (333, 17, 65, 16, "uniform3"),
+    (64, 9, 3, 0, "normal"),
+    (2500, 3, 2, 63, "normal"),
+]
+
+
+def run_all(x, coeffs, dy):
+    n_in, n_out, dp1 = coeffs.shape
+    xd, cd, dyd = x.cuda(), coeffs.cuda(), dy.cuda()
+    packed = ops.pack_coeffs(cd, "fp32")
+    y, yw = guarded((x.shape[0], n_out))
+    ops.forward(xd, packed, n_in, n_out, dp1 - 1, "fp32", out=y)
+    dC, dCw = guarded((n_in, n_out, dp1))
+    ops.bwd_dcoeff(xd, dyd, n_in, n_out, dp1 - 1, "fp32", out=dC)
+    dx, dxw = guarded(tuple(x.shape))
+    ops.bwd_dx(xd, dyd, cd, "fp32", out=dx)
+    torch.cuda.synchronize()
+    assert_guards_intact(y, yw)
+    assert_guards_intact(dC, dCw)
+    assert_guards_intact(dx, dxw)
+    return y.cpu(), dC.cpu(), dx.cpu()
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_vectors(golden, name):
+    c = golden[name]
+    n_in = int(c["meta"][0])
+    x = torch.from_numpy(c["x"]).reshape(-1, n_in).contiguous()
+    y, dC, dx = run_all(x, torch.from_numpy(c["coeffs"]), torch.from_numpy(c["dy"]))
+    assert o.rel_l2(y, c["y"]) <= FP32_TOL
+    assert o.rel_l2(dC, c["dC"]) <= FP32_TOL
+    if "dx" in c:
+        assert o.rel_l2(dx.reshape(-1), c["dx"].reshape(-1)) <= FP32_TOL
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", SHAPES)
+def test_fwd_bwd_vs_oracle(B, n_in, n_out, deg, dist):
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    y_ref, dC_ref, dx_ref = o.forward_backward(x, coeffs, dy)
+    y, dC, dx = run_all(x, coeffs, dy)
+    assert o.rel_l2(y, y_ref) <= FP32_TOL
+    assert o.rel_l2(dC, dC_ref) <= FP32_TOL
+    assert o.rel_l2(dx, dx_ref) <= FP32_TOL
+
+
+def test_bitwise_repeatable():
+    x, coeffs, dy = make_case(1000, 96, 80, 8, seed=5)
+    a = run_all(x, coeffs, dy)
+    b = run_all(x, coeffs, dy)
+    for u, v in zip(a, b):
+        assert torch.equal(u, v)
+
+
+def test_dcoeff_accumulate_and_split_batch():
+    # large batch on a narrow layer forces the batch-split path and its workspace
+    x, coeffs, dy = make_case(20000, 8, 8, 4, seed=9)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    assert _lib_ws(20000, 8, 8, 4) > 0
+    xd, dyd = x.cuda(), dy.cuda()
+    out = torch.ones(8, 8, 5, device="cuda")
+    ops.bwd_dcoeff(xd, dyd, 8, 8, 4, "fp32", out=out, accumulate=True)
+    assert o.rel_l2(out.cpu() - 1.0, dC_ref) <= 2e-5       # "+1" costs a few ulps of the sum
+    out2 = ops.bwd_dcoeff(xd, dyd, 8, 8, 4, "fp32")
+    assert o.rel_l2(out2.cpu(), dC_ref) <= FP32_TOL
+    # direct (single split) accumulate path
+    x, coeffs, dy = make_case(64, 300, 200, 4, seed=10)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    assert _lib_ws(64, 300, 200, 4) == 0
+    out = torch.zeros(300, 200, 5, device="cuda")
+    ops.bwd_dcoeff(x.cuda(), dy.cuda(), 300, 200, 4, "fp32", out=out, accumulate=True)
+    ops.bwd_dcoeff(x.cuda(), dy.cuda(), 300, 200, 4, "fp32", out=out, accumulate=True)
+    assert o.rel_l2(out.cpu(), 2 * dC_ref) <= FP32_TOL
+
+
+def _lib_ws(B, n_in, n_out, deg):
+    from kan_b200 import _lib
+    return _lib.load().chebykan_workspace_bytes(_lib.OP_BWD_DCOEFF, B, n_in, n_out, deg, 0)
+
+
+def test_known_answers_on_gpu():
+    layer = kan_b200.ChebyKANLayer(1, 1, 4).cuda()
+    with torch.no_grad():
+        layer.cheby_coeffs.fill_(1.0)
+    x = torch.tensor([[0.0], [20.0], [-20.0]], device="cuda")
+    y = layer(x).cpu().flatten()
+    # sum_d T_d: x=0 -> 1+0-1+0+1 = 1; t=+1 -> 5; t=-1 -> 1-1+1-1+1 = 1
+    assert torch.allclose(y, torch.tensor([1.0, 5.0, 1.0]), atol=1e-6)
+    # degree 0: y = sum_i C[i,o,0] for every row
+    l0 = kan_b200.ChebyKANLayer(7, 3, 0).cuda()
+    y0 = l0(torch.randn(11, 7, device="cuda"))
+    assert torch.allclose(y0, l0.cheby_coeffs[:, :, 0].sum(0).expand(11, 3), atol=1e-7)
+
+
+def test_saturated_tanh_gives_zero_dx_not_nan():
+    """Documented departure: the reference's autograd yields NaN where tanh(x) == +-1."""
+    x = torch.tensor([[12.0, 0.3], [-15.0, 9.0]])
+    coeffs = torch.randn(2, 2, 5)
+    dy = torch.ones(2, 2)
+    _, _, dx_ref = o.forward_backward(x, coeffs, dy)
+    dx = ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "fp32").cpu()
+    assert torch.isnan(dx_ref[0, 0]) and torch.isnan(dx_ref[1, 0])
+    assert dx[0, 0] == 0 and dx[1, 0] == 0
+    finite = torch.isfinite(dx_ref)
+    assert o.rel_l2(dx[finite], dx_ref[finite]) <= FP32_TOL
+
+
+def test_empty_batch_and_flatten_rule():
+    layer = kan_b200.ChebyKANLayer(4, 3, 3).cuda()
+    y = layer(torch.empty(0, 4, device="cuda"))
+    assert y.shape == (0, 3)
+    y = layer(torch.randn(2, 5, 4, device="cuda"))
+    assert y.shape == (10, 3)                     # leading dimensions are flattened, not restored
+    with pytest.raises(RuntimeError):
+        layer(torch.randn(4, 6, device="cuda").t())          # non-contiguous: view fails
+    with pytest.raises(RuntimeError, match="Float"):
+        layer(torch.randn(6, 4, device="cuda", dtype=torch.float64))
+
+
+def test_c_abi_rejects_bad_arguments():
+    from kan_b200 import _lib
+    lib = _lib.load()
+    buf = torch.zeros(1024, device="cuda")
+    st = ops.status_tensor("cuda")
+    p = buf.data_ptr()
+    assert lib.chebykan_fwd(p + 4, p, p, 4, 4, 4, 2, 0, st.data_ptr(), None) == -2     # misaligned
+    assert lib.chebykan_fwd(p, p, p, 4, 0, 4, 2, 0, st.data_ptr(), None) == -1         # in = 0
+    assert lib.chebykan_fwd(p, p, p, 4, 4, 4, 2, 9, st.data_ptr(), None) == -1         # bad mode
+    assert lib.chebykan_fwd(None, p, p, 4, 4, 4, 2, 0, st.data_ptr(), None) == -1      # null x
+    assert lib.chebykan_bwd_dcoeff(p, p, p, None, 0, 1 << 20, 8, 8, 4, 0, 0, None, None) == -6  # no workspace
+    assert lib.chebykan_adam_step(p, p, p, p, 16, 0.1, 0.9, 0.999, 1e-8, 0, 1.0, None) == -1   # step < 1
+    torch.cuda.synchronize()
+
+
+def test_layer_autograd_two_layer_model():
+    """Configuration 2 (784->64->LN->10, degree 4, batch 256, cross-entropy): gradients of every parameter."""
+    cfg = workloads.CONFIGS["cfg2"]
+    x, labels = workloads.make_inputs(cfg)
+    ref = workloads.build_model(cfg, OracleLayer)
+    ours = workloads.build_model(cfg, kan_b200.ChebyKANLayer)
+    for a, b in zip(ref.parameters(), ours.parameters()):
+        assert torch.equal(a, b)                      # same seed, same CPU RNG stream
+    ours = ours.cuda()
+    loss_ref = torch.nn.functional.cross_entropy(ref(x), labels)
+    loss_ref.backward()
+    loss = torch.nn.functional.cross_entropy(ours(x.cuda()), labels.cuda())
+    loss.backward()
+    assert abs(float(loss) - float(loss_ref)) <= 1e-5 * abs(float(loss_ref))
+    for (n, a), (_, b) in zip(ref.named_parameters(), ours.named_parameters()):
+        assert o.rel_l2(b.grad.cpu(), a.grad) <= 2e-5, n
+
+
+@pytest.mark.parametrize("opt_name", ["sgd", "adam"])
+def test_optimizer_steps_vs_torch(opt_name):
+    torch.manual_seed(3)
+    p_ref = torch.randn(1000 + 3).requires_grad_(True)        # odd length exercises the scalar tail
+    p = p_ref.detach().clone().cuda().requires_grad_(True)
+    if opt_name == "sgd":
+        ref_opt = torch.optim.SGD([p_ref], lr=1e-2)
+        opt = kan_b200.optim.SGD([p], lr=1e-2)
+    else:
+        ref_opt = torch.optim.Adam([p_ref], lr=1e-3)
+        opt = kan_b200.optim.Adam([p], lr=1e-3)
+    for step in range(20):
+        g = torch.randn(1003)
+        p_ref.grad = g.clone()
+        p.grad = g.cuda()
+        ref_opt.step()
+        opt.step()
+    assert o.rel_l2(p.detach().cpu(), p_ref.detach()) <= FP32_TOL
+
+
+def test_training_loop_config1(golden):
+    """README loop: 1 -> 1, degree 8, 100 points, MSE, Adam(0.01), 1000 steps, from the reference's weights."""
+    layer = kan_b200.ChebyKANLayer(1, 1, 8)
+    with torch.no_grad():
+        layer.cheby_coeffs.copy_(torch.from_numpy(golden["cfg1_train"]["init_coeffs"]))
+    layer = layer.cuda()
+    x, tgt = workloads.make_inputs(workloads.CONFIGS["cfg1"])
+    x, tgt = x.cuda(), tgt.cuda()
+    opt = kan_b200.optim.Adam(layer.parameters(), lr=0.01)
+    got = []
+    for step in range(1000):
+        opt.zero_grad()
+        loss = torch.nn.functional.mse_loss(layer(x), tgt)
+        loss.backward()
+        opt.step()
+        if step in (0, 99, 499, 999):
+            got.append(float(loss.detach()))
+    assert np.allclose(got, golden["cfg1_train"]["losses"], rtol=2e-3)
+    assert o.rel_l2(layer.cheby_coeffs.detach().cpu(), golden["cfg1_train"]["final_coeffs"]) <= 2e-3
+
+
+def test_forward_through_host_buffers():
+    x, coeffs, _ = make_case(777, 24, 40, 6, seed=21)
+    y_ref = o.forward(x, coeffs)
+    y, _ = ops.forward_host(x.pin_memory(), coeffs, "fp32")
+    assert o.rel_l2(y, y_ref) <= FP32_TOL

@@ -1,0 +1,128 @@
+"""GPU parity, tensor-core modes (tcgen05 bf16 / tf32 forward).  Tolerance:
+rel-L2 <= 2e-3.  In bf16 mode the coefficients are stored in bf16, so the
+oracle evaluates with the same bf16-rounded coefficients (activations stay
+fp32 in the oracle)."""
+import pytest
+import torch
+
+import kan_b200
+from kan_b200 import ops
+from oracle import chebykan_oracle as o
+from _util import TC_TOL, assert_guards_intact, guarded, make_case
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [
+    # B, in, out, deg, dist
+    (256, 64, 128, 4, "normal"),          # one tile, BN = 128
+    (4096, 1024, 1024, 8, "normal"),      # configuration 3 at reduced batch, BN = 256
+    (2048, 2048, 2048, 4, "normal"),      # configuration 4 layer at reduced batch
+    (8192, 64, 64, 32, "uniform3"),       # configuration 5 layer
+    (256, 784, 64, 4, "sparse"),          # in not a multiple of 64, out padded to 128
+    (256, 64, 10, 4, "normal"),           # out < 16
+    (100, 13, 7, 3, "normal"),            # in not a multiple of 4: scalar loads
+    (1000, 96, 300, 8, "normal"),         # ragged rows and three N tiles of 128
+    (129, 32, 256, 0, "normal"),          # degree 0
+    (20000, 128, 256, 2, "normal"),       # more tiles than SMs: persistent loop, both accumulators
+]
+
+
+def oracle_y(x, coeffs, mode):
+    c = coeffs.bfloat16().float() if mode == "bf16" else coeffs
+    return o.forward(x, c)
+
+
+def run_fwd(x, coeffs, mode):
+    n_in, n_out, dp1 = coeffs.shape
+    xd, cd = x.cuda(), coeffs.cuda()
+    packed = ops.pack_coeffs(cd, mode)
+    y, yw = guarded((x.shape[0], n_out))
+    ops.forward(xd, packed, n_in, n_out, dp1 - 1, mode, out=y)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(y, yw)
+    return y.cpu()
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", SHAPES)
+def test_tc_forward_vs_oracle(mode, B, n_in, n_out, deg, dist):
+    x, coeffs, _ = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    y = run_fwd(x, coeffs, mode)
+    err = o.rel_l2(y, oracle_y(x, coeffs, mode))
+    assert err <= TC_TOL, err
+    # and it is a real tensor-core result, not the fp32 path: some rounding must be visible
+    if deg > 0:
+        assert err > 1e-6
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+def test_tc_bitwise_repeatable_and_row_block_invariant(mode):
+    x, coeffs, _ = make_case(3000, 128, 256, 4, seed=77)
+    a = run_fwd(x, coeffs, mode)
+    b = run_fwd(x, coeffs, mode)
+    assert torch.equal(a, b)
+    # a block of rows starting on a tile boundary gives the same bits as the full batch
+    c = run_fwd(x[1280:2560].contiguous(), coeffs, mode)
+    assert torch.equal(a[1280:2560], c)
+
+
+def test_tc_layer_autograd_mixes_with_fp32_backward():
+    """math_mode='bf16': tensor-core forward, fp32 backward kernels; gradients within the tensor-core tolerance."""
+    torch.manual_seed(4)
+    layer = kan_b200.ChebyKANLayer(128, 64, 8, math_mode="bf16").cuda()
+    x = torch.randn(512, 128, device="cuda", requires_grad=True)
+    y = layer(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ops.check_status()
+    y_ref, dC_ref, dx_ref = o.forward_backward(x.detach().cpu(), layer.cheby_coeffs.detach().cpu(), dy.cpu())
+    assert o.rel_l2(y.detach().cpu(), y_ref) <= 3e-3      # against fp32-weight oracle: bf16 storage included
+    assert o.rel_l2(layer.cheby_coeffs.grad.cpu(), dC_ref) <= TC_TOL
+    assert o.rel_l2(x.grad.cpu(), dx_ref) <= TC_TOL
+
+
+def test_tc_repack_after_optimizer_step():
+    torch.manual_seed(6)
+    layer = kan_b200.ChebyKANLayer(64, 128, 4, math_mode="bf16").cuda()
+    x = torch.randn(256, 64, device="cuda")
+    opt = kan_b200.optim.SGD(layer.parameters(), lr=0.5)
+    y0 = layer(x)
+    y0.sum().backward()
+    opt.step()
+    y1 = layer(x).detach()
+    ref = o.forward(x.cpu(), layer.cheby_coeffs.detach().cpu().bfloat16().float())
+    assert o.rel_l2(y1.cpu(), ref) <= TC_TOL          # the packed copy followed the update
+    assert not torch.equal(y0.detach(), y1)
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+def test_full_size_properties(mode):
+    """Configuration 3 at full size (65536 x 1024 -> 1024, degree 8) through
+    properties that need no CPU oracle run of that size."""
+    B, n_in, n_out, deg = 65536, 1024, 1024, 8
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(B, n_in, device="cuda", generator=g)
+    coeffs = torch.randn(n_in, n_out, deg + 1, device="cuda", generator=g) / (n_in * (deg + 1))
+    packed = ops.pack_coeffs(coeffs, mode)
+    y = ops.forward(x, packed, n_in, n_out, deg, mode)
+    # (1) any row block recomputed alone gives the same bits
+    y_blk = ops.forward(x[32768:32768 + 256].contiguous(), packed, n_in, n_out, deg, mode)
+    assert torch.equal(y[32768:32768 + 256], y_blk)
+    # (2) a CPU oracle on a 64-row sample of the full-size result
+    rows = torch.tensor([0, 1, 127, 128, 4095, 32767, 32768, 65535] + list(range(50000, 50056)))
+    c_cpu = coeffs.cpu()
+    y_ref = oracle_y(x[rows.cuda()].cpu(), c_cpu, mode)
+    assert o.rel_l2(y[rows.cuda()].cpu(), y_ref) <= TC_TOL
+    # (3) linearity in the coefficients: y(C) + y(-C) == 0 exactly (sign flips commute with rounding)
+    packed_neg = ops.pack_coeffs(-coeffs, mode)
+    y_neg = ops.forward(x, packed_neg, n_in, n_out, deg, mode)
+    assert torch.equal(y, -y_neg)
+    # (4) degree-0-only coefficients: every row equals sum_i C[i,o,0]
+    c0 = torch.zeros_like(coeffs)
+    c0[:, :, 0] = coeffs[:, :, 0]
+    y0 = ops.forward(x, ops.pack_coeffs(c0, mode), n_in, n_out, deg, mode)
+    expect = (c0[:, :, 0].bfloat16().float() if mode == "bf16" else c0[:, :, 0]).sum(0)
+    assert o.rel_l2(y0[::997].cpu(), expect.cpu().expand(y0[::997].shape[0], n_out)) <= TC_TOL
+    torch.cuda.synchronize()
+    ops.check_status()
