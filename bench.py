@@ -95,7 +95,7 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def cpu_reference_throughput(rows: int, repeats: int, seed: int = 1003):
+def cpu_reference_throughput(rows: int, budget_s: float, seed: int = 1003):
     """The reference's CPU path for this layer, restated op for op (torch CPU kernels), all host threads."""
     from oracle import chebykan_oracle as o
     torch.set_num_threads(os.cpu_count() or 1)
@@ -106,7 +106,7 @@ def cpu_reference_throughput(rows: int, repeats: int, seed: int = 1003):
     o.forward(x[:256], coeffs)  # warm the thread pool
     best = float("inf")
     times = []
-    for _ in range(repeats):
+    while sum(times) < budget_s and len(times) < 50:
         t0 = time.perf_counter()
         o.forward(x, coeffs)
         dt = time.perf_counter() - t0
@@ -160,6 +160,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     B, n_in, n_out, deg = CFG["batch_per_gpu"], CFG["input_dim"], CFG["output_dim"], CFG["degree"]
+    if args.batch:
+        B = args.batch
     mode = args.mode
     torch.manual_seed(1003)
     layer = kan_b200.ChebyKANLayer(n_in, n_out, deg, math_mode=mode).to(dev)
@@ -211,19 +213,21 @@ def run_ours(args):
         yd = layer(xd)
         y_host.copy_(yd, non_blocking=True)
 
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
+    e2e_value = None
+    if not args.no_e2e:
         e2e_step()
-    e1.record()
-    barrier()
-    te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(te, op=dist.ReduceOp.MAX)
-    e2e_value = world * B / (float(te.item()) / e2e_steps * 1e-3)
-    ops.check_status()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        te = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(te, op=dist.ReduceOp.MAX)
+        e2e_value = world * B / (float(te.item()) / e2e_steps * 1e-3)
+        ops.check_status()
 
     if rank == 0:
         peaks = measured_peaks()
@@ -240,7 +244,7 @@ def run_ours(args):
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode],
             "data": "synthetic",
-            "config": dict(CFG, global_batch=world * B, parallelism=f"dp{world} (rows sharded, no collective)",
+            "config": dict(CFG, batch_per_gpu=B, global_batch=world * B, parallelism=f"dp{world} (rows sharded, no collective)",
                            l2_policy="inputs larger than L2 (x 268 MB + y 268 MB per step vs 126 MB L2)",
                            math_mode=mode),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
@@ -252,9 +256,10 @@ def run_ours(args):
             "clocks": clocks,
         }
         if world == 1 and not args.no_cpu_baseline:
-            v, cores, times = cpu_reference_throughput(8192, 3)
+            v, cores, times = cpu_reference_throughput(32768, 12.0)
             line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                                    "sample": f"8192 of 65536 rows, best of 3 ({sum(times):.1f} s of CPU work)"}
+                                    "sample": f"32768 of 65536 rows per pass, best of {len(times)} passes "
+                                              f"({sum(times):.1f} s of CPU work)"}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
@@ -272,6 +277,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's 65536)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
