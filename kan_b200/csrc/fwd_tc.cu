@@ -12,11 +12,18 @@
 //   warp  8     TMA: cp.async.bulk.tensor loads of the packed coefficient tile
 //               Wt[N][K] (B operand, K-major, 128B swizzle), no multicast.
 //   warp  9     MMA: one elected lane issues tcgen05.mma (cta_group::1,
-//               M=128, N=BN) into one of two TMEM accumulators, and
-//               tcgen05.commit releases shared-memory stages / publishes the
-//               accumulator.
-//   warps 10-13 epilogue: tcgen05.ld TMEM -> registers -> y, overlapped with
-//               the next tile's main loop through the second accumulator.
+//               M=128, N=BN) and tcgen05.commit releases shared-memory stages
+//               / publishes the accumulator.
+//   warps 10-13 epilogue: tcgen05.ld TMEM -> registers -> y.
+//
+// A CTA tile is 128 rows x (NSUB*BN) outputs.  Each generated A stage feeds
+// NSUB MMAs groups (one per BN-wide sub-accumulator), so with BN=256, NSUB=2
+// all 512 TMEM columns hold one tile's accumulators and every basis value is
+// generated out/512 times instead of out/256 times: basis generation, not the
+// tensor pipe, is what limits this kernel.  A and B stages live in separate
+// rings (A: 16 KB per stage, B: BN x 128 bytes per stage) with their own
+// full/empty mbarriers.  With NSUB*BN <= 256 two accumulator buffers
+// alternate, so the epilogue overlaps the next tile's main loop.
 //
 // Phi never reaches device memory.  Every mbarrier wait is bounded: when one
 // gives up the kernel raises an abort flag, records a code in *status, drains
@@ -66,9 +73,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false when another role already aborted or when this
 // wait itself ran out of time (it then raises the abort flag and records `code`).
-__device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                       int32_t* status, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                            int32_t* status, int code) {
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -81,6 +87,11 @@ __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile i
             }
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -134,42 +145,48 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // status codes recorded by a wait that gave up
-enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_FULL = 3, ST_MMA_ACC = 4, ST_EPILOGUE = 5, ST_DRAIN = 6 };
+enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6 };
 
-template <int BN>
+template <int BN, int NSUB>
 struct Smem {
+    static constexpr int NSA = 4;                         // A ring depth
+    static constexpr int NSB = (BN == 256) ? 5 : 8;       // B ring depth
+    static constexpr int NACC = (NSUB * BN <= 256) ? 2 : 1;
     static constexpr int B_STAGE_BYTES = BN * 128;
-    static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int NS = (BN == 256) ? 4 : 6;
-    static constexpr int BAR_OFFSET = NS * STAGE_BYTES;
-    // barriers: full[NS], empty[NS], acc_full[2], acc_empty[2], drain; then tmem slot + abort flag
-    static constexpr int NUM_BARS = 2 * NS + 5;
+    static constexpr int A_OFFSET = 0;
+    static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
+    static constexpr int BAR_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;
+    // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain
+    static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 5;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024 alignment slack
+    static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
-template <int MODE, int BN>
+template <int MODE, int BN, int NSUB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
               int64_t num_tiles, int32_t* status) {
-    using L = Smem<BN>;
-    constexpr int NS = L::NS;
+    using L = Smem<BN, NSUB>;
+    constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC;
+    constexpr int BNT = BN * NSUB;                              // outputs per CTA tile
     constexpr int IB = (MODE == CHEBYKAN_MODE_BF16) ? 64 : 32;  // inputs per K block
     constexpr int CH = (MODE == CHEBYKAN_MODE_BF16) ? 8 : 4;    // elements per 16-byte chunk
     constexpr uint32_t FMT = (MODE == CHEBYKAN_MODE_BF16) ? 1u : 2u;
     constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BN >> 3) << 17) |
                                ((uint32_t)(BM >> 4) << 24);
-    constexpr uint32_t TMEM_COLS = 2 * BN;
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bars = smem_base + L::BAR_OFFSET;
-    auto full_bar = [&](int s) { return bars + 8u * s; };
-    auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
-    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NS + a); };
-    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NS + 2 + a); };
-    const uint32_t drain_bar = bars + 8u * (2 * NS + 4);
+    auto fullA = [&](int s) { return bars + 8u * s; };
+    auto emptyA = [&](int s) { return bars + 8u * (NSA + s); };
+    auto fullB = [&](int s) { return bars + 8u * (2 * NSA + s); };
+    auto emptyB = [&](int s) { return bars + 8u * (2 * NSA + NSB + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NSA + 2 * NSB + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NSA + 2 * NSB + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * NSA + 2 * NSB + 4);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
@@ -178,7 +195,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
     const int nkb = n_iblk * dp1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), NUM_PRODUCERS + 1); mbar_init(empty_bar(s), 1); }
+        for (int s = 0; s < NSA; ++s) { mbar_init(fullA(s), NUM_PRODUCER_WARPS); mbar_init(emptyA(s), 1); }
+        for (int s = 0; s < NSB; ++s) { mbar_init(fullB(s), 1); mbar_init(emptyB(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4 * 32); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -186,7 +204,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
     }
     if (warp == MMA_WARP) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(TMEM_COLS) : "memory");
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tc_fence_before();
@@ -196,13 +214,48 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
 
     if (warp < NUM_PRODUCER_WARPS) {
         // ------------------------------ producers ------------------------------
+        // thread -> 16-byte chunk c of rows r0, r0+32, r0+64, r0+96: 8 lanes cover one
+        // 128-byte row, so x loads are coalesced and the swizzled stores conflict-free
         const int p = threadIdx.x;
-        const int c = p & 7;      // 16-byte chunk inside the 128-byte row
-        const int r0 = p >> 3;    // rows r0, r0+32, r0+64, r0+96
+        const int c = p & 7;
+        const int r0 = p >> 3;
         const bool vec = (in & 3) == 0;
-        float tt[4][CH], tm1[4][CH], tm2[4][CH];
+        const uint32_t st_off = (uint32_t)(r0 * 128 + ((c ^ (r0 & 7)) << 4));  // (r0+32j)&7 == r0&7
+        // recurrence state: ta/tb alternate as (T_{d-1}, T_{d-2}); tt = 2t
+        float tt[4][CH], ta[4][CH], tb[4][CH];
         int s = 0; uint32_t ph = 0;
         bool alive = true;
+
+        // pack one stage's values, wait for the slot, store, publish
+        auto emit = [&](const float (&v)[4][CH]) -> bool {
+            uint32_t w[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (MODE == CHEBYKAN_MODE_BF16) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const __nv_bfloat162 h = __floats2bfloat162_rn(v[j][(2 * q) % CH], v[j][(2 * q + 1) % CH]);
+                        w[j][q] = *reinterpret_cast<const uint32_t*>(&h);
+                    }
+                } else {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[j][q]) : "f"(v[j][q % CH]));
+                }
+            }
+            if (!mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) return false;
+            const uint32_t dst = smem_base + L::A_OFFSET + s * A_STAGE_BYTES + st_off;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                             ::"r"(dst + j * 4096), "r"(w[j][0]), "r"(w[j][1]), "r"(w[j][2]), "r"(w[j][3]) : "memory");
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(fullA(s));
+            if (++s == NSA) { s = 0; ph ^= 1u; }
+            return true;
+        };
+
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const int64_t m0 = (tile / n_tiles) * BM;
             for (int ib = 0; ib < n_iblk && alive; ++ib) {
@@ -231,45 +284,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
                         const float t = tanh_fast(v[e]);
-                        tt[j][e] = 2.f * t; tm1[j][e] = 1.f; tm2[j][e] = t;  // T_0 = 1, T_{-1} = t
+                        tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
                 }
-                for (int d = 0; d < dp1; ++d) {
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) { alive = false; break; }
-                    const uint32_t a_stage = smem_base + s * L::STAGE_BYTES;
+                // degree 0: T_0 = 1 (ta); then degrees alternate between tb and ta
+                if (!emit(ta)) { alive = false; break; }
+                for (int d = 1; d < dp1; d += 2) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        float phi[CH];
-                        if (d == 0) {
+                    for (int j = 0; j < 4; ++j)
 #pragma unroll
-                            for (int e = 0; e < CH; ++e) phi[e] = 1.f;
-                        } else {
+                        for (int e = 0; e < CH; ++e) tb[j][e] = fmaf(tt[j][e], ta[j][e], -tb[j][e]);
+                    if (!emit(tb)) { alive = false; break; }
+                    if (d + 1 < dp1) {
 #pragma unroll
-                            for (int e = 0; e < CH; ++e) {
-                                phi[e] = fmaf(tt[j][e], tm1[j][e], -tm2[j][e]);
-                                tm2[j][e] = tm1[j][e]; tm1[j][e] = phi[e];
-                            }
-                        }
-                        uint32_t w[4];
-                        if (MODE == CHEBYKAN_MODE_BF16) {
+                        for (int j = 0; j < 4; ++j)
 #pragma unroll
-                            for (int q = 0; q < 4; ++q) {
-                                const __nv_bfloat162 h = __floats2bfloat162_rn(phi[(2 * q) % CH], phi[(2 * q + 1) % CH]);
-                                w[q] = *reinterpret_cast<const uint32_t*>(&h);
-                            }
-                        } else {
-#pragma unroll
-                            for (int q = 0; q < 4; ++q)
-                                asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[q]) : "f"(phi[q % CH]));
-                        }
-                        const int row = r0 + 32 * j;
-                        const uint32_t dst = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
-                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
-                                     ::"r"(dst), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                            for (int e = 0; e < CH; ++e) ta[j][e] = fmaf(tt[j][e], tb[j][e], -ta[j][e]);
+                        if (!emit(ta)) { alive = false; break; }
                     }
-                    fence_proxy_async_smem();
-                    mbar_arrive(full_bar(s));
-                    if (++s == NS) { s = 0; ph ^= 1u; }
                 }
             }
         }
@@ -278,15 +310,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool alive = true;
-            int64_t issued = 0;
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                const int n0 = (int)(tile % n_tiles) * BN;
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), L::B_STAGE_BYTES);
-                    tma_load_2d(smem_base + s * L::STAGE_BYTES + A_STAGE_BYTES, &tmap_w, kb * IB, n0, full_bar(s));
-                    ++issued;
-                    if (++s == NS) { s = 0; ph ^= 1u; }
+                const int n0 = (int)(tile % n_tiles) * BNT;
+                for (int kb = 0; kb < nkb && alive; ++kb) {
+#pragma unroll
+                    for (int sub = 0; sub < NSUB; ++sub) {
+                        if (!mbar_wait(emptyB(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
+                        mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES);
+                        tma_load_2d(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
+                                    n0 + sub * BN, fullB(s));
+                        if (++s == NSB) { s = 0; ph ^= 1u; }
+                    }
                 }
             }
             if (!alive) {
@@ -298,27 +332,34 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
         if (lane == 0) {
-            int s = 0; uint32_t ph = 0;
+            int sa = 0; uint32_t pha = 0;
+            int sb = 0; uint32_t phb = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
                 if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
-                for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(full_bar(s), ph, abort_flag, status, ST_MMA_FULL)) { alive = false; break; }
-                    tc_fence_after();
-                    const uint32_t a_addr = smem_base + s * L::STAGE_BYTES;
-                    const uint64_t a_desc = make_smem_desc(a_addr);
-                    const uint64_t b_desc = make_smem_desc(a_addr + A_STAGE_BYTES);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BNT);
+                for (int kb = 0; kb < nkb && alive; ++kb) {
+                    if (!mbar_wait(fullA(sa), pha, abort_flag, status, ST_MMA_A)) { alive = false; break; }
+                    const uint64_t a_desc = make_smem_desc(smem_base + L::A_OFFSET + sa * A_STAGE_BYTES);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)   // 4 x 32 bytes of K per 128-byte row
-                        umma<MODE>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC, (uint32_t)((kb | k) != 0));
-                    umma_commit(empty_bar(s));
-                    if (++s == NS) { s = 0; ph ^= 1u; }
+                    for (int sub = 0; sub < NSUB; ++sub) {
+                        if (!mbar_wait(fullB(sb), phb, abort_flag, status, ST_MMA_B)) { alive = false; break; }
+                        tc_fence_after();
+                        const uint64_t b_desc = make_smem_desc(smem_base + L::B_OFFSET + sb * L::B_STAGE_BYTES);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)   // 4 x 32 bytes of K per 128-byte row
+                            umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                       (uint32_t)((kb | k) != 0));
+                        umma_commit(emptyB(sb));
+                        if (++sb == NSB) { sb = 0; phb ^= 1u; }
+                    }
+                    umma_commit(emptyA(sa));
+                    if (++sa == NSA) { sa = 0; pha ^= 1u; }
                 }
                 if (alive) umma_commit(acc_full_bar(acc));
-                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+                if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
             }
             if (!alive) {
                 // wait (bounded) until the MMAs already issued have retired
@@ -335,14 +376,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
         const bool vec = (out & 3) == 0;
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const int64_t row = (tile / n_tiles) * BM + q * 32 + lane;
-            const int n0 = (int)(tile % n_tiles) * BN;
+            const int n0 = (int)(tile % n_tiles) * BNT;
             // tcgen05.ld is warp-collective: leave the loop only as a whole warp
             const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, ST_EPILOGUE);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BNT);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < BNT; c0 += 32) {
+                if (n0 + c0 >= out) break;   // padded outputs: nothing to store (uniform across the warp)
                 uint32_t r[32];
                 tmem_ld32(taddr + c0, r);
                 tmem_ld_wait();
@@ -365,7 +407,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
             }
             tc_fence_before();
             mbar_arrive(acc_empty_bar(acc));
-            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+            if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
         }
     }
 
@@ -373,7 +415,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
     __syncthreads();
     if (warp == MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
     }
 }
 
@@ -394,27 +436,35 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-template <int MODE, int BN>
+template <int MODE, int BN, int NSUB>
 int launch_one(const CUtensorMap& tmap, const float* x, float* y, int64_t B, int in, int out, int dp1,
                int n_pad, int32_t* status, cudaStream_t s) {
-    using L = Smem<BN>;
+    using L = Smem<BN, NSUB>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN>,
+        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN, NSUB>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
         attr_set[dev] = true;
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    const int n_tiles = n_pad / BN;
+    const int n_tiles = (int)ceil_div(n_pad, BN * NSUB);
     const int64_t num_tiles = ceil_div(B, BM) * n_tiles;
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    fwd_tc_kernel<MODE, BN><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, x, y, B, in, out, dp1, n_tiles,
-                                                                num_tiles, status);
+    fwd_tc_kernel<MODE, BN, NSUB><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, x, y, B, in, out, dp1, n_tiles,
+                                                                      num_tiles, status);
     return check_cuda(cudaGetLastError());
+}
+
+template <int MODE>
+int launch_mode(const CUtensorMap& tmap, int bn, int nsub, const float* x, float* y, int64_t B, int in, int out,
+                int dp1, int n_pad, int32_t* status, cudaStream_t s) {
+    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
+    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
+    return launch_one<MODE, 128, 1>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
 }
 
 }  // namespace
@@ -424,7 +474,10 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     const PackedDims p = packed_dims(in, out, deg, mode);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
-    const int bn = (p.n_pad % 256 == 0) ? 256 : 128;
+    // tile width: 2 x 256 outputs (all of TMEM) when there are that many, else 256 or 128
+    int bn = 128, nsub = 1;
+    if (p.n_pad >= 384) { bn = 256; nsub = 2; }
+    else if (p.n_pad == 256) { bn = 256; }
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
     const cuuint64_t strides[1] = {(cuuint64_t)(p.k_pad * p.elem)};
@@ -432,17 +485,15 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = (mode == CHEBYKAN_MODE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+    // rows of the box past n_pad (ragged last tile) are filled with zeros
     const CUresult r = encode(&tmap, dt, 2, const_cast<void*>(wt), dims, strides, box, estr,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
     const int dp1 = (int)deg + 1;
-    if (mode == CHEBYKAN_MODE_BF16) {
-        if (bn == 256) return launch_one<CHEBYKAN_MODE_BF16, 256>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
-        return launch_one<CHEBYKAN_MODE_BF16, 128>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
-    }
-    if (bn == 256) return launch_one<CHEBYKAN_MODE_TF32, 256>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
-    return launch_one<CHEBYKAN_MODE_TF32, 128>(tmap, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+    if (mode == CHEBYKAN_MODE_BF16)
+        return launch_mode<CHEBYKAN_MODE_BF16>(tmap, bn, nsub, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+    return launch_mode<CHEBYKAN_MODE_TF32>(tmap, bn, nsub, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
 }
 
 }  // namespace chebykan
