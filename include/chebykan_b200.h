@@ -38,6 +38,7 @@ extern "C" {
 #define CHEBYKAN_ETIMEOUT     -5  /* a bounded device-side wait gave up             */
 #define CHEBYKAN_EWORKSPACE   -6  /* workspace / packed buffer too small            */
 #define CHEBYKAN_EDEVICE      -7  /* current device is not compute capability 10.x  */
+#define CHEBYKAN_ESTATIC      -8  /* problem needs more than the built-in 16 MiB scratch */
 
 /* arithmetic mode of the contraction */
 #define CHEBYKAN_MODE_FP32 0  /* fp32 FFMA on CUDA cores, correctly rounded tanh   */
@@ -92,6 +93,32 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs,
                         void* workspace, int64_t workspace_bytes,
                         int64_t B, int64_t in, int64_t out, int64_t deg,
                         int mode, int accumulate, int32_t* status, void* stream);
+
+/*
+ * chebykan_bwd_dcoeff without a workspace argument, for callers that cannot
+ * allocate device memory: code that only receives raw pointers from a host
+ * owning all of the GPU's memory (a server that gave the whole device to its
+ * own pool, a plugin callback where CUDA allocation calls are off limits, a
+ * real-time loop that must not hit cudaMalloc's implicit synchronisation).
+ * It has no counterpart in the reference, which leaves all memory to PyTorch.
+ *   - Scratch is a 16 MiB array built into the library; every GPU that loads
+ *     the library keeps it reserved until the process exits.
+ *   - Shapes whose batch-split partial sums need more than 16 MiB (what
+ *     chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DCOEFF, ...) reports) are
+ *     refused with CHEBYKAN_ESTATIC; use chebykan_bwd_dcoeff for those.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     outside any stream capture.  No call allocates or frees anything.
+ *   - All calls share the one array.  A call overwrites every byte it later
+ *     reads, so leftovers of earlier calls are harmless, but two calls that
+ *     may run on the GPU at the same time (different streams, different host
+ *     threads) race on it: keep calls on one device in stream order.
+ * Arithmetic is fp32 (the only dC path so far) and the result is identical to
+ * chebykan_bwd_dcoeff's.
+ */
+int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float* dcoeffs,
+                               int64_t B, int64_t in, int64_t out, int64_t deg,
+                               int accumulate, void* stream);
 
 /*
  * Input gradient dx[b,i] = (1-t^2) * sum_d T_d'(t) * sum_o dY[b,o] C[i,o,d],

@@ -29,6 +29,8 @@ SIGNATURES = {
                              c_void_p, c_void_p]),
     "chebykan_bwd_dcoeff": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "chebykan_bwd_dcoeff_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                                           c_int, c_void_p]),
     "chebykan_bwd_dx": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_int, c_void_p, c_void_p]),
     "chebykan_sgd_step": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_void_p]),

@@ -50,6 +50,7 @@ const char* chebykan_strerror(int code) {
         case CHEBYKAN_ETIMEOUT: return "a bounded device-side wait gave up";
         case CHEBYKAN_EWORKSPACE: return "workspace or packed buffer too small";
         case CHEBYKAN_EDEVICE: return "current device is not compute capability 10.x (B200)";
+        case CHEBYKAN_ESTATIC: return "shape needs more scratch than the library's built-in 16 MiB array; use the workspace variant";
         default: return "unknown error code";
     }
 }

@@ -241,6 +241,43 @@ int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int
 }
 
 // ---------------------------------------------------------------------------
+// Workspace-free entry point.
+//
+// chebykan_bwd_dcoeff needs a caller-provided workspace whenever it splits the
+// batch over several CTAs.  Some callers have no way to provide one: they are
+// handed raw device pointers by a host that owns all device memory (a serving
+// process that reserved the whole GPU for its own pool at start-up, a plugin
+// callback in which CUDA allocation calls are forbidden, a latency-critical
+// loop that cannot afford the device-wide synchronisation cudaMalloc implies).
+// For them the same kernels run against a fixed scratch array that is part of
+// the library image: it is reserved on every GPU that loads the library, for
+// the life of the process, whether or not this entry point is ever called.
+// ---------------------------------------------------------------------------
+constexpr int64_t STATIC_SCRATCH_BYTES = (int64_t)16 << 20;   // 16 MiB
+static __device__ __align__(256) unsigned char g_dcoeff_scratch[STATIC_SCRATCH_BYTES];
+
+// Device address of g_dcoeff_scratch per device ordinal.  In host code the
+// array's name is only a handle for the runtime, not a device address, so the
+// address is looked up once per device with that device current.
+static void* g_dcoeff_scratch_addr[64] = {nullptr};
+
+static int static_scratch_address(void** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return check_cuda(e);
+    if (dev < 0 || dev >= 64) return CHEBYKAN_EDEVICE;
+    if (g_dcoeff_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_dcoeff_scratch);
+        if (e != cudaSuccess) return check_cuda(e);
+        if (ptr == nullptr) return CHEBYKAN_ECUDA;
+        g_dcoeff_scratch_addr[dev] = ptr;
+    }
+    *out = g_dcoeff_scratch_addr[dev];
+    return CHEBYKAN_OK;
+}
+
+// ---------------------------------------------------------------------------
 // dx: tile = 64 rows x (TI inputs x all degrees); G = dY * C^T accumulated over
 // all outputs (8 per stage), then each (row, input) pair folds its deg+1 values
 // of G with d*U_{d-1}(t) and the tanh derivative.
@@ -364,3 +401,31 @@ int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* 
 }
 
 }  // namespace chebykan
+
+// Declared in include/chebykan_b200.h.  Same result as chebykan_bwd_dcoeff (same
+// kernels, same batch split, same summation order), no workspace argument.
+extern "C" int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float* dcoeffs, int64_t B,
+                                          int64_t in, int64_t out, int64_t deg, int accumulate,
+                                          void* stream) {
+    using namespace chebykan;
+    if (B < 0 || in < 1 || out < 1 || deg < 0 || deg > 127 || in > (1 << 20) || out > (1 << 20) ||
+        B > ((int64_t)1 << 31) || in * (deg + 1) > ((int64_t)1 << 24) || !dcoeffs)
+        return CHEBYKAN_EINVAL;
+    if (!aligned16(dcoeffs)) return CHEBYKAN_EALIGN;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (B == 0) {
+        if (!accumulate) return check_cuda(cudaMemsetAsync(dcoeffs, 0, in * out * (deg + 1) * 4, s));
+        return CHEBYKAN_OK;
+    }
+    if (!x || !dy) return CHEBYKAN_EINVAL;
+    if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
+    // the partial sums of every batch slice must fit the fixed array
+    const int64_t need = dcoeff_workspace_bytes(B, in, out, deg, CHEBYKAN_MODE_FP32);
+    if (need > STATIC_SCRATCH_BYTES) return CHEBYKAN_ESTATIC;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc) return rc;
+    // Every slice's tile overwrites its whole part of the scratch before the
+    // reduction reads it, so nothing left by an earlier call needs clearing.
+    return launch_dcoeff_ffma(x, dy, dcoeffs, scratch, STATIC_SCRATCH_BYTES, B, in, out, deg, accumulate, s);
+}
