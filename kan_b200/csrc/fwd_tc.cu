@@ -15,6 +15,10 @@
 //               M=128, N=BN) and tcgen05.commit releases shared-memory stages
 //               / publishes the accumulator.
 //   warps 10-13 epilogue: tcgen05.ld TMEM -> registers -> y.
+//   warp  14    TMA: prefetches the next [128 rows x IB inputs] fp32 tile of x into
+//               shared memory while the producers work on the current one, so no
+//               producer ever waits on a global load (when in % 4 != 0 the tile is
+//               not TMA-addressable and the producers load x themselves).
 //
 // A CTA tile is 128 rows x (NSUB*BN) outputs.  Each generated A stage feeds
 // NSUB MMAs groups (one per BN-wide sub-accumulator), so with BN=256, NSUB=2
@@ -38,10 +42,10 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int NUM_PRODUCER_WARPS = 8;
-constexpr int NUM_PRODUCERS = NUM_PRODUCER_WARPS * 32;
 constexpr int TMA_WARP = 8;
 constexpr int MMA_WARP = 9;
-constexpr int NUM_THREADS = 14 * 32;
+constexpr int X_WARP = 14;
+constexpr int NUM_THREADS = 15 * 32;
 constexpr int A_STAGE_BYTES = BM * 128;
 constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
@@ -145,26 +149,30 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // status codes recorded by a wait that gave up
-enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6 };
+enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6, ST_X_LOAD = 7,
+       ST_X_WAIT = 8 };
 
 template <int BN, int NSUB>
 struct Smem {
     static constexpr int NSA = 4;                         // A ring depth
-    static constexpr int NSB = (BN == 256) ? 5 : 8;       // B ring depth
+    static constexpr int NSB = (BN == 256) ? 4 : 8;       // B ring depth
     static constexpr int NACC = (NSUB * BN <= 256) ? 2 : 1;
     static constexpr int B_STAGE_BYTES = BN * 128;
     static constexpr int A_OFFSET = 0;
     static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
-    static constexpr int BAR_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;
-    // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain
-    static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 5;
+    static constexpr int X_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;   // x tile: 128 rows x 128 bytes... x 2
+    static constexpr int X_BYTES = BM * 256;                          // up to 64 fp32 inputs per row
+    static constexpr int BAR_OFFSET = X_OFFSET + X_BYTES;
+    // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain x_full x_empty
+    static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 7;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024 alignment slack
     static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
 template <int MODE, int BN, int NSUB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restrict__ x,
+fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+              int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
               int64_t num_tiles, int32_t* status) {
     using L = Smem<BN, NSUB>;
@@ -187,6 +195,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NSA + 2 * NSB + a); };
     auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NSA + 2 * NSB + 2 + a); };
     const uint32_t drain_bar = bars + 8u * (2 * NSA + 2 * NSB + 4);
+    const uint32_t x_full_bar = bars + 8u * (2 * NSA + 2 * NSB + 5);
+    const uint32_t x_empty_bar = bars + 8u * (2 * NSA + 2 * NSB + 6);
+    constexpr uint32_t X_TILE_BYTES = BM * IB * 4;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
@@ -199,6 +210,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
         for (int s = 0; s < NSB; ++s) { mbar_init(fullB(s), 1); mbar_init(emptyB(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4 * 32); }
         mbar_init(drain_bar, 1);
+        mbar_init(x_full_bar, 1);
+        mbar_init(x_empty_bar, NUM_PRODUCER_WARPS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -224,6 +237,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
         // recurrence state: ta/tb alternate as (T_{d-1}, T_{d-2}); tt = 2t
         float tt[4][CH], ta[4][CH], tb[4][CH];
         int s = 0; uint32_t ph = 0;
+        uint32_t xph = 0;
         bool alive = true;
 
         // pack one stage's values, wait for the slot, store, publish
@@ -260,13 +274,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
             const int64_t m0 = (tile / n_tiles) * BM;
             for (int ib = 0; ib < n_iblk && alive; ++ib) {
                 const int i_base = ib * IB + c * CH;
+                if (use_x_tma) {
+                    if (!mbar_wait(x_full_bar, xph, abort_flag, status, ST_X_WAIT)) { alive = false; break; }
+                    xph ^= 1u;
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int64_t row = m0 + r0 + 32 * j;
                     float v[CH];
 #pragma unroll
                     for (int e = 0; e < CH; ++e) v[e] = 0.f;
-                    if (row < B) {
+                    if (use_x_tma) {
+                        // x tile in shared memory: [128 rows][IB fp32]; rows and inputs past the ends read as 0
+                        const uint32_t src = smem_base + L::X_OFFSET + (uint32_t)((r0 + 32 * j) * (IB * 4) + c * (CH * 4));
+#pragma unroll
+                        for (int q = 0; q < CH / 4; ++q)
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(v[4 * q]), "=f"(v[4 * q + 1]), "=f"(v[4 * q + 2]), "=f"(v[4 * q + 3])
+                                         : "r"(src + 16 * q));
+                    } else if (row < B) {
                         const float* src = x + row * in + i_base;
                         if (vec) {
 #pragma unroll
@@ -286,6 +312,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
                         const float t = tanh_fast(v[e]);
                         tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
+                }
+                if (use_x_tma) {
+                    // the tile is in registers now: hand the buffer back for the next prefetch
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(x_empty_bar);
                 }
                 // degree 0: T_0 = 1 (ta); then degrees alternate between tb and ta
                 if (!emit(ta)) { alive = false; break; }
@@ -325,6 +356,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
             }
             if (!alive) {
                 // let the copies already issued land before the CTA gives up its shared memory
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000ull) { }
+            }
+        }
+    } else if (warp == X_WARP) {
+        // ------------------------------ x tile prefetch ------------------------------
+        if (lane == 0 && use_x_tma) {
+            uint32_t xph = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                const int m0 = (int)((tile / n_tiles) * BM);
+                for (int ib = 0; ib < n_iblk; ++ib) {
+                    if (!mbar_wait(x_empty_bar, xph ^ 1u, abort_flag, status, ST_X_LOAD)) { alive = false; break; }
+                    mbar_arrive_expect_tx(x_full_bar, X_TILE_BYTES);
+                    tma_load_2d(smem_base + L::X_OFFSET, &tmap_x, ib * IB, m0, x_full_bar);
+                    xph ^= 1u;
+                }
+            }
+            if (!alive) {
                 const uint64_t t0 = globaltimer_ns();
                 while (globaltimer_ns() - t0 < 200000ull) { }
             }
@@ -373,7 +423,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0; uint32_t acc_ph = 0;
         bool alive = true;
-        const bool vec = (out & 3) == 0;
+        const bool vec4 = (out & 3) == 0;
+        const bool vec8 = (out & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
+        // one row's 32 consecutive outputs from registers to y
+        auto store32 = [&](const uint32_t (&r)[32], int64_t row, int col0) {
+            if (row >= B) return;
+            float* dst = y + row * out + col0;
+            if (vec8 && col0 + 32 <= out) {
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                                 ::"l"(dst + 8 * g), "r"(r[8 * g]), "r"(r[8 * g + 1]), "r"(r[8 * g + 2]),
+                                   "r"(r[8 * g + 3]), "r"(r[8 * g + 4]), "r"(r[8 * g + 5]), "r"(r[8 * g + 6]),
+                                   "r"(r[8 * g + 7]) : "memory");
+            } else {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                    const int col = col0 + 4 * g;
+                    if (vec4 && col + 3 < out) {
+                        *reinterpret_cast<float4*>(dst + 4 * g) =
+                            make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                        __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            if (col + e < out) dst[4 * g + e] = __uint_as_float(r[4 * g + e]);
+                    }
+                }
+            }
+        };
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const int64_t row = (tile / n_tiles) * BM + q * 32 + lane;
             const int n0 = (int)(tile % n_tiles) * BNT;
@@ -382,31 +460,26 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const float* __restric
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BNT);
+            // columns that hold real outputs (a ragged last tile ends early), in chunks of 32
+            int ncols = out - n0;
+            if (ncols > BNT) ncols = BNT;
+            const int nchunks = (ncols + 31) >> 5;
+            // two register buffers: the TMEM load of chunk i+1 is in flight while chunk i is stored
+            uint32_t ra[32], rb[32];
+            tmem_ld32(taddr, ra);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BNT; c0 += 32) {
-                if (n0 + c0 >= out) break;   // padded outputs: nothing to store (uniform across the warp)
-                uint32_t r[32];
-                tmem_ld32(taddr + c0, r);
+            for (int ch = 0; ch < nchunks; ch += 2) {
                 tmem_ld_wait();
-                if (row < B) {
-                    float* dst = y + row * out + n0 + c0;
-#pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        const int col = n0 + c0 + 4 * g;
-                        if (vec && col + 3 < out) {
-                            *reinterpret_cast<float4*>(dst + 4 * g) =
-                                make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                                            __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
-                        } else {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e)
-                                if (col + e < out) dst[4 * g + e] = __uint_as_float(r[4 * g + e]);
-                        }
-                    }
+                if (ch + 1 < nchunks) tmem_ld32(taddr + (ch + 1) * 32, rb);
+                else { tc_fence_before(); mbar_arrive(acc_empty_bar(acc)); }   // accumulator fully read
+                store32(ra, row, n0 + ch * 32);
+                if (ch + 1 < nchunks) {
+                    tmem_ld_wait();
+                    if (ch + 2 < nchunks) tmem_ld32(taddr + (ch + 2) * 32, ra);
+                    else { tc_fence_before(); mbar_arrive(acc_empty_bar(acc)); }
+                    store32(rb, row, n0 + (ch + 1) * 32);
                 }
             }
-            tc_fence_before();
-            mbar_arrive(acc_empty_bar(acc));
             if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
         }
     }
@@ -437,8 +510,8 @@ EncodeTiledFn get_encode_fn() {
 }
 
 template <int MODE, int BN, int NSUB>
-int launch_one(const CUtensorMap& tmap, const float* x, float* y, int64_t B, int in, int out, int dp1,
-               int n_pad, int32_t* status, cudaStream_t s) {
+int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
+               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s) {
     using L = Smem<BN, NSUB>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -454,17 +527,17 @@ int launch_one(const CUtensorMap& tmap, const float* x, float* y, int64_t B, int
     const int n_tiles = (int)ceil_div(n_pad, BN * NSUB);
     const int64_t num_tiles = ceil_div(B, BM) * n_tiles;
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    fwd_tc_kernel<MODE, BN, NSUB><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, x, y, B, in, out, dp1, n_tiles,
-                                                                      num_tiles, status);
+    fwd_tc_kernel<MODE, BN, NSUB><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x, y, B, in, out,
+                                                                      dp1, n_tiles, num_tiles, status);
     return check_cuda(cudaGetLastError());
 }
 
 template <int MODE>
-int launch_mode(const CUtensorMap& tmap, int bn, int nsub, const float* x, float* y, int64_t B, int in, int out,
-                int dp1, int n_pad, int32_t* status, cudaStream_t s) {
-    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
-    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
-    return launch_one<MODE, 128, 1>(tmap, x, y, B, in, out, dp1, n_pad, status, s);
+int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, const float* x, float* y,
+                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s) {
+    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
+    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
+    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
 }
 
 }  // namespace
@@ -490,10 +563,24 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    // x[B][in] fp32 as a TMA tensor: needs a 16-byte row pitch; rows/inputs outside read as zeros
+    CUtensorMap tmap_x = tmap;
+    const int use_x_tma = (in % 4 == 0) ? 1 : 0;
+    if (use_x_tma) {
+        const cuuint64_t xdims[2] = {(cuuint64_t)in, (cuuint64_t)B};
+        const cuuint64_t xstrides[1] = {(cuuint64_t)(in * 4)};
+        const cuuint32_t xbox[2] = {(cuuint32_t)p.ib, (cuuint32_t)BM};
+        const CUresult rx = encode(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), xdims, xstrides,
+                                   xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rx != CUDA_SUCCESS) { set_last_cuda_error((int)rx); return CHEBYKAN_ECUDA; }
+    }
     const int dp1 = (int)deg + 1;
     if (mode == CHEBYKAN_MODE_BF16)
-        return launch_mode<CHEBYKAN_MODE_BF16>(tmap, bn, nsub, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
-    return launch_mode<CHEBYKAN_MODE_TF32>(tmap, bn, nsub, x, y, B, (int)in, (int)out, dp1, (int)p.n_pad, status, s);
+        return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
+                                               (int)p.n_pad, status, s);
+    return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
+                                           (int)p.n_pad, status, s);
 }
 
 }  // namespace chebykan
