@@ -99,7 +99,7 @@ int chebykan_fwd(const float* x, const void* packed, float* y, int64_t B, int64_
 
 int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* workspace,
                         int64_t workspace_bytes, int64_t B, int64_t in, int64_t out, int64_t deg,
-                        int mode, int accumulate, int32_t* /*status*/, void* stream) {
+                        int mode, int accumulate, int32_t* status, void* stream) {
     if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !dcoeffs) return CHEBYKAN_EINVAL;
     if (!aligned16(dcoeffs) || !aligned16(workspace)) return CHEBYKAN_EALIGN;
     int rc = check_device();
@@ -111,7 +111,13 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* w
     }
     if (!x || !dy) return CHEBYKAN_EINVAL;
     if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
-    // every mode currently accumulates dC in fp32 on the FFMA pipe
+    // tf32 and bf16 modes: tcgen05 kind::tf32 (bf16 operands would miss the 2e-3 budget for this
+    // product); shapes it does not cover, and fp32 mode, accumulate in fp32 on the FFMA pipe
+    if (mode != CHEBYKAN_MODE_FP32 && dcoeff_tc_supported(B, in, out, deg)) {
+        if (!status) return CHEBYKAN_EINVAL;
+        return launch_dcoeff_tc(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate,
+                                status, s);
+    }
     return launch_dcoeff_ffma(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg,
                               accumulate, s);
 }

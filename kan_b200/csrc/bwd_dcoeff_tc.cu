@@ -1,0 +1,362 @@
+// Tensor-core coefficient gradient for sm_100a (tcgen05 kind::tf32):
+//   dC[(i,d), o] = sum_b T_d(tanh x[b,i]) * dY[b,o]
+// i.e. D[M, N] = A[M, K] * B[K, N] with M = (input, degree) slots, N = outputs and the
+// BATCH as the contraction dimension K.  It is the dW half of what autograd derives
+// from reference kan/basis/chebyshev.py:101,119-145, with Phi regenerated on chip.
+//
+//   A (Phi^T, generated): K-major tile [128 slots][32 batch rows] tf32, 128B swizzle.  A CTA owns
+//       TI = 128/(deg+1) inputs with all their degrees (slot = ii*(deg+1) + d, the
+//       coefficient tensor's own order).  A producer lane owns one input and four
+//       consecutive batch rows: it runs four recurrences side by side and writes one
+//       16-byte chunk per degree.  A producer warp is bound to one stage of the ring
+//       (alone, or as one of two warps that split the stage's pairs) and prefetches the
+//       x values of its next K block before it generates the current one.
+//   B (dY, via TMA): MN-major tile [32 batch rows][BN outputs] fp32 straight from the
+//       row-major dY, as BN/32 boxes of 32 rows x 128 bytes in the 32-byte-atom 128B
+//       swizzle (the only layout the tensor pipe takes for MN-major 32-bit operands).
+//       The tensor pipe reads fp32 as tf32.
+//   D: 128 x BN fp32 in TMEM for the CTA's whole slice of the batch; the batch is split
+//      over CTAs and the slices' partial sums are added by dcoeff_reduce (fixed order).
+//
+// Precision: tf32 operands, fp32 accumulate (plain bf16 operands would miss the 2e-3
+// budget for this product).  Every mbarrier wait is bounded, as in the forward kernel.
+#include "tc_common.cuh"
+
+namespace chebykan {
+
+namespace {
+using namespace tc;
+
+constexpr int DC_PRODUCER_WARPS = 8;
+constexpr int DC_TMA_WARP = 8;
+constexpr int DC_MMA_WARP = 9;
+constexpr int DC_THREADS = 10 * 32;
+constexpr int DC_A_STAGE = 128 * 128;     // 128 slots x 32 tf32
+constexpr int DC_KB = 32;                 // batch rows per K block
+constexpr int DC_MAX_ROUNDS = 8;          // (input, 4-row chunk) pairs per lane per K block: TI*8/32
+
+enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_MMA_B = 14, DST_EPILOGUE = 15 };
+
+template <int BN>
+struct DcSmem {
+    static constexpr int B_STAGE = BN * 128;                 // 32 rows x BN fp32
+    static constexpr int STAGE = DC_A_STAGE + B_STAGE;
+    // NS divides the 8 producer warps: 8/NS warps share one stage and split its pairs, and a
+    // warp only ever fills its own stage, so it is never more than one mbarrier phase ahead
+    static constexpr int NS = (BN == 64) ? 8 : 4;
+    static constexpr int BAR_OFFSET = NS * STAGE;
+    static constexpr int NUM_BARS = 3 * NS + 2;              // fullA, fullB, empty, acc_full, drain
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+    static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+};
+
+// MN-major tf32 operand.  32-bit MN-major operands exist only in the "128B swizzle with 32-byte
+// atoms" layout: rows of 128 bytes (32 outputs), groups of 4 K rows (512 B) inside which the
+// 32-byte chunk index is XORed with the row index; TMA writes it with SWIZZLE_128B_ATOM_32B.
+// Column blocks of 32 outputs are 32 rows = 4096 B apart.
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)(4096 >> 4) << 16;   // leading byte offset: next 128-byte block along N
+    d |= (uint64_t)(512 >> 4) << 32;    // stride byte offset: next group of 4 K rows
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;             // SWIZZLE_128B_BASE32B
+    return d;
+}
+
+template <int BN>
+__global__ void __launch_bounds__(DC_THREADS, 1)
+dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __restrict__ x,
+                 float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
+                 int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
+                 int32_t* status) {
+    using L = DcSmem<BN>;
+    constexpr int NS = L::NS;
+    // tf32 x tf32 -> f32, A K-major, B MN-major, M = 128, N = BN
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
+                               ((uint32_t)(128 >> 4) << 24);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + L::BAR_OFFSET;
+    auto fullA = [&](int s) { return bars + 8u * s; };
+    auto fullB = [&](int s) { return bars + 8u * (NS + s); };
+    auto empty = [&](int s) { return bars + 8u * (2 * NS + s); };
+    const uint32_t acc_full_bar = bars + 8u * (3 * NS);
+    const uint32_t drain_bar = bars + 8u * (3 * NS + 1);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int bid = blockIdx.x;
+    const int n_t = bid % n_tiles; bid /= n_tiles;
+    const int i_t = bid % i_tiles; bid /= i_tiles;
+    const int split = bid;
+    const int i0 = i_t * TI, n0 = n_t * BN;
+    const int ti = min(TI, in - i0);
+    const int64_t b_begin = (int64_t)split * rows_per_split;      // a multiple of 32
+    const int64_t b_end = min(B, b_begin + rows_per_split);
+    const int nkb = (int)((b_end - b_begin + DC_KB - 1) / DC_KB);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(fullA(s), DC_PRODUCER_WARPS / NS); mbar_init(fullB(s), 1); mbar_init(empty(s), 1);
+        }
+        mbar_init(acc_full_bar, 1);
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DC_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < DC_PRODUCER_WARPS) {
+        // ------------------------------ producers ------------------------------
+        constexpr int G = DC_PRODUCER_WARPS / NS;   // warps sharing a stage
+        const int my_stage = warp % NS, sub = warp / NS;
+        const int npairs = ti * 8;                  // (input, chunk of 4 batch rows)
+        const int rounds = (npairs + 32 * G - 1) / (32 * G);      // <= DC_MAX_ROUNDS
+        float xn[DC_MAX_ROUNDS][4];
+        auto load_x = [&](int kb) {
+            const int64_t b0 = b_begin + (int64_t)kb * DC_KB;
+#pragma unroll
+            for (int r = 0; r < DC_MAX_ROUNDS; ++r) {
+                const int pair = lane + 32 * (G * r + sub);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xn[r][e] = 0.f;
+                if (r < rounds && pair < npairs && kb < nkb) {
+                    const int ii = pair >> 3, c = pair & 7;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int64_t row = b0 + 4 * c + e;
+                        if (row < b_end) xn[r][e] = __ldg(x + row * in + i0 + ii);
+                    }
+                }
+            }
+        };
+        bool alive = true;
+        load_x(my_stage);
+        for (int kb = my_stage; kb < nkb && alive; kb += NS) {
+            const int s = my_stage;
+            const uint32_t ph = (uint32_t)((kb / NS) & 1);
+            float xc[DC_MAX_ROUNDS][4];
+#pragma unroll
+            for (int r = 0; r < DC_MAX_ROUNDS; ++r)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) xc[r][e] = xn[r][e];
+            load_x(kb + NS);            // in flight while this block is generated
+            if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_PRODUCER)) { alive = false; break; }
+            const uint32_t a_stage = smem_base + s * L::STAGE;
+#pragma unroll
+            for (int r = 0; r < DC_MAX_ROUNDS; ++r) {
+                const int pair = lane + 32 * (G * r + sub);
+                if (r < rounds && pair < npairs) {
+                    const int ii = pair >> 3, c = pair & 7;
+                    float t2[4], ta[4], tb[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float t = tanh_fast(xc[r][e]);
+                        t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
+                    }
+                    int row = ii * dp1;
+                    for (int d = 0; d < dp1; ++d, ++row) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            float v = ta[e];
+                            if (d > 0) { v = fmaf(t2[e], ta[e], -tb[e]); tb[e] = ta[e]; ta[e] = v; }
+                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[e]) : "f"(v));
+                        }
+                        const uint32_t dsta = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
+                        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                     ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                    }
+                }
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(fullA(s));
+        }
+    } else if (warp == DC_TMA_WARP) {
+        // ------------------------------ dY loads ------------------------------
+        if (lane == 0) {
+            bool alive = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % NS;
+                const uint32_t ph = (uint32_t)((kb / NS) & 1);
+                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
+                mbar_arrive_expect_tx(fullB(s), L::B_STAGE);
+                const uint32_t b_stage = smem_base + s * L::STAGE + DC_A_STAGE;
+                const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
+#pragma unroll
+                for (int m = 0; m < BN / 32; ++m)
+                    tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, fullB(s));
+            }
+            if (!alive) {
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000ull) { }
+            }
+        }
+    } else {
+        // ------------------------------ MMA issue ------------------------------
+        if (lane == 0) {
+            bool alive = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % NS;
+                const uint32_t ph = (uint32_t)((kb / NS) & 1);
+                if (!mbar_wait(fullA(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
+                if (!mbar_wait(fullB(s), ph, abort_flag, status, DST_MMA_B)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t a_addr = smem_base + s * L::STAGE;
+                const uint64_t a_desc = make_smem_desc(a_addr);
+                const uint64_t b_desc = make_smem_desc_mn(a_addr + DC_A_STAGE);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)   // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
+                    umma<CHEBYKAN_MODE_TF32>(tmem_base, a_desc + 2 * k, b_desc + 64 * k, IDESC,
+                                             (uint32_t)((kb | k) != 0));
+                umma_commit(empty(s));
+            }
+            if (alive) umma_commit(acc_full_bar);
+            else {
+                umma_commit(drain_bar);
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
+            }
+        }
+    }
+
+    // ------------------------------ epilogue: warps 0-3 own TMEM lanes 32w..32w+31 ------------------------------
+    if (warp < 4) {
+        const bool ok = nkb == 0 ? true : mbar_wait(acc_full_bar, 0, abort_flag, status, DST_EPILOGUE);
+        if (__all_sync(0xffffffffu, ok)) {
+            tc_fence_after();
+            const int kk = warp * 32 + lane;                 // slot = TMEM lane
+            const bool valid = kk < ti * dp1;
+            const int ii = kk / dp1, d = kk % dp1;
+            float* base = dst + (int64_t)split * split_stride + ((int64_t)(i0 + ii) * out) * dp1 + d;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                if (n0 + c0 >= out) break;
+                uint32_t r[32];
+                if (nkb > 0) { tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c0, r); tmem_ld_wait(); }
+                else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) r[e] = 0u;
+                }
+                if (valid) {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) {
+                        const int col = n0 + c0 + e;
+                        if (col < out) {
+                            float* q = base + (int64_t)col * dp1;
+                            const float v = __uint_as_float(r[e]);
+                            *q = add_to_dst ? (*q + v) : v;
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == DC_MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+struct DcTcPlan { int TI, i_tiles, bn, n_tiles, splits; int64_t rows_per_split; };
+
+DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    DcTcPlan p{};
+    const int dp1 = (int)deg + 1;
+    p.TI = 128 / dp1;
+    if (p.TI > in) p.TI = (int)in;
+    p.i_tiles = (int)ceil_div(in, p.TI);
+    p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : 256);
+    p.n_tiles = (int)ceil_div(out, p.bn);
+    const int64_t base = (int64_t)p.i_tiles * p.n_tiles;
+    int64_t splits = ceil_div(2 * 148, base);
+    const int64_t max_splits = ceil_div(B, 1024);
+    if (splits > max_splits) splits = max_splits;
+    if (splits < 1) splits = 1;
+    p.rows_per_split = round_up(ceil_div(B, splits), DC_KB);
+    p.splits = (int)ceil_div(B, p.rows_per_split);
+    if (p.splits < 1) p.splits = 1;
+    return p;
+}
+
+template <int BN>
+int launch_dc(const CUtensorMap& tmap, const float* x, float* dst, int64_t B, int in, int out, int dp1,
+              const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s) {
+    using L = DcSmem<BN>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(dcoeff_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                 L::TOTAL));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    const unsigned grid = (unsigned)((int64_t)p.i_tiles * p.n_tiles * p.splits);
+    dcoeff_tc_kernel<BN><<<grid, DC_THREADS, L::TOTAL, s>>>(tmap, x, dst, B, in, out, dp1, p.TI, p.i_tiles,
+                                                           p.n_tiles, p.rows_per_split, split_stride, add, status);
+    return check_cuda(cudaGetLastError());
+}
+
+}  // namespace
+
+// shapes the tensor-core kernel handles: dY rows must be TMA-addressable (16-byte pitch) and a
+// lane must hold its (input, chunk) pairs in registers (TI*8 <= 32*DC_MAX_ROUNDS)
+bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    const int dp1 = (int)deg + 1;
+    int TI = 128 / dp1;
+    if (TI > in) TI = (int)in;
+    return B > 0 && (out % 4) == 0 && dp1 <= 128 && TI * 8 <= 32 * DC_MAX_ROUNDS;
+}
+
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    const DcTcPlan p = dc_tc_plan(B, in, out, deg);
+    return p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
+}
+
+int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s) {
+    const DcTcPlan p = dc_tc_plan(B, in, out, deg);
+    const int dp1 = (int)deg + 1;
+    const int64_t n = in * out * dp1;
+    const bool direct = p.splits == 1;
+    if (!direct && (ws == nullptr || ws_bytes < (int64_t)p.splits * n * 4)) return CHEBYKAN_EWORKSPACE;
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return CHEBYKAN_ECUDA;
+    CUtensorMap tmap;
+    const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
+    const cuuint64_t strides[1] = {(cuuint64_t)(out * 4)};
+    const cuuint32_t box[2] = {32, (cuuint32_t)DC_KB};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(dy), dims, strides, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    float* dst = direct ? dc : reinterpret_cast<float*>(ws);
+    const int add = direct && accumulate;
+    int rc;
+    if (p.bn == 64) rc = launch_dc<64>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else if (p.bn == 128) rc = launch_dc<128>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else rc = launch_dc<256>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    if (rc) return rc;
+    if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
+    return rc;
+}
+
+}  // namespace chebykan

@@ -186,6 +186,13 @@ dcoeff_reduce_kernel(const float* __restrict__ ws, float* __restrict__ dc, int64
     }
 }
 
+int launch_dcoeff_reduce(const float* ws, float* dc, int64_t n, int splits, int accumulate, cudaStream_t s) {
+    int64_t blocks = ceil_div(n, 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    dcoeff_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(ws, dc, n, splits, accumulate);
+    return check_cuda(cudaGetLastError());
+}
+
 struct DcoeffPlan { int TI, i_tiles, n_tiles, g_n, splits; int64_t rows_per_split; };
 
 static DcoeffPlan dcoeff_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
@@ -206,7 +213,9 @@ static DcoeffPlan dcoeff_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     return p;
 }
 
-int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int /*mode*/) {
+int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (mode != CHEBYKAN_MODE_FP32 && dcoeff_tc_supported(B, in, out, deg))
+        return dcoeff_tc_workspace_bytes(B, in, out, deg);
     const DcoeffPlan p = dcoeff_plan(B, in, out, deg);
     return p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
 }
@@ -230,13 +239,7 @@ int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int
                                                   p.i_tiles, p.n_tiles, p.rows_per_split, n, add);
     int rc = check_cuda(cudaGetLastError());
     if (rc) return rc;
-    if (!direct) {
-        int64_t blocks = ceil_div(n, 256);
-        if (blocks > 148 * 8) blocks = 148 * 8;
-        dcoeff_reduce_kernel<<<(unsigned)blocks, 256, 0, s>>>(reinterpret_cast<const float*>(ws), dc, n,
-                                                             p.splits, accumulate);
-        rc = check_cuda(cudaGetLastError());
-    }
+    if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
     return rc;
 }
 

@@ -85,6 +85,11 @@ int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, 
 int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
                        int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
                        cudaStream_t s);
+int launch_dcoeff_reduce(const float* ws, float* dc, int64_t n, int splits, int accumulate, cudaStream_t s);
+bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg);
+int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s);
 int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
                    int64_t in, int64_t out, int64_t deg, cudaStream_t s);
 int launch_sgd(float* p, const float* g, int64_t n, float lr, float gs, cudaStream_t s);

@@ -126,3 +126,50 @@ def test_full_size_properties(mode):
     assert o.rel_l2(y0[::997].cpu(), expect.cpu().expand(y0[::997].shape[0], n_out)) <= TC_TOL
     torch.cuda.synchronize()
     ops.check_status()
+
+
+DC_SHAPES = [
+    # B, in, out, deg, dist
+    (8192, 64, 64, 32, "uniform3"),      # configuration 5 layer: 3 inputs per tile, BN = 64
+    (4096, 1024, 1024, 8, "normal"),     # configuration 3 shape: 14 inputs per tile, four N tiles of 256
+    (256, 784, 64, 4, "sparse"),         # configuration 2 first layer: 25 inputs per tile
+    (100, 16, 12, 3, "normal"),          # out < 32: second half of the 64-wide tile is out of bounds
+    (300, 13, 20, 8, "normal"),          # ragged inputs and rows
+    (5000, 40, 132, 5, "normal"),        # BN = 256 with a ragged N tile
+    (40000, 8, 8, 7, "normal"),          # batch split over many CTAs (workspace + reduction)
+    (1, 4, 4, 2, "normal"),              # single row
+]
+
+
+@pytest.mark.parametrize("mode", ["tf32", "bf16"])
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", DC_SHAPES)
+def test_tc_dcoeff_vs_oracle(mode, B, n_in, n_out, deg, dist):
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    dC, dCw = guarded((n_in, n_out, deg + 1))
+    ops.bwd_dcoeff(x.cuda(), dy.cuda(), n_in, n_out, deg, mode, out=dC)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dC, dCw)
+    err = o.rel_l2(dC.cpu(), dC_ref)
+    assert err <= TC_TOL, err
+    assert err > 1e-6            # tf32 operands leave a visible rounding: this is the tensor-core path
+
+
+def test_tc_dcoeff_accumulate_and_repeatable():
+    x, coeffs, dy = make_case(6000, 24, 64, 8, seed=31)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    xd, dyd = x.cuda(), dy.cuda()
+    a = ops.bwd_dcoeff(xd, dyd, 24, 64, 8, "tf32")
+    b = ops.bwd_dcoeff(xd, dyd, 24, 64, 8, "tf32")
+    assert torch.equal(a, b)
+    acc = torch.zeros_like(a)
+    ops.bwd_dcoeff(xd, dyd, 24, 64, 8, "tf32", out=acc, accumulate=True)
+    ops.bwd_dcoeff(xd, dyd, 24, 64, 8, "tf32", out=acc, accumulate=True)
+    assert o.rel_l2(acc.cpu(), 2 * dC_ref) <= TC_TOL
+    # a shape the tensor-core kernel does not take (out % 4 != 0) falls back to the fp32 kernel
+    x, coeffs, dy = make_case(500, 10, 7, 4, seed=32)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    got = ops.bwd_dcoeff(x.cuda(), dy.cuda(), 10, 7, 4, "tf32")
+    assert o.rel_l2(got.cpu(), dC_ref) <= 1e-5
+    ops.check_status()
