@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 1
+#define CHEBYKAN_ABI_VERSION 2
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -88,6 +88,8 @@ int chebykan_fwd(const float* x, const void* packed, float* y,
  * Replaces the dW half of autograd's BmmBackward plus the permute back to
  * [in,out,deg+1] (backward of kan/basis/chebyshev.py:101,119-145).
  * accumulate != 0 adds into dcoeffs, otherwise dcoeffs is overwritten.
+ * TF32 and BF16 modes both contract in tcgen05 kind::tf32 (bf16 operands would
+ * miss the 2e-3 budget for this product); FP32 mode uses the FFMA pipe.
  */
 int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs,
                         void* workspace, int64_t workspace_bytes,
@@ -126,10 +128,13 @@ int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float* dcoeffs,
  * Cos/Mul/Acos/Clamp/Tanh backward chain (backward of
  * kan/basis/chebyshev.py:78,136-145).  Where tanh saturates to exactly +-1
  * the reference produces NaN (0 * inf); this library returns 0 there.
- * Reads the coefficients in their own [in][out][deg+1] layout.
+ * Reads the coefficients in their own [in][out][deg+1] layout.  The tensor-core
+ * modes repack them into `workspace` on every call
+ * (chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DX, ...) bytes; 0 in FP32 mode).
  */
 int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs,
-                    float* dx, int64_t B, int64_t in, int64_t out, int64_t deg,
+                    float* dx, void* workspace, int64_t workspace_bytes,
+                    int64_t B, int64_t in, int64_t out, int64_t deg,
                     int mode, int32_t* status, void* stream);
 
 /*

@@ -31,8 +31,8 @@ SIGNATURES = {
                                     c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "chebykan_bwd_dcoeff_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,
                                            c_int, c_void_p]),
-    "chebykan_bwd_dx": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                c_int64, c_int, c_void_p, c_void_p]),
+    "chebykan_bwd_dx": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "chebykan_sgd_step": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_void_p]),
     "chebykan_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                                    c_float, c_float, c_int64, c_float, c_void_p]),
@@ -58,7 +58,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 1:
+    if lib.chebykan_abi_version() != 2:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -77,7 +77,8 @@ int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int
     switch (op) {
         case CHEBYKAN_OP_FWD: return 0;
         case CHEBYKAN_OP_BWD_DCOEFF: return B == 0 ? 0 : dcoeff_workspace_bytes(B, in, out, deg, mode);
-        case CHEBYKAN_OP_BWD_DX: return 0;
+        case CHEBYKAN_OP_BWD_DX:
+            return (mode != CHEBYKAN_MODE_FP32 && dx_tc_supported(B, in, out, deg)) ? dx_tc_workspace_bytes(in, out, deg) : 0;
         default: return CHEBYKAN_EINVAL;
     }
 }
@@ -122,15 +123,22 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* w
                               accumulate, s);
 }
 
-int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
-                    int64_t in, int64_t out, int64_t deg, int mode, int32_t* /*status*/,
-                    void* stream) {
+int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float* dx, void* workspace,
+                    int64_t workspace_bytes, int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
+                    int32_t* status, void* stream) {
     if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !coeffs) return CHEBYKAN_EINVAL;
     if (B == 0) return CHEBYKAN_OK;
     if (!x || !dy || !dx) return CHEBYKAN_EINVAL;
-    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(coeffs)) return CHEBYKAN_EALIGN;
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(coeffs) || !aligned16(workspace))
+        return CHEBYKAN_EALIGN;
     int rc = check_device();
     if (rc) return rc;
+    // tf32 and bf16 modes: tcgen05 kind::tf32 with the coefficients repacked into the workspace
+    if (mode != CHEBYKAN_MODE_FP32 && dx_tc_supported(B, in, out, deg)) {
+        if (!status) return CHEBYKAN_EINVAL;
+        return launch_dx_tc(x, dy, coeffs, dx, workspace, workspace_bytes, B, in, out, deg, status,
+                            (cudaStream_t)stream);
+    }
     return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream);
 }
 

@@ -1,0 +1,283 @@
+// Tensor-core input gradient for sm_100a (tcgen05 kind::tf32):
+//   dx[b,i] = (1 - t^2) * sum_d d U_{d-1}(t) * G[b,(i,d)],   G = dY * Wd^T,   t = tanh x[b,i]
+// i.e. the dPhi half of autograd's BmmBackward followed by the Cos/Mul/Acos/Clamp/Tanh
+// backward chain of reference kan/basis/chebyshev.py:78,136-145, in one kernel: G lives only
+// in TMEM and is folded with the derivative recurrence (T_d' = d U_{d-1}) by the epilogue.
+//
+//   A (dY):  K-major tile [128 rows][32 outputs] fp32 read as tf32, TMA, 128B swizzle.
+//   B (Wd):  packed coefficients Wd[(i,d)][out_pad] (slot = i*(deg+1)+d, outputs contiguous,
+//            rounded to tf32), K-major tile [256 slots][32 outputs], TMA, 128B swizzle.
+//   D (G):   128 x 256 fp32 in TMEM, two buffers: the epilogue of one tile overlaps the
+//            MMAs of the next.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
+//   warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two warps per TMEM lane quarter, each
+//   taking half of the tile's inputs; a thread owns one batch row).
+// Every mbarrier wait is bounded, as in the forward kernel.
+#include "tc_common.cuh"
+
+namespace chebykan {
+
+namespace {
+using namespace tc;
+
+constexpr int DX_TMA_WARP = 0;
+constexpr int DX_MMA_WARP = 1;
+constexpr int DX_EPI_WARP0 = 2;
+constexpr int DX_EPI_WARPS = 8;
+constexpr int DX_THREADS = (2 + DX_EPI_WARPS) * 32;
+constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;
+constexpr int DX_A_STAGE = DX_BM * 128;
+constexpr int DX_B_STAGE = DX_BN * 128;
+constexpr int DX_STAGE = DX_A_STAGE + DX_B_STAGE;
+constexpr int DX_NS = 4;
+constexpr int DX_BAR_OFFSET = DX_NS * DX_STAGE;
+constexpr int DX_NUM_BARS = 2 * DX_NS + 5;     // full, empty, acc_full[2], acc_empty[2], drain
+constexpr int DX_SMEM = DX_BAR_OFFSET + DX_NUM_BARS * 8 + 16 + 1024;
+
+enum { XST_TMA = 21, XST_MMA_FULL = 22, XST_MMA_ACC = 23, XST_EPILOGUE = 24 };
+
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
+}
+
+// Wd[(i,d)][out_pad] <- tf32(C[i][o][d]); columns o >= out are zero
+__global__ void __launch_bounds__(256)
+pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad) {
+    const int64_t total = (int64_t)in * dp1 * out_pad;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int o = (int)(e % out_pad);
+        const int64_t slot = e / out_pad;
+        const int64_t i = slot / dp1;
+        const int d = (int)(slot % dp1);
+        float v = 0.f;
+        if (o < out) v = c[(i * out + o) * dp1 + d];
+        uint32_t r;
+        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+        wd[e] = r;
+    }
+}
+
+__global__ void __launch_bounds__(DX_THREADS, 1)
+dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
+             const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
+             int i_tiles, int64_t num_tiles, int32_t* status) {
+    constexpr int NS = DX_NS;
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(DX_BN >> 3) << 17) |
+                               ((uint32_t)(DX_BM >> 4) << 24);
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+    const uint32_t bars = smem_base + DX_BAR_OFFSET;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NS + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NS + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * NS + 4);
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DX_BAR_OFFSET + DX_NUM_BARS * 8);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DX_BAR_OFFSET + DX_NUM_BARS * 8 + 4);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nkb = (out + DX_KB - 1) / DX_KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), DX_EPI_WARPS); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == DX_MMA_WARP) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == DX_TMA_WARP) {
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                const int m0 = (int)((tile / i_tiles) * DX_BM);
+                const int slot0 = (int)(tile % i_tiles) * TI * dp1;
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, XST_TMA)) { alive = false; break; }
+                    mbar_arrive_expect_tx(full_bar(s), DX_STAGE);
+                    const uint32_t st = smem_base + s * DX_STAGE;
+                    tma_load_2d(st, &tmap_dy, kb * DX_KB, m0, full_bar(s));
+                    tma_load_2d(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0, full_bar(s));
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+            }
+            if (!alive) {
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000ull) { }
+            }
+        }
+    } else if (warp == DX_MMA_WARP) {
+        if (lane == 0) {
+            int s = 0; uint32_t ph = 0;
+            int acc = 0; uint32_t acc_ph = 0;
+            bool alive = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+                if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, XST_MMA_ACC)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * DX_BN);
+                for (int kb = 0; kb < nkb; ++kb) {
+                    if (!mbar_wait(full_bar(s), ph, abort_flag, status, XST_MMA_FULL)) { alive = false; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * DX_STAGE;
+                    const uint64_t a_desc = make_smem_desc(a_addr);
+                    const uint64_t b_desc = make_smem_desc(a_addr + DX_A_STAGE);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        umma<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                 (uint32_t)((kb | k) != 0));
+                    umma_commit(empty_bar(s));
+                    if (++s == NS) { s = 0; ph ^= 1u; }
+                }
+                if (alive) umma_commit(acc_full_bar(acc));
+                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+            }
+            if (!alive) {
+                umma_commit(drain_bar);
+                const uint64_t t0 = globaltimer_ns();
+                while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
+            }
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;                          // TMEM lane quarter
+        const int half = (warp - DX_EPI_WARP0) >> 2;     // which half of the tile's inputs
+        int acc = 0; uint32_t acc_ph = 0;
+        bool alive = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            const int64_t row = (tile / i_tiles) * DX_BM + q * 32 + lane;
+            const int i0 = (int)(tile % i_tiles) * TI;
+            const int ti = min(TI, in - i0);
+            const int per = (ti + 1) >> 1;
+            const int ii_begin = half * per, ii_end = min(ti, ii_begin + per);
+            const bool row_ok = row < B;
+            const float* xrow = x + (row_ok ? row : 0) * in + i0;
+            float* dxrow = dx + (row_ok ? row : 0) * in + i0;
+            // first x value in flight before the accumulator is awaited
+            float xnext = (row_ok && ii_begin < ii_end) ? __ldg(xrow + ii_begin) : 0.f;
+            const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, XST_EPILOGUE);
+            if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * DX_BN);
+            for (int ii = ii_begin; ii < ii_end; ++ii) {
+                const float t = tanh_fast(xnext);
+                if (row_ok && ii + 1 < ii_end) xnext = __ldg(xrow + ii + 1);
+                const float t2 = 2.f * t;
+                float um1 = 1.f, um2 = 0.f, sum = 0.f, fd = 0.f;    // U_0 = 1, U_{-1} = 0
+                const uint32_t col0 = taddr + (uint32_t)(ii * dp1);
+                for (int c = 0; c < dp1; c += 8) {
+                    // 8 columns per TMEM read; the last read of the tile is shifted left so that it
+                    // never reaches past the 256 columns of this accumulator buffer
+                    const int over = ii * dp1 + c + 8 - DX_BN;
+                    const int shift = over > 0 ? over : 0;
+                    uint32_t r[8];
+                    tmem_ld8(col0 + c - shift, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        const int d = c - shift + e;
+                        if (d >= c && d >= 1 && d < dp1) {
+                            fd += 1.f;
+                            sum = fmaf(fd * um1, __uint_as_float(r[e]), sum);    // T_d' = d U_{d-1}
+                            const float u = fmaf(t2, um1, -um2);
+                            um2 = um1; um1 = u;
+                        }
+                    }
+                }
+                if (row_ok) dxrow[ii] = fmaf(-t, t, 1.f) * sum;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == DX_MMA_WARP) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+}  // namespace
+
+// dY and Wd rows must be TMA-addressable (16-byte pitch) and one input's degrees must fit a tile
+bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    return B > 0 && (out % 4) == 0 && deg + 1 <= DX_BN && in * (deg + 1) < ((int64_t)1 << 31);
+}
+
+int64_t dx_tc_workspace_bytes(int64_t in, int64_t out, int64_t deg) {
+    return in * (deg + 1) * round_up(out, 32) * 4;
+}
+
+int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s) {
+    const int dp1 = (int)deg + 1;
+    const int64_t out_pad = round_up(out, 32);
+    const int64_t slots = in * dp1;
+    if (ws == nullptr || ws_bytes < slots * out_pad * 4) return CHEBYKAN_EWORKSPACE;
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return CHEBYKAN_ECUDA;
+    {
+        int64_t blocks = ceil_div(slots * out_pad, 256);
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        pack_dx_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, reinterpret_cast<uint32_t*>(ws), (int)in, (int)out,
+                                                        dp1, (int)out_pad);
+        int rc = check_cuda(cudaGetLastError());
+        if (rc) return rc;
+    }
+    CUtensorMap tmap_dy, tmap_w;
+    const cuuint32_t estr[2] = {1, 1};
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
+        const cuuint64_t strides[1] = {(cuuint64_t)(out * 4)};
+        const cuuint32_t box[2] = {DX_KB, DX_BM};
+        const CUresult r = encode(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(dy), dims, strides,
+                                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)out_pad, (cuuint64_t)slots};
+        const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 4)};
+        const cuuint32_t box[2] = {DX_KB, DX_BN};
+        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ws, dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    }
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(dx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DX_SMEM));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int TI = DX_BN / dp1;
+    if (TI > in) TI = (int)in;
+    const int i_tiles = (int)ceil_div(in, TI);
+    const int64_t num_tiles = ceil_div(B, DX_BM) * i_tiles;
+    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
+    dx_tc_kernel<<<grid, DX_THREADS, DX_SMEM, s>>>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, TI, i_tiles,
+                                                   num_tiles, status);
+    return check_cuda(cudaGetLastError());
+}
+
+}  // namespace chebykan

@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib
-from ._lib import MODES, OP_BWD_DCOEFF
+from ._lib import MODES, OP_BWD_DCOEFF, OP_BWD_DX
 
 _status = {}  # device index -> int32[1] tensor the tensor-core kernels report into
 
@@ -141,10 +141,15 @@ def bwd_dx(x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor, mode,
         out = torch.empty_like(x)
     else:
         _require(out, "out")
+    lib = _lib.load()
+    m = _mode(mode)
+    ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DX, B, n_in, n_out, dp1 - 1, m)
+    _lib.check(ws_bytes, "chebykan_workspace_bytes")
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     with torch.cuda.device(x.device):
-        rc = _lib.load().chebykan_bwd_dx(x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(), out.data_ptr(), B,
-                                         n_in, n_out, dp1 - 1, _mode(mode),
-                                         status_tensor(x.device).data_ptr(), _stream(x))
+        rc = lib.chebykan_bwd_dx(x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(), out.data_ptr(), ws.data_ptr(),
+                                 ws_bytes, B, n_in, n_out, dp1 - 1, m,
+                                 status_tensor(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "chebykan_bwd_dx")
     return out
 

@@ -154,6 +154,7 @@ def test_c_abi_rejects_bad_arguments():
     assert lib.chebykan_fwd(None, p, p, 4, 4, 4, 2, 0, st.data_ptr(), None) == -1      # null x
     assert lib.chebykan_bwd_dcoeff(p, p, p, None, 0, 1 << 20, 8, 8, 4, 0, 0, None, None) == -6  # no workspace
     assert lib.chebykan_adam_step(p, p, p, p, 16, 0.1, 0.9, 0.999, 1e-8, 0, 1.0, None) == -1   # step < 1
+    assert lib.chebykan_bwd_dx(p, p, p, p, None, 0, 64, 8, 8, 3, 1, st.data_ptr(), None) == -6   # tf32 dx: no workspace
     torch.cuda.synchronize()
 
 

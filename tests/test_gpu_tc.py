@@ -173,3 +173,46 @@ def test_tc_dcoeff_accumulate_and_repeatable():
     got = ops.bwd_dcoeff(x.cuda(), dy.cuda(), 10, 7, 4, "tf32")
     assert o.rel_l2(got.cpu(), dC_ref) <= 1e-5
     ops.check_status()
+
+
+DX_SHAPES = [
+    # B, in, out, deg, dist
+    (8192, 64, 64, 32, "uniform3"),      # configuration 5 layer: 7 inputs per 256-slot tile
+    (4096, 1024, 1024, 8, "normal"),     # configuration 3 shape: 28 inputs per tile, 32 K blocks
+    (256, 64, 12, 4, "normal"),          # configuration 2 second-layer-like, out < 32
+    (300, 13, 20, 8, "normal"),          # ragged rows and inputs
+    (1000, 51, 40, 4, "normal"),         # 51 inputs x 5 degrees = 255 slots: last TMEM read is shifted
+    (129, 5, 36, 63, "normal"),          # degree 63: 4 inputs per tile
+    (20000, 8, 8, 7, "normal"),          # more tiles than SMs, both accumulator buffers
+    (1, 4, 4, 0, "normal"),              # degree 0: dx is identically zero
+]
+
+
+@pytest.mark.parametrize("mode", ["tf32", "bf16"])
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", DX_SHAPES)
+def test_tc_dx_vs_oracle(mode, B, n_in, n_out, deg, dist):
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    _, _, dx_ref = o.forward_backward(x, coeffs, dy)
+    dx, dxw = guarded((B, n_in))
+    ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), mode, out=dx)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dx, dxw)
+    err = o.rel_l2(dx.cpu(), dx_ref)
+    assert err <= TC_TOL, err
+    if deg > 0:
+        assert err > 1e-6            # tf32 operands leave a visible rounding: this is the tensor-core path
+    else:
+        assert float(dx.abs().max()) == 0.0
+
+
+def test_tc_dx_repeatable_and_fallback():
+    x, coeffs, dy = make_case(3000, 24, 64, 8, seed=41)
+    xd, dyd, cd = x.cuda(), dy.cuda(), coeffs.cuda()
+    assert torch.equal(ops.bwd_dx(xd, dyd, cd, "tf32"), ops.bwd_dx(xd, dyd, cd, "tf32"))
+    # out % 4 != 0 is not TMA-addressable: the fp32 kernel takes over
+    x, coeffs, dy = make_case(500, 10, 7, 4, seed=42)
+    _, _, dx_ref = o.forward_backward(x, coeffs, dy)
+    got = ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "tf32")
+    assert o.rel_l2(got.cpu(), dx_ref) <= 1e-5
+    ops.check_status()
