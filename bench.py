@@ -265,6 +265,107 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_model_config(args):
+    """Other configurations (not the headline): one step = one forward pass (cfg4) or one
+    forward + backward + optimizer step (cfg1, cfg2, cfg5) of the configuration's model."""
+    import torch.distributed as dist
+    import kan_b200
+    from kan_b200 import dp, ops, workloads
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    cfg = workloads.CONFIGS[args.config]
+    B = args.batch or cfg.batch
+    mode = args.mode
+    train = cfg.task == "train"
+    model = workloads.build_model(cfg, kan_b200.ChebyKANLayer, math_mode=mode).to(dev)
+    x, tgt = workloads.make_inputs(cfg, batch=B, seed=cfg.seed + rank)
+    x = x.to(dev)
+    tgt = tgt.to(dev) if tgt is not None else None
+    n_cheby = len(cfg.layers)
+    if train:
+        loss_fn = workloads.loss_fn(cfg)
+        buf = dp.FlatGradBuffer(model.parameters())
+        Opt = kan_b200.optim.Adam if cfg.optimizer == "adam" else kan_b200.optim.SGD
+        opt = Opt(list(model.parameters()), lr=cfg.lr)
+        opt.grad_scale = 1.0 / world
+        last_loss = [None]
+
+        def step():
+            buf.zero()
+            loss = loss_fn(model(x), tgt)
+            loss.backward()
+            buf.all_reduce()
+            opt.step()
+            last_loss[0] = loss
+    else:
+        for p in model.parameters():
+            p.requires_grad_(False)
+
+        def step():
+            with torch.no_grad():
+                model(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        step()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ops.check_status()
+    t = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = float(t.item()) / args.steps
+    value = world * B / (ms_step * 1e-3)
+    if rank == 0:
+        peaks = measured_peaks()
+        fwd_flops = workloads.flops_per_sample(cfg) * B
+        # training: forward + dC for every layer + dx for every layer but the first
+        later = sum(2 * i * (d + 1) * o for i, o, d in cfg.layers[1:]) * B
+        flops = (2 * fwd_flops + later) if train else fwd_flops
+        achieved = flops / (ms_step * 1e-3) / 1e12
+        peak = peaks["bf16_tflops"] if (mode == "bf16" and not train) else (
+            peaks["bf16_tflops"] / 2 if mode != "fp32" else 148 * 128 * 2 * 1.965e9 / 1e12)
+        launches = n_cheby * (1 if not train else 6) + (len(list(model.parameters())) if train else 0)
+        line = {
+            "metric": "chebykan_%s_samples_per_s" % ("train_step" if train else "stack_fwd"), "value": value,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode], "data": "synthetic",
+            "config": {"workload": f"{cfg.name}: layers {list(cfg.layers)}, batch {B} per GPU, "
+                                   f"{'fwd+bwd+' + cfg.optimizer if train else 'forward'}",
+                       "global_batch": world * B, "math_mode": mode,
+                       "parallelism": f"dp{world}" + (" (flat-buffer all-reduce of the gradients)" if train and world > 1 else "")},
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None, "flops_per_step": flops},
+            "gpu_launches": args.steps * launches, "clocks": clocks,
+        }
+        if train:
+            line["final_loss"] = float(last_loss[0].detach())
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 # DRAM bytes (read + write) of one forward launch taken from an ncu capture; None until one exists.
 # bf16/tf32/fp32: captured at 32768 rows (profiles/), x and y traffic doubled for the full 65536-row launch.
 TRAFFIC_BYTES = {"bf16": 583.3e6, "tf32": 759.7e6, "fp32": 592.4e6}
@@ -279,10 +380,14 @@ def main():
     ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32", "fp32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
-    ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's 65536)")
+    ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's batch)")
+    ap.add_argument("--config", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
+                    help="cfg3 (default) is the headline forward; the others time the configuration's model step")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.config != "cfg3":
+        run_model_config(args)
     else:
         run_ours(args)
 
