@@ -151,6 +151,15 @@ int chebykan_adam_step(float* param, const float* grad, float* exp_avg,
                        void* stream);
 
 /*
+ * Self-test of the bounded device-side wait the tensor-core kernels use: one
+ * CTA waits (at most limit_ns, <= 1 s) on an mbarrier nothing arrives on,
+ * gives up, and writes `code` to the device word *status.  The context stays
+ * usable.  No counterpart in the reference (it has no device code).
+ */
+int chebykan_selftest_bounded_wait(int32_t* status, int64_t limit_ns, int code,
+                                   void* stream);
+
+/*
  * Forward with HOST buffers: copies x and the coefficients to the device,
  * packs, runs chebykan_fwd and copies y back; synchronous.  The caller lends
  * device scratch of at least chebykan_fwd_host_scratch_bytes(...) bytes.

@@ -38,13 +38,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Bounded wait.  Returns false when another role already aborted or when this
 // wait itself ran out of time (it then raises the abort flag and records `code`).
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                            int32_t* status, int code) {
+                                                   int32_t* status, int code,
+                                                   uint64_t limit_ns = WAIT_LIMIT_NS) {
     const uint64_t t0 = globaltimer_ns();
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+            if (globaltimer_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
                 return false;

@@ -216,3 +216,28 @@ def test_tc_dx_repeatable_and_fallback():
     got = ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "tf32")
     assert o.rel_l2(got.cpu(), dx_ref) <= 1e-5
     ops.check_status()
+
+
+def test_bounded_wait_gives_up_and_reports():
+    """A wait nothing will ever satisfy runs out after its limit, reports through the status word
+    and leaves the GPU context usable (the mechanism that keeps a broken pipeline from hanging)."""
+    from kan_b200 import _lib
+    lib = _lib.load()
+    st = torch.zeros(1, dtype=torch.int32, device="cuda")
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    rc = lib.chebykan_selftest_bounded_wait(st.data_ptr(), 20_000_000, 77, torch.cuda.current_stream().cuda_stream)
+    t1.record()
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert int(st.item()) == 77
+    assert 15.0 <= t0.elapsed_time(t1) <= 500.0          # about the 20 ms limit, far from the 4 s of the second warp
+    # the context still works, and the Python layer turns a non-zero status into an exception
+    ops.status_tensor("cuda").fill_(3)
+    with pytest.raises(RuntimeError, match="bounded wait"):
+        ops.check_status()
+    ops.check_status()
+    assert lib.chebykan_selftest_bounded_wait(st.data_ptr(), 0, 1, None) == -1
+    x, coeffs, _ = make_case(256, 64, 128, 4, seed=1)
+    assert o.rel_l2(run_fwd(x, coeffs, "bf16"), oracle_y(x, coeffs, "bf16")) <= TC_TOL
