@@ -265,6 +265,50 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def cpu_model_baseline(cfg, budget_s: float = 10.0):
+    """The configuration's model built from the oracle's layer, timed on the host cores on a bounded batch."""
+    import torch.nn as nn
+    from kan_b200 import workloads
+    from oracle import chebykan_oracle as o
+
+    class OracleLayer(nn.Module):
+        def __init__(self, input_dim, output_dim, degree):
+            super().__init__()
+            self.input_dim = input_dim
+            self.cheby_coeffs = nn.Parameter(o.init_coeffs(input_dim, output_dim, degree))
+
+        def forward(self, x):
+            return o.forward(x.view(-1, self.input_dim), self.cheby_coeffs)
+
+    torch.set_num_threads(os.cpu_count() or 1)
+    rows = {"cfg1": 100, "cfg2": 256, "cfg4": 2048, "cfg5": 32768}[cfg.name]
+    model = workloads.build_model(cfg, OracleLayer)
+    x, tgt = workloads.make_inputs(cfg, batch=rows)
+    train = cfg.task == "train"
+    if train:
+        loss_fn = workloads.loss_fn(cfg)
+        opt = (torch.optim.Adam if cfg.optimizer == "adam" else torch.optim.SGD)(model.parameters(), lr=cfg.lr)
+
+        def step():
+            opt.zero_grad()
+            loss_fn(model(x), tgt).backward()
+            opt.step()
+    else:
+        def step():
+            with torch.no_grad():
+                model(x)
+    step()
+    times = []
+    while sum(times) < budget_s and len(times) < 2000:
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    best = min(times)
+    return {"value": rows / best, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "ms_per_step": best * 1e3,
+            "sample": f"{rows} of {cfg.batch} rows per step, best of {len(times)} steps ({sum(times):.1f} s of CPU work)"}
+
+
 def run_model_config(args):
     """Other configurations (not the headline): one step = one forward pass (cfg4) or one
     forward + backward + optimizer step (cfg1, cfg2, cfg5) of the configuration's model."""
@@ -361,6 +405,8 @@ def run_model_config(args):
         }
         if train:
             line["final_loss"] = float(last_loss[0].detach())
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_model_baseline(cfg)
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
