@@ -101,11 +101,21 @@ class _PackedCache:
         self._entries.clear()
 
 
+def _aligned(t: torch.Tensor) -> torch.Tensor:
+    """Contiguous and 16-byte aligned (a view into the middle of a buffer may be neither): the kernels use
+    vector and TMA accesses.  Fresh torch allocations are always aligned, so a copy fixes both."""
+    t = t.contiguous()
+    if t.numel() and t.data_ptr() % 16:
+        t = t.clone()
+    return t
+
+
 class _ChebyKANFunction(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, coeffs, mode, cache):
         n_in, n_out, dp1 = coeffs.shape
         packed = cache.get(coeffs, mode) if cache is not None else ops.pack_coeffs(coeffs.detach(), mode)
+        x = _aligned(x)
         y = ops.forward(x, packed, n_in, n_out, dp1 - 1, mode)
         ctx.save_for_backward(x, coeffs)
         ctx.mode = mode
@@ -115,7 +125,7 @@ class _ChebyKANFunction(torch.autograd.Function):
     def backward(ctx, dy):
         x, coeffs = ctx.saved_tensors
         n_in, n_out, dp1 = coeffs.shape
-        dy = dy.contiguous()
+        dy = _aligned(dy)
         dx = dc = None
         if ctx.needs_input_grad[1]:
             dc = ops.bwd_dcoeff(x, dy, n_in, n_out, dp1 - 1, ctx.mode)
@@ -129,6 +139,8 @@ def chebykan_apply(x: torch.Tensor, coeffs: torch.Tensor, mode: str = "fp32", ca
     if not x.is_cuda or not coeffs.is_cuda:
         raise RuntimeError("kan_b200.ChebyKANLayer runs on CUDA (sm_100a) only: move the layer and its "
                            "input to the GPU; there is no CPU path")
+    if x.device != coeffs.device:
+        raise RuntimeError(f"input is on {x.device} but the layer's coefficients are on {coeffs.device}")
     if x.dtype != torch.float32:
         # the reference's einsum raises the same way on a dtype mismatch
         raise RuntimeError(f"expected scalar type Float but found {str(x.dtype).replace('torch.', '').capitalize()}")

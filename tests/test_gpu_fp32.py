@@ -142,6 +142,21 @@ def test_empty_batch_and_flatten_rule():
         layer(torch.randn(6, 4, device="cuda", dtype=torch.float64))
 
 
+def test_unaligned_view_input_is_accepted():
+    """A contiguous view that starts in the middle of a buffer (not 16-byte aligned) works like in the reference."""
+    torch.manual_seed(8)
+    layer = kan_b200.ChebyKANLayer(5, 6, 3).cuda()
+    base = torch.randn(1 + 40 * 5, device="cuda")
+    x = base[1:].view(40, 5).requires_grad_(True)          # data_ptr is 4 bytes past an aligned address
+    assert x.data_ptr() % 16 != 0
+    y = layer(x)
+    y.sum().backward()
+    y_ref, dC_ref, dx_ref = o.forward_backward(x.detach().cpu(), layer.cheby_coeffs.detach().cpu(), torch.ones(40, 6))
+    assert o.rel_l2(y.detach().cpu(), y_ref) <= FP32_TOL
+    assert o.rel_l2(x.grad.cpu(), dx_ref) <= FP32_TOL
+    assert o.rel_l2(layer.cheby_coeffs.grad.cpu(), dC_ref) <= FP32_TOL
+
+
 def test_c_abi_rejects_bad_arguments():
     from kan_b200 import _lib
     lib = _lib.load()
