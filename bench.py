@@ -160,6 +160,8 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=dev)
 
     B, n_in, n_out, deg = CFG["batch_per_gpu"], CFG["input_dim"], CFG["output_dim"], CFG["degree"]
+    if args.shape:
+        B, n_in, n_out, deg = [int(v) for v in args.shape.split(",")]
     if args.batch:
         B = args.batch
     mode = args.mode
@@ -174,8 +176,22 @@ def run_ours(args):
     packed = ops.pack_coeffs(layer.cheby_coeffs.detach(), mode)
     y = torch.empty(B, n_out, dtype=torch.float32, device=dev)
 
-    def step():
-        ops.forward(x, packed, n_in, n_out, deg, mode, out=y)
+    if args.op == "fwd":
+        def step():
+            ops.forward(x, packed, n_in, n_out, deg, mode, out=y)
+    else:
+        # single backward kernels on the same shape (not the headline metric): dY ~ N(0,1)
+        dy = torch.randn(B, n_out, device=dev)
+        dc = torch.empty(n_in, n_out, deg + 1, device=dev)
+        dx = torch.empty(B, n_in, device=dev)
+        cdev = layer.cheby_coeffs.detach()
+        if args.op == "dcoeff":
+            def step():
+                ops.bwd_dcoeff(x, dy, n_in, n_out, deg, mode, out=dc)
+        else:
+            def step():
+                ops.bwd_dx(x, dy, cdev, mode, out=dx)
+        args.no_e2e = True
 
     def barrier():
         if world > 1:
@@ -240,15 +256,20 @@ def run_ours(args):
         else:
             peak, peak_note = peaks["bf16_tflops"], f"{peaks['source']} cuBLAS bf16 burst peak"
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "metric": METRIC if args.op == "fwd" else f"chebykan_layer_{args.op}_samples_per_s", "value": value,
+            "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode],
             "data": "synthetic",
-            "config": dict(CFG, batch_per_gpu=B, global_batch=world * B, parallelism=f"dp{world} (rows sharded, no collective)",
+            "config": dict(CFG if not args.shape else {"workload": f"layer {args.op}, shape {args.shape}"},
+                           batch_per_gpu=B, input_dim=n_in, output_dim=n_out, degree=deg, op=args.op,
+                           global_batch=world * B, parallelism=f"dp{world} (rows sharded, no collective)",
                            l2_policy="inputs larger than L2 (x 268 MB + y 268 MB per step vs 126 MB L2)",
                            math_mode=mode),
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": TRAFFIC_BYTES.get(mode), "peak_note": peak_note,
+                         "frac": achieved / peak,
+                         "traffic": TRAFFIC_BYTES.get(mode) if (args.op == "fwd" and not args.shape and not args.batch) else None,
+                         "peak_note": peak_note,
                          "flops_per_launch": flops},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * 4,
                     "d2h_bytes_per_step": y_host.numel() * 4, "steps": e2e_steps},
@@ -427,6 +448,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's batch)")
+    ap.add_argument("--op", default="fwd", choices=["fwd", "dcoeff", "dx"],
+                    help="cfg3 path only: time the forward (headline) or one backward kernel on the same shape")
+    ap.add_argument("--shape", default="", help="cfg3 path only: B,in,out,deg override (profiling other layer shapes)")
     ap.add_argument("--config", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg3 (default) is the headline forward; the others time the configuration's model step")
     args = ap.parse_args()
