@@ -353,7 +353,21 @@ def run_model_config(args):
     x = x.to(dev)
     tgt = tgt.to(dev) if tgt is not None else None
     n_cheby = len(cfg.layers)
-    if train:
+    if train and args.graph:
+        # the whole step (forward, loss, backward, optimizer) replayed as one CUDA graph
+        if world > 1:
+            raise SystemExit("--graph is a single-GPU mode")
+        loss_fn = workloads.loss_fn(cfg)
+        if cfg.optimizer == "adam":
+            opt = kan_b200.optim.Adam(list(model.parameters()), lr=cfg.lr, capturable=True)
+        else:
+            opt = kan_b200.optim.SGD(list(model.parameters()), lr=cfg.lr)
+        graphed = kan_b200.graph.GraphedTrainStep(model, loss_fn, opt, x, tgt)
+        last_loss = [None]
+
+        def step():
+            last_loss[0] = graphed()
+    elif train:
         loss_fn = workloads.loss_fn(cfg)
         buf = dp.FlatGradBuffer(model.parameters())
         Opt = kan_b200.optim.Adam if cfg.optimizer == "adam" else kan_b200.optim.SGD
@@ -418,7 +432,7 @@ def run_model_config(args):
             "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode], "data": "synthetic",
             "config": {"workload": f"{cfg.name}: layers {list(cfg.layers)}, batch {B} per GPU, "
                                    f"{'fwd+bwd+' + cfg.optimizer if train else 'forward'}",
-                       "global_batch": world * B, "math_mode": mode,
+                       "global_batch": world * B, "math_mode": mode, "cuda_graph": bool(args.graph and train),
                        "parallelism": f"dp{world}" + (" (flat-buffer all-reduce of the gradients)" if train and world > 1 else "")},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": None, "flops_per_step": flops},
@@ -448,6 +462,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's batch)")
+    ap.add_argument("--graph", action="store_true",
+                    help="training configurations: replay the whole step as one CUDA graph (single GPU)")
     ap.add_argument("--op", default="fwd", choices=["fwd", "dcoeff", "dx"],
                     help="cfg3 path only: time the forward (headline) or one backward kernel on the same shape")
     ap.add_argument("--shape", default="", help="cfg3 path only: B,in,out,deg override (profiling other layer shapes)")

@@ -151,6 +151,18 @@ int chebykan_adam_step(float* param, const float* grad, float* exp_avg,
                        void* stream);
 
 /*
+ * Adam update whose step count lives in device memory (*step_dev = number of
+ * updates already applied; the call uses step_dev + 1 and then increments it),
+ * so that a training step captured in a CUDA graph can be replayed.  Same
+ * replaced reference line as chebykan_adam_step (torch.optim.Adam.step,
+ * README.md:59-66).
+ */
+int chebykan_adam_step_graph(float* param, const float* grad, float* exp_avg,
+                             float* exp_avg_sq, int64_t n, float lr, float beta1,
+                             float beta2, float eps, int64_t* step_dev,
+                             float grad_scale, void* stream);
+
+/*
  * Self-test of the bounded device-side wait the tensor-core kernels use: one
  * CTA waits (at most limit_ns, <= 1 s) on an mbarrier nothing arrives on,
  * gives up, and writes `code` to the device word *status.  The context stays

@@ -36,6 +36,8 @@ SIGNATURES = {
     "chebykan_sgd_step": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_void_p]),
     "chebykan_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                                    c_float, c_float, c_int64, c_float, c_void_p]),
+    "chebykan_adam_step_graph": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
+                                         c_float, c_float, c_void_p, c_float, c_void_p]),
     "chebykan_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_int, c_void_p]),
     "chebykan_fwd_host_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "chebykan_fwd_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -165,6 +165,19 @@ int chebykan_adam_step(float* param, const float* grad, float* exp_avg, float* e
                        grad_scale, (cudaStream_t)stream);
 }
 
+int chebykan_adam_step_graph(float* param, const float* grad, float* exp_avg, float* exp_avg_sq,
+                             int64_t n, float lr, float beta1, float beta2, float eps,
+                             int64_t* step_dev, float grad_scale, void* stream) {
+    if (n < 0 || !param || !grad || !exp_avg || !exp_avg_sq || !step_dev) return CHEBYKAN_EINVAL;
+    if (!aligned16(param) || !aligned16(grad) || !aligned16(exp_avg) || !aligned16(exp_avg_sq))
+        return CHEBYKAN_EALIGN;
+    if (n == 0) return CHEBYKAN_OK;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_adam_dev(param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, step_dev,
+                           grad_scale, (cudaStream_t)stream);
+}
+
 // ---- host-buffer forward ------------------------------------------------------------
 static int64_t a256(int64_t v) { return round_up(v, 256); }
 

@@ -166,18 +166,27 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
                         const float t = tanh_fast(xc[r][e]);
                         t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
                     }
-                    int row = ii * dp1;
-                    for (int d = 0; d < dp1; ++d, ++row) {
+                    // one 16-byte chunk (4 batch rows) per degree; ta / tb alternate as the newest value
+                    auto store4 = [&](int row, const float (&v)[4]) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            float v = ta[e];
-                            if (d > 0) { v = fmaf(t2[e], ta[e], -tb[e]); tb[e] = ta[e]; ta[e] = v; }
-                            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[e]) : "f"(v));
-                        }
+                        for (int e = 0; e < 4; ++e) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[e]) : "f"(v[e]));
                         const uint32_t dsta = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                      ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                    };
+                    int row = ii * dp1;
+                    store4(row, ta);                                   // degree 0
+                    ++row;
+                    for (int d = 1; d < dp1; d += 2, row += 2) {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
+                        store4(row, tb);
+                        if (d + 1 < dp1) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
+                            store4(row + 1, ta);
+                        }
                     }
                 }
             }

@@ -1,5 +1,6 @@
 // Tensor-core input gradient for sm_100a (tcgen05 kind::tf32):
-//   dx[b,i] = (1 - t^2) * sum_d d U_{d-1}(t) * G[b,(i,d)],   G = dY * Wd^T,   t = tanh x[b,i]
+//   dx[b,i] = (1 - t^2) * sum_d U_{d-1}(t) * G[b,(i,d)],   G = dY * Wd^T,  Wd[(i,d)][o] = d C[i,o,d],
+//   t = tanh x[b,i]   (T_d' = d U_{d-1}; the factor d rides in the packed coefficients)
 // i.e. the dPhi half of autograd's BmmBackward followed by the Cos/Mul/Acos/Clamp/Tanh
 // backward chain of reference kan/basis/chebyshev.py:78,136-145, in one kernel: G lives only
 // in TMEM and is folded with the derivative recurrence (T_d' = d U_{d-1}) by the epilogue.
@@ -41,7 +42,8 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr) : "memory");
 }
 
-// Wd[(i,d)][out_pad] <- tf32(C[i][o][d]); columns o >= out are zero
+// Wd[(i,d)][out_pad] <- tf32(d * C[i][o][d]); columns o >= out are zero.  The degree factor of
+// T_d' = d U_{d-1} is folded in here so that the epilogue only needs U_{d-1} * G per value.
 __global__ void __launch_bounds__(256)
 pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad) {
     const int64_t total = (int64_t)in * dp1 * out_pad;
@@ -52,7 +54,7 @@ pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, i
         const int64_t i = slot / dp1;
         const int d = (int)(slot % dp1);
         float v = 0.f;
-        if (o < out) v = c[(i * out + o) * dp1 + d];
+        if (o < out) v = (float)d * c[(i * out + o) * dp1 + d];
         uint32_t r;
         asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
         wd[e] = r;
@@ -175,11 +177,26 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 const float t = tanh_fast(xnext);
                 if (row_ok && ii + 1 < ii_end) xnext = __ldg(xrow + ii + 1);
                 const float t2 = 2.f * t;
-                float um1 = 1.f, um2 = 0.f, sum = 0.f, fd = 0.f;    // U_0 = 1, U_{-1} = 0
+                // ua / ub alternate as (U_{d-1}, U_{d-2}); U_{-1} = 0, U_{-2} = -1 make U_0 = 1 and
+                // give the d = 0 column (whose coefficients are 0 * C) weight zero without a branch
+                float ua = 0.f, ub = -1.f, sum = 0.f;
                 const uint32_t col0 = taddr + (uint32_t)(ii * dp1);
-                for (int c = 0; c < dp1; c += 8) {
-                    // 8 columns per TMEM read; the last read of the tile is shifted left so that it
-                    // never reaches past the 256 columns of this accumulator buffer
+                int c = 0;
+                for (; c + 8 <= dp1; c += 8) {
+                    uint32_t r[8];
+                    tmem_ld8(col0 + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int e = 0; e < 8; e += 2) {
+                        sum = fmaf(ua, __uint_as_float(r[e]), sum);
+                        ub = fmaf(t2, ua, -ub);
+                        sum = fmaf(ub, __uint_as_float(r[e + 1]), sum);
+                        ua = fmaf(t2, ub, -ua);
+                    }
+                }
+                if (c < dp1) {
+                    // last, partial group of 8 columns; the read is shifted left where it would reach
+                    // past the 256 columns of this accumulator buffer
                     const int over = ii * dp1 + c + 8 - DX_BN;
                     const int shift = over > 0 ? over : 0;
                     uint32_t r[8];
@@ -188,11 +205,10 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const int d = c - shift + e;
-                        if (d >= c && d >= 1 && d < dp1) {
-                            fd += 1.f;
-                            sum = fmaf(fd * um1, __uint_as_float(r[e]), sum);    // T_d' = d U_{d-1}
-                            const float u = fmaf(t2, um1, -um2);
-                            um2 = um1; um1 = u;
+                        if (d >= c && d < dp1) {
+                            sum = fmaf(ua, __uint_as_float(r[e]), sum);
+                            const float u = fmaf(t2, ua, -ub);
+                            ub = ua; ua = u;
                         }
                     }
                 }

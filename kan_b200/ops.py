@@ -179,6 +179,23 @@ def adam_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, ex
     _lib.check(rc, "chebykan_adam_step")
 
 
+def adam_step_graph(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, exp_avg_sq: torch.Tensor,
+                    step_dev: torch.Tensor, lr: float, beta1: float = 0.9, beta2: float = 0.999, eps: float = 1e-8,
+                    grad_scale: float = 1.0) -> None:
+    """Adam update with the step counter in device memory (int64[1]); safe to capture in a CUDA graph."""
+    for t, n in ((param, "param"), (grad, "grad"), (exp_avg, "exp_avg"), (exp_avg_sq, "exp_avg_sq")):
+        _require(t, n)
+        if t.numel() != param.numel():
+            raise RuntimeError(f"{n} and param sizes differ")
+    if step_dev.dtype != torch.int64 or not step_dev.is_cuda or step_dev.numel() != 1:
+        raise RuntimeError("step_dev must be a CUDA int64 tensor with one element")
+    with torch.cuda.device(param.device):
+        rc = _lib.load().chebykan_adam_step_graph(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(),
+                                                  exp_avg_sq.data_ptr(), param.numel(), lr, beta1, beta2, eps,
+                                                  step_dev.data_ptr(), grad_scale, _stream(param))
+    _lib.check(rc, "chebykan_adam_step_graph")
+
+
 def forward_host(x_host: torch.Tensor, coeffs_host: torch.Tensor, mode, scratch: torch.Tensor | None = None,
                  out: torch.Tensor | None = None):
     """Forward with HOST tensors through chebykan_fwd_host; returns (y_host, scratch).

@@ -53,22 +53,40 @@ class SGD(_Base):
 
 
 class Adam(_Base):
-    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8):
+    """``capturable=True`` keeps the step counters in device memory so that ``step()`` can be
+    captured in a CUDA graph and replayed (the host-side counter of the default mode would be
+    frozen into the graph)."""
+
+    def __init__(self, params, lr: float = 1e-3, betas=(0.9, 0.999), eps: float = 1e-8, capturable: bool = False):
         super().__init__(params, lr)
         self.betas = (float(betas[0]), float(betas[1]))
         self.eps = float(eps)
+        self.capturable = bool(capturable)
         self.state = {}
+        if self.capturable:
+            for p in self.params:     # allocate before any capture
+                self._state(p)
+
+    def _state(self, p):
+        st = self.state.get(p)
+        if st is None:
+            st = {"step": 0, "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
+            if self.capturable:
+                st["step_dev"] = torch.zeros(1, dtype=torch.int64, device=p.device)
+            self.state[p] = st
+        return st
 
     @torch.no_grad()
     def step(self) -> None:
         for p in self.params:
             if p.grad is None:
                 continue
-            st = self.state.get(p)
-            if st is None:
-                st = {"step": 0, "exp_avg": torch.zeros_like(p), "exp_avg_sq": torch.zeros_like(p)}
-                self.state[p] = st
-            st["step"] += 1
-            ops.adam_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], st["step"], self.lr,
-                          self.betas[0], self.betas[1], self.eps, self.grad_scale)
+            st = self._state(p)
+            if self.capturable:
+                ops.adam_step_graph(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], st["step_dev"],
+                                    self.lr, self.betas[0], self.betas[1], self.eps, self.grad_scale)
+            else:
+                st["step"] += 1
+                ops.adam_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], st["step"], self.lr,
+                              self.betas[0], self.betas[1], self.eps, self.grad_scale)
             _bump(p)

@@ -137,7 +137,10 @@ def test_empty_batch_and_flatten_rule():
     y = layer(torch.randn(2, 5, 4, device="cuda"))
     assert y.shape == (10, 3)                     # leading dimensions are flattened, not restored
     with pytest.raises(RuntimeError):
-        layer(torch.randn(4, 6, device="cuda").t())          # non-contiguous: view fails
+        layer(torch.randn(2, 4, 5, device="cuda").transpose(1, 2))   # leading dims cannot be merged: view fails
+    # a non-contiguous input whose view succeeds is accepted, as in the reference
+    xt = torch.randn(4, 6, device="cuda").t()
+    assert o.rel_l2(layer(xt).detach().cpu(), o.forward(xt.cpu().contiguous(), layer.cheby_coeffs.detach().cpu())) <= FP32_TOL
     with pytest.raises(RuntimeError, match="Float"):
         layer(torch.randn(6, 4, device="cuda", dtype=torch.float64))
 
@@ -186,7 +189,7 @@ def test_layer_autograd_two_layer_model():
     loss_ref.backward()
     loss = torch.nn.functional.cross_entropy(ours(x.cuda()), labels.cuda())
     loss.backward()
-    assert abs(float(loss) - float(loss_ref)) <= 1e-5 * abs(float(loss_ref))
+    assert abs(float(loss.detach()) - float(loss_ref.detach())) <= 1e-5 * abs(float(loss_ref.detach()))
     for (n, a), (_, b) in zip(ref.named_parameters(), ours.named_parameters()):
         assert o.rel_l2(b.grad.cpu(), a.grad) <= 2e-5, n
 
@@ -237,3 +240,52 @@ def test_forward_through_host_buffers():
     y_ref = o.forward(x, coeffs)
     y, _ = ops.forward_host(x.pin_memory(), coeffs, "fp32")
     assert o.rel_l2(y, y_ref) <= FP32_TOL
+
+
+def test_graphed_training_step_config1(golden):
+    """The README loop replayed as one CUDA graph per step (capturable Adam): same loss curve and final coefficients."""
+    layer = kan_b200.ChebyKANLayer(1, 1, 8)
+    with torch.no_grad():
+        layer.cheby_coeffs.copy_(torch.from_numpy(golden["cfg1_train"]["init_coeffs"]))
+    layer = layer.cuda()
+    x, tgt = workloads.make_inputs(workloads.CONFIGS["cfg1"])
+    x, tgt = x.cuda(), tgt.cuda()
+    opt = kan_b200.optim.Adam(layer.parameters(), lr=0.01, capturable=True)
+    # the constructor runs 3 eager warm-up steps and 1 capture step: restore the start state afterwards
+    step = kan_b200.graph.GraphedTrainStep(layer, torch.nn.functional.mse_loss, opt, x, tgt)
+    with torch.no_grad():
+        layer.cheby_coeffs.copy_(torch.from_numpy(golden["cfg1_train"]["init_coeffs"]).cuda())
+    for st in opt.state.values():
+        st["exp_avg"].zero_(); st["exp_avg_sq"].zero_(); st["step_dev"].zero_()
+    got = []
+    for i in range(1000):
+        loss = step()
+        if i in (0, 99, 499, 999):
+            got.append(float(loss.detach()))
+    assert np.allclose(got, golden["cfg1_train"]["losses"], rtol=2e-3)
+    assert o.rel_l2(layer.cheby_coeffs.detach().cpu(), golden["cfg1_train"]["final_coeffs"]) <= 2e-3
+    assert int(next(iter(opt.state.values()))["step_dev"].item()) == 1000
+    with pytest.raises(ValueError):
+        kan_b200.graph.GraphedTrainStep(layer, torch.nn.functional.mse_loss,
+                                        kan_b200.optim.Adam(layer.parameters(), lr=0.01), x, tgt)
+
+
+def test_graphed_step_equals_eager_config2():
+    cfg = workloads.CONFIGS["cfg2"]
+    x, labels = workloads.make_inputs(cfg)
+    x, labels = x.cuda(), labels.cuda()
+    eager = workloads.build_model(cfg, kan_b200.ChebyKANLayer).cuda()
+    graphed_model = workloads.build_model(cfg, kan_b200.ChebyKANLayer).cuda()
+    opt_e = kan_b200.optim.Adam(eager.parameters(), lr=1e-3)
+    opt_g = kan_b200.optim.Adam(graphed_model.parameters(), lr=1e-3, capturable=True)
+    step = kan_b200.graph.GraphedTrainStep(graphed_model, torch.nn.functional.cross_entropy, opt_g, x, labels)
+    n_done = 3                                           # 3 eager warm-up steps; capturing records, it does not run
+    for _ in range(6):
+        step()
+        n_done += 1
+    for _ in range(n_done):
+        opt_e.zero_grad()
+        torch.nn.functional.cross_entropy(eager(x), labels).backward()
+        opt_e.step()
+    for a, b in zip(eager.parameters(), graphed_model.parameters()):
+        assert o.rel_l2(b.detach().cpu(), a.detach().cpu()) <= 1e-5
