@@ -241,3 +241,22 @@ def test_bounded_wait_gives_up_and_reports():
     assert lib.chebykan_selftest_bounded_wait(st.data_ptr(), 0, 1, None) == -1
     x, coeffs, _ = make_case(256, 64, 128, 4, seed=1)
     assert o.rel_l2(run_fwd(x, coeffs, "bf16"), oracle_y(x, coeffs, "bf16")) <= TC_TOL
+
+
+@pytest.mark.parametrize("mode,tol", [("fp32", 1e-5), ("bf16", TC_TOL)])
+def test_forward_host_pipelined(mode, tol):
+    """Host tensors in and out through the layer's pipelined call: same result as the device call."""
+    torch.manual_seed(12)
+    layer = kan_b200.ChebyKANLayer(96, 72, 5, math_mode=mode).cuda()
+    x = torch.randn(5000, 96).pin_memory()
+    y = layer.forward_host(x, chunk_rows=1024)              # 5 blocks, the last one ragged
+    assert y.shape == (5000, 72) and not y.is_cuda
+    y_dev = layer(x.cuda()).detach().cpu()
+    assert torch.equal(y, y_dev)
+    c = layer.cheby_coeffs.detach().cpu()
+    assert o.rel_l2(y, o.forward(x, c.bfloat16().float() if mode == "bf16" else c)) <= tol
+    out = torch.empty(5000, 72).pin_memory()
+    assert layer.forward_host(x, out=out, chunk_rows=100000) is out and torch.equal(out, y)
+    with pytest.raises(RuntimeError):
+        layer.forward_host(x.cuda())
+    ops.check_status()
