@@ -11,8 +11,9 @@
 
 namespace chebykan {
 
+// two CTAs per SM (<= 128 registers): the second CTA covers the first one's FFMA and LDS latency
 template <int G_M, int G_N>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 2)
 fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float* __restrict__ y,
                 int64_t B, int in, int out, int dp1, int n_pad, int n_tiles) {
     constexpr int BM = 64 * G_M, BN = 64 * G_N;
