@@ -384,10 +384,11 @@ def run_model_config(args):
     else:
         for p in model.parameters():
             p.requires_grad_(False)
+        runner = kan_b200.fuse_layernorm(model) if (args.fuse_ln and mode != "fp32") else model
 
         def step():
             with torch.no_grad():
-                model(x)
+                runner(x)
 
     def barrier():
         if world > 1:
@@ -432,6 +433,7 @@ def run_model_config(args):
             "config": {"workload": f"{cfg.name}: layers {list(cfg.layers)}, batch {B} per GPU, "
                                    f"{'fwd+bwd+' + cfg.optimizer if train else 'forward'}",
                        "global_batch": world * B, "math_mode": mode, "cuda_graph": bool(args.graph and train),
+                       "layernorm_fused": bool(args.fuse_ln and not train and mode != "fp32"),
                        "parallelism": f"dp{world}" + (" (flat-buffer all-reduce of the gradients)" if train and world > 1 else "")},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": None, "flops_per_step": flops},
@@ -461,6 +463,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's batch)")
+    ap.add_argument("--fuse-ln", action="store_true",
+                    help="forward stacks: fold the LayerNorms between layers into the ChebyKAN kernels")
     ap.add_argument("--graph", action="store_true",
                     help="training configurations: replay the whole step as one CUDA graph (single GPU)")
     ap.add_argument("--op", default="fwd", choices=["fwd", "dcoeff", "dx"],

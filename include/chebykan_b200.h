@@ -84,6 +84,26 @@ int chebykan_fwd(const float* x, const void* packed, float* y,
                  int32_t* status, void* stream);
 
 /*
+ * Forward with the LayerNorm that sits between two ChebyKAN layers of a stack
+ * fused in (tensor-core modes only; FP32 mode returns CHEBYKAN_EUNSUPPORTED).
+ * The reference chains layers through torch.nn.LayerNorm modules in a
+ * Sequential (kan/layers/base.py:144-153); each LayerNorm costs a read and a
+ * write of the whole activation.  Here
+ *   - ln_stats_out (nullable, float[B][2], zeroed by the caller): the kernel adds
+ *     each produced row's sum and sum of squares of y;
+ *   - ln_stats_in / ln_gamma / ln_beta / ln_eps (stats nullable): the kernel
+ *     normalises its input rows, x' = (x - mean) * rstd * gamma + beta with
+ *     mean and rstd from the previous layer's sums over `in` features, before tanh.
+ * So y of layer k is written once, un-normalised, and layer k+1 applies the
+ * LayerNorm while it loads it.
+ */
+int chebykan_fwd_ln(const float* x, const void* packed, float* y,
+                    int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
+                    const float* ln_stats_in, const float* ln_gamma,
+                    const float* ln_beta, float ln_eps, float* ln_stats_out,
+                    int32_t* status, void* stream);
+
+/*
  * Coefficient gradient dC[i,o,d] = sum_b T_d(tanh x[b,i]) * dY[b,o].
  * Replaces the dW half of autograd's BmmBackward plus the permute back to
  * [in,out,deg+1] (backward of kan/basis/chebyshev.py:101,119-145).

@@ -7,8 +7,9 @@ data-parallel helpers in ``dp``.  Everything computes in hand-written CUDA
 behind the C ABI of ``include/chebykan_b200.h``; there is no CPU fallback.
 """
 from .layer import ChebyKANLayer, ChebyshevBasis, KANLayer, chebykan_apply, install_into_reference
+from .stack import FusedChebyKANStack, fuse_layernorm
 from . import ops, optim, dp, workloads, graph
 
-__all__ = ["ChebyKANLayer", "ChebyshevBasis", "KANLayer", "chebykan_apply", "install_into_reference",
+__all__ = ["FusedChebyKANStack", "fuse_layernorm", "ChebyKANLayer", "ChebyshevBasis", "KANLayer", "chebykan_apply", "install_into_reference",
            "ops", "optim", "dp", "workloads", "graph"]
 __version__ = "0.1.0"

@@ -27,6 +27,8 @@ SIGNATURES = {
     "chebykan_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int64, c_int]),
     "chebykan_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
                              c_void_p, c_void_p]),
+    "chebykan_fwd_ln": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
+                                c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p]),
     "chebykan_bwd_dcoeff": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                     c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "chebykan_bwd_dcoeff_static": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64,

@@ -13,6 +13,16 @@ static int check_device() {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) { set_last_cuda_error((int)e); return CHEBYKAN_ECUDA; }
+    // Tensor maps are encoded through the driver API, which needs the device's primary context
+    // bound to the CALLING thread.  A thread that has only ever selected a device (autograd's
+    // backward threads, for instance) has none until its first runtime call that touches the
+    // device: cudaFree(0) is that call.  Once per thread and device.
+    static thread_local int bound_dev = -1;
+    if (bound_dev != dev) {
+        e = cudaFree(nullptr);
+        if (e != cudaSuccess) { set_last_cuda_error((int)e); return CHEBYKAN_ECUDA; }
+        bound_dev = dev;
+    }
     if (dev < 0 || dev >= 64) return CHEBYKAN_EDEVICE;
     if (g_cc_ok[dev] == 0) {
         int major = 0;
@@ -96,6 +106,22 @@ int chebykan_fwd(const float* x, const void* packed, float* y, int64_t B, int64_
                                (cudaStream_t)stream);
     if (!status) return CHEBYKAN_EINVAL;
     return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream);
+}
+
+int chebykan_fwd_ln(const float* x, const void* packed, float* y, int64_t B, int64_t in, int64_t out,
+                    int64_t deg, int mode, const float* ln_stats_in, const float* ln_gamma,
+                    const float* ln_beta, float ln_eps, float* ln_stats_out, int32_t* status, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !packed || !status) return CHEBYKAN_EINVAL;
+    if (mode == CHEBYKAN_MODE_FP32) return CHEBYKAN_EUNSUPPORTED;   // fusion lives in the tensor-core kernel
+    if (ln_stats_in && (!ln_gamma || !ln_beta)) return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x || !y) return CHEBYKAN_EINVAL;
+    if (!aligned16(x) || !aligned16(y) || !aligned16(packed)) return CHEBYKAN_EALIGN;
+    int rc = check_device();
+    if (rc) return rc;
+    LnFusion ln;
+    ln.stats_in = ln_stats_in; ln.gamma = ln_gamma; ln.beta = ln_beta; ln.eps = ln_eps; ln.stats_out = ln_stats_out;
+    return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream, ln);
 }
 
 int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* workspace,

@@ -74,13 +74,25 @@ inline int check_cuda(cudaError_t e) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Optional LayerNorm fusion of the tensor-core forward.  stats_* hold two floats per row (sum and
+// sum of squares over the row's features).  With stats_in the kernel normalises its input rows,
+// x' = (x - mean) * rstd * gamma + beta, before tanh; with stats_out it adds the sums of the rows
+// of y it produces (the caller zeroes the buffer), which the next layer consumes as its stats_in.
+struct LnFusion {
+    const float* stats_in = nullptr;
+    const float* gamma = nullptr;
+    const float* beta = nullptr;
+    float eps = 1e-5f;
+    float* stats_out = nullptr;
+};
+
 // ---- launchers implemented in the .cu files ------------------------------------
 int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, int mode,
                 cudaStream_t s);
 int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
                     int64_t deg, cudaStream_t s);
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
-                  int64_t deg, int mode, int32_t* status, cudaStream_t s);
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion());
 int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
 int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
                        int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,

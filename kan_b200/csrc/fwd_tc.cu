@@ -44,7 +44,11 @@ constexpr int NUM_PRODUCER_WARPS = 8;
 constexpr int TMA_WARP = 8;
 constexpr int MMA_WARP = 9;
 constexpr int X_WARP = 14;
-constexpr int NUM_THREADS = 15 * 32;
+// 16 warps = four warpgroups (warp 15 idles): the two producer warpgroups take registers from the
+// other two with setmaxnreg, 8*32*168 + 8*32*88 = 65536
+constexpr int NUM_THREADS = 16 * 32;
+constexpr int PRODUCER_REGS = 168;
+constexpr int OTHER_REGS = 88;
 constexpr int A_STAGE_BYTES = BM * 128;
 
 // status codes recorded by a wait that gave up
@@ -61,19 +65,21 @@ struct Smem {
     static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
     static constexpr int X_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;   // x tile: 128 rows x 128 bytes... x 2
     static constexpr int X_BYTES = BM * 256;                          // up to 64 fp32 inputs per row
-    static constexpr int BAR_OFFSET = X_OFFSET + X_BYTES;
+    static constexpr int GB_OFFSET = X_OFFSET + X_BYTES;               // LayerNorm gamma | beta of the input block
+    static constexpr int GB_BYTES = 512;                              // 2 x 64 fp32
+    static constexpr int BAR_OFFSET = GB_OFFSET + GB_BYTES;
     // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain x_full x_empty
     static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 7;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024 alignment slack
     static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
-template <int MODE, int BN, int NSUB>
+template <int MODE, int BN, int NSUB, bool LN>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
-              int64_t num_tiles, int32_t* status) {
+              int64_t num_tiles, int32_t* status, LnFusion ln) {
     using L = Smem<BN, NSUB>;
     constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC;
     constexpr int BNT = BN * NSUB;                              // outputs per CTA tile
@@ -124,6 +130,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
+    if (warp < NUM_PRODUCER_WARPS) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(PRODUCER_REGS));
+    else                           asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(OTHER_REGS));
+
     if (warp < NUM_PRODUCER_WARPS) {
         // ------------------------------ producers ------------------------------
         // thread -> 16-byte chunk c of rows r0, r0+32, r0+64, r0+96: 8 lanes cover one
@@ -171,11 +180,51 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const int64_t m0 = (tile / n_tiles) * BM;
+            // fused LayerNorm of the input rows: per-row mean and 1/std from the previous layer's sums
+            float ln_mean[4], ln_rstd[4];
+            if (LN && ln.stats_in != nullptr) {
+                const float inv_n = 1.f / (float)in;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int64_t row = m0 + r0 + 32 * j;
+                    float s1 = 0.f, s2 = 0.f;
+                    if (row < B) { s1 = __ldg(ln.stats_in + 2 * row); s2 = __ldg(ln.stats_in + 2 * row + 1); }
+                    const float mean = s1 * inv_n;
+                    const float var = fmaxf(fmaf(-mean, mean, s2 * inv_n), 0.f);
+                    ln_rstd[j] = rsqrtf(var + ln.eps);
+                    ln_mean[j] = -mean * ln_rstd[j];       // (x - mean) * rstd as one fma
+                }
+            }
             for (int ib = 0; ib < n_iblk && alive; ++ib) {
                 const int i_base = ib * IB + c * CH;
+                float ln_g[CH], ln_b[CH];
+                if (LN && ln.stats_in != nullptr && !use_x_tma) {
+#pragma unroll
+                    for (int e = 0; e < CH; ++e) {
+                        const bool ok = i_base + e < in;       // padded inputs stay exactly 0
+                        ln_g[e] = ok ? __ldg(ln.gamma + i_base + e) : 0.f;
+                        ln_b[e] = ok ? __ldg(ln.beta + i_base + e) : 0.f;
+                    }
+                }
                 if (use_x_tma) {
                     if (!mbar_wait(x_full_bar, xph, abort_flag, status, ST_X_WAIT)) { alive = false; break; }
                     xph ^= 1u;
+                    if (LN && ln.stats_in != nullptr) {
+                        // gamma and beta of this input block arrived next to the x tile
+                        const uint32_t gsrc = smem_base + L::GB_OFFSET + (uint32_t)(c * (CH * 4));
+#pragma unroll
+                        for (int q = 0; q < CH / 4; ++q) {
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(ln_g[4 * q]), "=f"(ln_g[4 * q + 1]), "=f"(ln_g[4 * q + 2]), "=f"(ln_g[4 * q + 3])
+                                         : "r"(gsrc + 16 * q));
+                            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                         : "=f"(ln_b[4 * q]), "=f"(ln_b[4 * q + 1]), "=f"(ln_b[4 * q + 2]), "=f"(ln_b[4 * q + 3])
+                                         : "r"(gsrc + 256 + 16 * q));
+                        }
+#pragma unroll
+                        for (int e = 0; e < CH; ++e)
+                            if (i_base + e >= in) { ln_g[e] = 0.f; ln_b[e] = 0.f; }   // padded inputs stay exactly 0
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
@@ -205,6 +254,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                             for (int e = 0; e < CH; ++e)
                                 if (i_base + e < in) v[e] = __ldg(src + e);
                         }
+                    }
+                    if (LN && ln.stats_in != nullptr) {
+#pragma unroll
+                        for (int e = 0; e < CH; ++e)
+                            v[e] = fmaf(fmaf(v[e], ln_rstd[j], ln_mean[j]), ln_g[e], ln_b[e]);
                     }
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
@@ -268,7 +322,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 const int m0 = (int)((tile / n_tiles) * BM);
                 for (int ib = 0; ib < n_iblk; ++ib) {
                     if (!mbar_wait(x_empty_bar, xph ^ 1u, abort_flag, status, ST_X_LOAD)) { alive = false; break; }
-                    mbar_arrive_expect_tx(x_full_bar, X_TILE_BYTES);
+                    if (LN && ln.stats_in != nullptr) {
+                        // gamma | beta of this block of inputs ride on the same barrier (plain bulk copies)
+                        const int i0 = ib * IB;
+                        const uint32_t gb_bytes = (uint32_t)(min(IB, in - i0) * 4);     // in % 4 == 0 here
+                        mbar_arrive_expect_tx(x_full_bar, X_TILE_BYTES + 2 * gb_bytes);
+                        bulk_load_1d(smem_base + L::GB_OFFSET, ln.gamma + i0, gb_bytes, x_full_bar);
+                        bulk_load_1d(smem_base + L::GB_OFFSET + 256, ln.beta + i0, gb_bytes, x_full_bar);
+                    } else {
+                        mbar_arrive_expect_tx(x_full_bar, X_TILE_BYTES);
+                    }
                     tma_load_2d(smem_base + L::X_OFFSET, &tmap_x, ib * IB, m0, x_full_bar);
                     xph ^= 1u;
                 }
@@ -317,7 +380,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
         }
-    } else {
+    } else if (warp < X_WARP) {
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3;  // TMEM lane quarter this warp may read
         int acc = 0; uint32_t acc_ph = 0;
@@ -325,8 +388,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         const bool vec4 = (out & 3) == 0;
         const bool vec8 = (out & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
         // one row's 32 consecutive outputs from registers to y
+        float ln_s1 = 0.f, ln_s2 = 0.f;    // this row's sum and sum of squares over the tile (fused LayerNorm)
         auto store32 = [&](const uint32_t (&r)[32], int64_t row, int col0) {
             if (row >= B) return;
+            if (LN && ln.stats_out != nullptr) {
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    if (col0 + e < out) {
+                        const float v = __uint_as_float(r[e]);
+                        ln_s1 += v; ln_s2 = fmaf(v, v, ln_s2);
+                    }
+            }
             float* dst = y + row * out + col0;
             if (vec8 && col0 + 32 <= out) {
 #pragma unroll
@@ -379,6 +451,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     store32(rb, row, n0 + (ch + 1) * 32);
                 }
             }
+            if (LN && ln.stats_out != nullptr) {
+                if (row < B) {
+                    atomicAdd(ln.stats_out + 2 * row, ln_s1);
+                    atomicAdd(ln.stats_out + 2 * row + 1, ln_s2);
+                }
+                ln_s1 = 0.f; ln_s2 = 0.f;
+            }
             if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
         }
     }
@@ -391,15 +470,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
 }
 
-template <int MODE, int BN, int NSUB>
-int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
-               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s) {
+template <int MODE, int BN, int NSUB, bool LN>
+int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
+               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
     using L = Smem<BN, NSUB>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN, NSUB>,
+        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN, NSUB, LN>,
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
         attr_set[dev] = true;
@@ -409,23 +488,32 @@ int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma
     const int n_tiles = (int)ceil_div(n_pad, BN * NSUB);
     const int64_t num_tiles = ceil_div(B, BM) * n_tiles;
     const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    fwd_tc_kernel<MODE, BN, NSUB><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x, y, B, in, out,
-                                                                      dp1, n_tiles, num_tiles, status);
+    fwd_tc_kernel<MODE, BN, NSUB, LN><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x, y, B, in, out,
+                                                                      dp1, n_tiles, num_tiles, status, ln);
     return check_cuda(cudaGetLastError());
+}
+
+// the LayerNorm-fused variant is a separate instantiation, so the plain kernel carries none of its registers
+template <int MODE, int BN, int NSUB>
+int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
+               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+    if (ln.stats_in != nullptr || ln.stats_out != nullptr)
+        return launch_one_ln<MODE, BN, NSUB, true>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    return launch_one_ln<MODE, BN, NSUB, false>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
 }
 
 template <int MODE>
 int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, const float* x, float* y,
-                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s) {
-    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
-    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
-    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s);
+                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
 }
 
 }  // namespace
 
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
-                  int64_t deg, int mode, int32_t* status, cudaStream_t s) {
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln) {
     const PackedDims p = packed_dims(in, out, deg, mode);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
@@ -460,9 +548,9 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     const int dp1 = (int)deg + 1;
     if (mode == CHEBYKAN_MODE_BF16)
         return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
-                                               (int)p.n_pad, status, s);
+                                               (int)p.n_pad, status, s, ln);
     return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
-                                           (int)p.n_pad, status, s);
+                                           (int)p.n_pad, status, s, ln);
 }
 
 }  // namespace chebykan

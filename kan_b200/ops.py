@@ -101,6 +101,41 @@ def forward(x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, de
     return out
 
 
+def forward_ln(x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, degree: int, mode,
+               ln_in=None, stats_out: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Forward with a fused LayerNorm on the input (ln_in = (stats[B,2], gamma, beta, eps)) and/or
+    row sums of y accumulated into `stats_out` ([B,2], zeroed by the caller).  Tensor-core modes only."""
+    _require(x, "x")
+    if x.dim() != 2 or x.shape[1] != in_dim:
+        raise RuntimeError(f"x must have shape [B, {in_dim}]")
+    B = x.shape[0]
+    if out is None:
+        out = torch.empty(B, out_dim, dtype=torch.float32, device=x.device)
+    else:
+        _require(out, "out")
+    st_in = g = b = 0
+    eps = 1e-5
+    if ln_in is not None:
+        stats, gamma, beta, eps = ln_in
+        for t, n in ((stats, "ln stats"), (gamma, "ln gamma"), (beta, "ln beta")):
+            _require(t, n)
+        if stats.shape != (B, 2) or gamma.numel() != in_dim or beta.numel() != in_dim:
+            raise RuntimeError("LayerNorm statistics must be [B, 2] and gamma/beta [in]")
+        st_in, g, b = stats.data_ptr(), gamma.data_ptr(), beta.data_ptr()
+    so = 0
+    if stats_out is not None:
+        _require(stats_out, "stats_out")
+        if stats_out.shape != (B, 2):
+            raise RuntimeError("stats_out must be [B, 2]")
+        so = stats_out.data_ptr()
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_fwd_ln(x.data_ptr(), packed.data_ptr(), out.data_ptr(), B, in_dim, out_dim, degree,
+                                         _mode(mode), st_in, g, b, float(eps), so,
+                                         status_tensor(x.device).data_ptr(), _stream(x))
+    _lib.check(rc, "chebykan_fwd_ln")
+    return out
+
+
 def bwd_dcoeff(x: torch.Tensor, dy: torch.Tensor, in_dim: int, out_dim: int, degree: int, mode,
                out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
     """dC[in,out,deg+1] = sum_b T_d(tanh x[b,i]) dY[b,o]."""

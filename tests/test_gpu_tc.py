@@ -260,3 +260,48 @@ def test_forward_host_pipelined(mode, tol):
     with pytest.raises(RuntimeError):
         layer.forward_host(x.cuda())
     ops.check_status()
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("widths,deg,B", [((256, 256, 256, 256), 4, 1000), ((200, 136, 72), 3, 333), ((64, 512, 64), 8, 4096)])
+def test_fused_layernorm_stack(mode, widths, deg, B):
+    """Sequential(Cheby, LN, Cheby, LN, ...) with the LayerNorms folded into the kernels: same output as the
+    unfused modules (tight), and within the tensor-core tolerance per layer of the CPU oracle model."""
+    from _util import OracleLayer
+    torch.manual_seed(widths[0] + deg)
+    mods, ref_mods = [], []
+    for k in range(len(widths) - 1):
+        if k > 0:
+            ln = torch.nn.LayerNorm(widths[k])
+            with torch.no_grad():                      # a non-trivial affine part
+                ln.weight.uniform_(0.5, 1.5)
+                ln.bias.uniform_(-0.5, 0.5)
+            mods.append(ln)
+            ref_ln = torch.nn.LayerNorm(widths[k])
+            ref_ln.load_state_dict(ln.state_dict())
+            ref_mods.append(ref_ln)
+        layer = kan_b200.ChebyKANLayer(widths[k], widths[k + 1], deg, math_mode=mode)
+        ref_layer = OracleLayer(widths[k], widths[k + 1], deg)
+        c = layer.cheby_coeffs.detach()
+        with torch.no_grad():
+            ref_layer.cheby_coeffs.copy_(c.bfloat16().float() if mode == "bf16" else c)
+        mods.append(layer)
+        ref_mods.append(ref_layer)
+    model = torch.nn.Sequential(*mods).cuda()
+    ref = torch.nn.Sequential(*ref_mods)
+    fused = kan_b200.fuse_layernorm(model)
+    x = torch.randn(B, widths[0])
+    with torch.no_grad():
+        y_plain = model(x.cuda()).cpu()
+        y_ref = ref(x)
+    y_fused = fused(x.cuda()).cpu()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert y_fused.shape == y_plain.shape
+    assert o.rel_l2(y_fused, y_plain) <= 2e-4          # LayerNorm arithmetic order only
+    # against the oracle the fused path is as good as the unfused one (rounding accumulates over layers either way)
+    err_plain, err_fused = o.rel_l2(y_plain, y_ref), o.rel_l2(y_fused, y_ref)
+    assert err_fused <= 1.1 * err_plain + 1e-4
+    assert err_fused <= 1.5 * TC_TOL * (len(widths) - 1)
+    # parameters are shared, not copied
+    assert fused.layers[0].cheby_coeffs is model[0].cheby_coeffs
