@@ -95,7 +95,7 @@ class ClockSampler:
                 "samples": len(self.samples)}
 
 
-def cpu_reference_throughput(rows: int, budget_s: float, seed: int = 1003):
+def cpu_reference_throughput(rows: int, max_seconds: float, seed: int = 1003):
     """The reference's CPU path for this layer, restated op for op (torch CPU kernels), all host threads."""
     from oracle import chebykan_oracle as o
     torch.set_num_threads(os.cpu_count() or 1)
@@ -106,7 +106,7 @@ def cpu_reference_throughput(rows: int, budget_s: float, seed: int = 1003):
     o.forward(x[:256], coeffs)  # warm the thread pool
     best = float("inf")
     times = []
-    while sum(times) < budget_s and len(times) < 50:
+    while sum(times) < max_seconds and len(times) < 50:
         t0 = time.perf_counter()
         o.forward(x, coeffs)
         dt = time.perf_counter() - t0
@@ -285,7 +285,7 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-def cpu_model_baseline(cfg, budget_s: float = 10.0):
+def cpu_model_baseline(cfg, max_seconds: float = 10.0):
     """The configuration's model built from the oracle's layer, timed on the host cores on a bounded batch."""
     import torch.nn as nn
     from kan_b200 import workloads
@@ -319,7 +319,7 @@ def cpu_model_baseline(cfg, budget_s: float = 10.0):
                 model(x)
     step()
     times = []
-    while sum(times) < budget_s and len(times) < 2000:
+    while sum(times) < max_seconds and len(times) < 2000:
         t0 = time.perf_counter()
         step()
         times.append(time.perf_counter() - t0)

@@ -109,7 +109,7 @@ int chebykan_fwd_ln(const float* x, const void* packed, float* y,
  * [in,out,deg+1] (backward of kan/basis/chebyshev.py:101,119-145).
  * accumulate != 0 adds into dcoeffs, otherwise dcoeffs is overwritten.
  * TF32 and BF16 modes both contract in tcgen05 kind::tf32 (bf16 operands would
- * miss the 2e-3 budget for this product); FP32 mode uses the FFMA pipe.
+ * miss the 2e-3 tolerance for this product); FP32 mode uses the FFMA pipe.
  */
 int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs,
                         void* workspace, int64_t workspace_bytes,

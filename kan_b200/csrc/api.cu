@@ -138,7 +138,7 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* w
     }
     if (!x || !dy) return CHEBYKAN_EINVAL;
     if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
-    // tf32 and bf16 modes: tcgen05 kind::tf32 (bf16 operands would miss the 2e-3 budget for this
+    // tf32 and bf16 modes: tcgen05 kind::tf32 (bf16 operands would miss the 2e-3 tolerance for this
     // product); shapes it does not cover, and fp32 mode, accumulate in fp32 on the FFMA pipe
     if (mode != CHEBYKAN_MODE_FP32 && dcoeff_tc_supported(B, in, out, deg)) {
         if (!status) return CHEBYKAN_EINVAL;

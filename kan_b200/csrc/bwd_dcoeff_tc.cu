@@ -19,7 +19,7 @@
 //      over CTAs and the slices' partial sums are added by dcoeff_reduce (fixed order).
 //
 // Precision: tf32 operands, fp32 accumulate (plain bf16 operands would miss the 2e-3
-// budget for this product).  Every mbarrier wait is bounded, as in the forward kernel.
+// tolerance for this product).  Every mbarrier wait is bounded, as in the forward kernel.
 #include "tc_common.cuh"
 
 namespace chebykan {

@@ -50,7 +50,7 @@ inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64
 // ---- tanh ------------------------------------------------------------------
 // FP32 mode: tanh evaluated in double and rounded once, i.e. the correctly
 // rounded fp32 value (high-degree T_d amplifies an error in t by up to d^2, so
-// a 2-ulp tanh alone would spend the whole 1e-5 budget at degree 32).
+// a 2-ulp tanh alone would spend the whole 1e-5 tolerance at degree 32).
 __device__ __forceinline__ float tanh_exact(float x) { return (float)tanh((double)x); }
 
 // Tensor-core modes: 1 - 2/(1+2^(2x log2 e)) with the approximate ex2 and rcp
