@@ -35,7 +35,7 @@ constexpr int DC_A_STAGE = 128 * 128;     // 128 slots x 32 tf32
 constexpr int DC_KB = 32;                 // batch rows per K block
 constexpr int DC_MAX_ROUNDS = 8;          // (input, 4-row chunk) pairs per lane per K block: TI*8/32
 
-enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_MMA_B = 14, DST_EPILOGUE = 15 };
+enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_EPILOGUE = 15 };
 
 template <int BN>
 struct DcSmem {
@@ -45,7 +45,7 @@ struct DcSmem {
     // warp only ever fills its own stage, so it is never more than one mbarrier phase ahead
     static constexpr int NS = (BN == 64) ? 8 : 4;
     static constexpr int BAR_OFFSET = NS * STAGE;
-    static constexpr int NUM_BARS = 3 * NS + 2;              // fullA, fullB, empty, acc_full, drain
+    static constexpr int NUM_BARS = 2 * NS + 2;              // full, empty, acc_full, drain
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
     static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 };
@@ -80,11 +80,11 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bars = smem_base + L::BAR_OFFSET;
-    auto fullA = [&](int s) { return bars + 8u * s; };
-    auto fullB = [&](int s) { return bars + 8u * (NS + s); };
-    auto empty = [&](int s) { return bars + 8u * (2 * NS + s); };
-    const uint32_t acc_full_bar = bars + 8u * (3 * NS);
-    const uint32_t drain_bar = bars + 8u * (3 * NS + 1);
+    // one "full" barrier per stage: the producer warps of the stage and the TMA's byte count
+    auto full = [&](int s) { return bars + 8u * s; };
+    auto empty = [&](int s) { return bars + 8u * (NS + s); };
+    const uint32_t acc_full_bar = bars + 8u * (2 * NS);
+    const uint32_t drain_bar = bars + 8u * (2 * NS + 1);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
@@ -101,7 +101,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(fullA(s), DC_PRODUCER_WARPS / NS); mbar_init(fullB(s), 1); mbar_init(empty(s), 1);
+            mbar_init(full(s), DC_PRODUCER_WARPS / NS + 1); mbar_init(empty(s), 1);
         }
         mbar_init(acc_full_bar, 1);
         mbar_init(drain_bar, 1);
@@ -192,7 +192,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(fullA(s));
+            if (lane == 0) mbar_arrive(full(s));
         }
     } else if (warp == DC_TMA_WARP) {
         // ------------------------------ dY loads ------------------------------
@@ -202,12 +202,12 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
                 const int s = kb % NS;
                 const uint32_t ph = (uint32_t)((kb / NS) & 1);
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
-                mbar_arrive_expect_tx(fullB(s), L::B_STAGE);
+                mbar_arrive_expect_tx(full(s), L::B_STAGE);
                 const uint32_t b_stage = smem_base + s * L::STAGE + DC_A_STAGE;
                 const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
 #pragma unroll
                 for (int m = 0; m < BN / 32; ++m)
-                    tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, fullB(s));
+                    tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, full(s));
             }
             if (!alive) {
                 const uint64_t t0 = globaltimer_ns();
@@ -221,8 +221,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % NS;
                 const uint32_t ph = (uint32_t)((kb / NS) & 1);
-                if (!mbar_wait(fullA(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
-                if (!mbar_wait(fullB(s), ph, abort_flag, status, DST_MMA_B)) { alive = false; break; }
+                if (!mbar_wait(full(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + s * L::STAGE;
                 const uint64_t a_desc = make_smem_desc(a_addr);
@@ -294,11 +293,20 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : 256);
     p.n_tiles = (int)ceil_div(out, p.bn);
     const int64_t base = (int64_t)p.i_tiles * p.n_tiles;
-    int64_t splits = ceil_div(2 * 148, base);
-    const int64_t max_splits = ceil_div(B, 1024);
-    if (splits > max_splits) splits = max_splits;
-    if (splits < 1) splits = 1;
-    p.rows_per_split = round_up(ceil_div(B, splits), DC_KB);
+    // Split the batch so that the CTAs fill whole waves of the 148 SMs: among the candidate split
+    // counts take the one with the least (waves x rows per CTA), i.e. the shortest critical path.
+    int64_t max_splits = ceil_div(B, 1024);
+    if (max_splits < 1) max_splits = 1;
+    int64_t cand_hi = ceil_div(4 * 148, base);
+    if (cand_hi > max_splits) cand_hi = max_splits;
+    int64_t best_s = 1, best_cost = -1;
+    for (int64_t sp = 1; sp <= cand_hi; ++sp) {
+        const int64_t rows = round_up(ceil_div(B, sp), DC_KB);
+        const int64_t ctas = base * ceil_div(B, rows);
+        const int64_t cost = ceil_div(ctas, 148) * (rows + 2048);   // + fixed cost of a CTA (setup, epilogue)
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = sp; }
+    }
+    p.rows_per_split = round_up(ceil_div(B, best_s), DC_KB);
     p.splits = (int)ceil_div(B, p.rows_per_split);
     if (p.splits < 1) p.splits = 1;
     return p;
