@@ -158,6 +158,17 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs,
                     int mode, int32_t* status, void* stream);
 
 /*
+ * Jacobian jac[b][o][i] = d y[b,o] / d x[b,i] (fp32).  Stands where the
+ * reference has KANLayer.jacobian / compute_derivatives
+ * (kan/layers/base.py:102-141 over kan/basis/chebyshev.py:174-267); those do
+ * not return this derivative (their coefficient rule is wrong), this entry
+ * point returns what autograd gives.  The output has B*out*in elements.
+ */
+int chebykan_jacobian(const float* x, const float* coeffs, float* jac,
+                      int64_t B, int64_t in, int64_t out, int64_t deg,
+                      void* stream);
+
+/*
  * Optimizer updates on a flat fp32 parameter of n elements.  Replace
  * torch.optim.SGD(lr) / torch.optim.Adam(lr) as called by the reference's
  * training loop (README.md:59-66).  grad_scale multiplies the gradient first

@@ -35,6 +35,7 @@ SIGNATURES = {
                                            c_int, c_void_p]),
     "chebykan_bwd_dx": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int, c_void_p, c_void_p]),
+    "chebykan_jacobian": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "chebykan_sgd_step": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_void_p]),
     "chebykan_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                                    c_float, c_float, c_int64, c_float, c_void_p]),

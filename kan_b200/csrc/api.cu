@@ -168,6 +168,16 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float*
     return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream);
 }
 
+int chebykan_jacobian(const float* x, const float* coeffs, float* jac, int64_t B, int64_t in, int64_t out,
+                      int64_t deg, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !coeffs) return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x || !jac) return CHEBYKAN_EINVAL;
+    int rc = check_device();
+    if (rc) return rc;
+    return launch_jacobian(x, coeffs, jac, B, in, out, deg, (cudaStream_t)stream);
+}
+
 int chebykan_sgd_step(float* param, const float* grad, int64_t n, float lr, float grad_scale,
                       void* stream) {
     if (n < 0 || !param || !grad) return CHEBYKAN_EINVAL;

@@ -112,6 +112,8 @@ int launch_sgd(float* p, const float* g, int64_t n, float lr, float gs, cudaStre
 int launch_adam(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1,
                 float b2, float eps, int64_t step, float gs, cudaStream_t s);
 
+int launch_jacobian(const float* x, const float* coeffs, float* jac, int64_t B, int64_t in, int64_t out,
+                    int64_t deg, cudaStream_t s);
 int launch_adam_dev(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1,
                     float b2, float eps, int64_t* step_dev, float gs, cudaStream_t s);
 

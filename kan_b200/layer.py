@@ -239,6 +239,26 @@ def make_chebykan_layer_class(base_cls, basis_cls, name: str = "ChebyKANLayer"):
             cur.synchronize()
             return out
 
+        @torch.no_grad()
+        def jacobian(self, x: torch.Tensor) -> torch.Tensor:
+            """True Jacobian d y / d x, shape (batch, output_dim, input_dim), as autograd would give it.
+
+            The reference's ``KANLayer.jacobian`` (kan/layers/base.py:116-141) has this shape but is built
+            on ``ChebyshevBasis.derivative``, which is not the derivative of the layer.
+            """
+            x = _aligned(x.view(-1, self.input_dim))
+            if not x.is_cuda:
+                raise RuntimeError("kan_b200 runs on CUDA only")
+            return ops.jacobian(x, self.cheby_coeffs.detach())
+
+        @torch.no_grad()
+        def compute_derivatives(self, x: torch.Tensor, order: int = 1) -> torch.Tensor:
+            """First derivative summed over the inputs, shape (batch, output_dim): sum_i d y_o / d x_i.
+            Same shape as the reference's ``compute_derivatives`` (kan/layers/base.py:102-114), true values."""
+            if order != 1:
+                raise NotImplementedError("only first derivatives are implemented")
+            return self.jacobian(x).sum(-1)
+
         def get_analytical_form(self) -> Dict[str, Any]:
             return {
                 'type': 'ChebyKANLayer',

@@ -189,6 +189,22 @@ def bwd_dx(x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor, mode,
     return out
 
 
+def jacobian(x: torch.Tensor, coeffs: torch.Tensor) -> torch.Tensor:
+    """J[B, out, in] = d y / d x of the layer (the derivative autograd gives), fp32."""
+    _require(x, "x")
+    _require(coeffs, "coeffs")
+    n_in, n_out, dp1 = coeffs.shape
+    if x.dim() != 2 or x.shape[1] != n_in:
+        raise RuntimeError(f"x must have shape [B, {n_in}]")
+    B = x.shape[0]
+    out = torch.empty(B, n_out, n_in, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_jacobian(x.data_ptr(), coeffs.data_ptr(), out.data_ptr(), B, n_in, n_out, dp1 - 1,
+                                           _stream(x))
+    _lib.check(rc, "chebykan_jacobian")
+    return out
+
+
 def sgd_step(param: torch.Tensor, grad: torch.Tensor, lr: float, grad_scale: float = 1.0) -> None:
     _require(param, "param")
     _require(grad, "grad")

@@ -289,3 +289,21 @@ def test_graphed_step_equals_eager_config2():
         opt_e.step()
     for a, b in zip(eager.parameters(), graphed_model.parameters()):
         assert o.rel_l2(b.detach().cpu(), a.detach().cpu()) <= 1e-5
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg", [(33, 7, 5, 8), (100, 1, 1, 8), (16, 40, 12, 3), (9, 3, 2, 32), (5, 4, 4, 0)])
+def test_jacobian_matches_autograd(B, n_in, n_out, deg):
+    """layer.jacobian returns d y / d x of the oracle (autograd on the CPU), shape [B, out, in]."""
+    torch.manual_seed(B + deg)
+    layer = kan_b200.ChebyKANLayer(n_in, n_out, deg, init_scale=0.3).cuda()
+    x = torch.randn(B, n_in)
+    J = layer.jacobian(x.cuda()).cpu()
+    assert J.shape == (B, n_out, n_in)
+    c = layer.cheby_coeffs.detach().cpu()
+    xr = x.clone().requires_grad_(True)
+    y = o.forward(xr, c)
+    J_ref = torch.stack([torch.autograd.grad(y[:, k].sum(), xr, retain_graph=True)[0] for k in range(n_out)], 1)
+    assert o.rel_l2(J, J_ref) <= FP32_TOL
+    assert o.rel_l2(layer.compute_derivatives(x.cuda()).cpu(), J_ref.sum(-1)) <= FP32_TOL
+    with pytest.raises(NotImplementedError):
+        layer.compute_derivatives(x.cuda(), order=2)
