@@ -30,10 +30,14 @@ using namespace tc;
 constexpr int DC_PRODUCER_WARPS = 8;
 constexpr int DC_TMA_WARP = 8;
 constexpr int DC_MMA_WARP = 9;
-constexpr int DC_THREADS = 10 * 32;
+constexpr int DC_X_WARP = 10;             // prefetches x tiles by TMA
+constexpr int DC_THREADS = 11 * 32;
 constexpr int DC_A_STAGE = 128 * 128;     // 128 slots x 32 tf32
 constexpr int DC_KB = 32;                 // batch rows per K block
 constexpr int DC_MAX_ROUNDS = 8;          // (input, 4-row chunk) pairs per lane per K block: TI*8/32
+constexpr int DC_MAX_TI = 28;             // inputs per tile: TI + 3 columns of x fit the 32-float x buffer
+constexpr int DC_X_REGION = 32 * 1024;    // shared memory for the ring of x tiles
+constexpr int DC_MAX_XSLOTS = 16;         // ring depth: twice the stage count where the tiles are small enough
 
 enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_EPILOGUE = 15 };
 
@@ -44,8 +48,9 @@ struct DcSmem {
     // NS divides the 8 producer warps: 8/NS warps share one stage and split its pairs, and a
     // warp only ever fills its own stage, so it is never more than one mbarrier phase ahead
     static constexpr int NS = (BN == 64) ? 8 : 4;
-    static constexpr int BAR_OFFSET = NS * STAGE;
-    static constexpr int NUM_BARS = 2 * NS + 2;              // full, empty, acc_full, drain
+    static constexpr int X_OFFSET = NS * STAGE;
+    static constexpr int BAR_OFFSET = X_OFFSET + DC_X_REGION;
+    static constexpr int NUM_BARS = 2 * NS + 2 * DC_MAX_XSLOTS + 2;   // full, empty, xfull, xempty, acc_full, drain
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
     static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
 };
@@ -66,7 +71,8 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t addr) {
 
 template <int BN>
 __global__ void __launch_bounds__(DC_THREADS, 1)
-dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __restrict__ x,
+dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
+                 int use_x_tma, int x_box_w, int nxs, int x_slot_bytes, const float* __restrict__ x,
                  float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
                  int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
                  int32_t* status) {
@@ -83,8 +89,12 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
     // one "full" barrier per stage: the producer warps of the stage and the TMA's byte count
     auto full = [&](int s) { return bars + 8u * s; };
     auto empty = [&](int s) { return bars + 8u * (NS + s); };
-    const uint32_t acc_full_bar = bars + 8u * (2 * NS);
-    const uint32_t drain_bar = bars + 8u * (2 * NS + 1);
+    // x tiles live in their own ring of nxs slots (K block kb uses slot kb % nxs), deeper than the
+    // stage ring so that the prefetch runs well ahead of the producers
+    auto xfull = [&](int xs) { return bars + 8u * (2 * NS + xs); };                     // tile has landed
+    auto xempty = [&](int xs) { return bars + 8u * (2 * NS + DC_MAX_XSLOTS + xs); };    // tile has been consumed
+    const uint32_t acc_full_bar = bars + 8u * (2 * NS + 2 * DC_MAX_XSLOTS);
+    const uint32_t drain_bar = bars + 8u * (2 * NS + 2 * DC_MAX_XSLOTS + 1);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
@@ -102,6 +112,9 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(full(s), DC_PRODUCER_WARPS / NS + 1); mbar_init(empty(s), 1);
+        }
+        for (int xs = 0; xs < DC_MAX_XSLOTS; ++xs) {
+            mbar_init(xfull(xs), 1); mbar_init(xempty(xs), DC_PRODUCER_WARPS / NS);
         }
         mbar_init(acc_full_bar, 1);
         mbar_init(drain_bar, 1);
@@ -143,17 +156,41 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
             }
         };
         bool alive = true;
-        load_x(my_stage);
+        // x tile in shared memory: [32 rows][x_box_w floats], first column = input (i0 & ~3)
+        const int x_col0 = i0 & 3;
+        if (!use_x_tma) load_x(my_stage);
         for (int kb = my_stage; kb < nkb && alive; kb += NS) {
             const int s = my_stage;
             const uint32_t ph = (uint32_t)((kb / NS) & 1);
             float xc[DC_MAX_ROUNDS][4];
+            if (use_x_tma) {
+                // the x warp loaded this tile as soon as the previous one in this slot had been read
+                const int xslot = kb % nxs;
+                const uint32_t xph = (uint32_t)((kb / nxs) & 1);
+                if (!mbar_wait(xfull(xslot), xph, abort_flag, status, DST_PRODUCER)) { alive = false; break; }
+                const uint32_t xs = smem_base + L::X_OFFSET + xslot * x_slot_bytes;
 #pragma unroll
-            for (int r = 0; r < DC_MAX_ROUNDS; ++r)
+                for (int r = 0; r < DC_MAX_ROUNDS; ++r) {
+                    const int pair = lane + 32 * (G * r + sub);
 #pragma unroll
-                for (int e = 0; e < 4; ++e) xc[r][e] = xn[r][e];
-            load_x(kb + NS);            // in flight while this block is generated
-            if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_PRODUCER)) { alive = false; break; }
+                    for (int e = 0; e < 4; ++e) xc[r][e] = 0.f;
+                    if (r < rounds && pair < npairs) {
+                        const int ii = pair >> 3, c = pair & 7;
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            asm volatile("ld.shared.f32 %0, [%1];" : "=f"(xc[r][e])
+                                         : "r"(xs + (uint32_t)(((4 * c + e) * x_box_w + x_col0 + ii) * 4)));
+                    }
+                }
+                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_PRODUCER)) { alive = false; break; }
+            } else {
+#pragma unroll
+                for (int r = 0; r < DC_MAX_ROUNDS; ++r)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) xc[r][e] = xn[r][e];
+                load_x(kb + NS);            // in flight while this block is generated
+                if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_PRODUCER)) { alive = false; break; }
+            }
             const uint32_t a_stage = smem_base + s * L::STAGE;
 #pragma unroll
             for (int r = 0; r < DC_MAX_ROUNDS; ++r) {
@@ -192,7 +229,12 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
             }
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(full(s));
+            if (lane == 0) {
+                mbar_arrive(full(s));
+                // every x value of this stage has been consumed by now (the loads' results were used
+                // above), so the slot can take the tile of K block kb + NS
+                if (use_x_tma) mbar_arrive(xempty(kb % nxs));
+            }
         }
     } else if (warp == DC_TMA_WARP) {
         // ------------------------------ dY loads ------------------------------
@@ -202,9 +244,9 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
                 const int s = kb % NS;
                 const uint32_t ph = (uint32_t)((kb / NS) & 1);
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
+                const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
                 mbar_arrive_expect_tx(full(s), L::B_STAGE);
                 const uint32_t b_stage = smem_base + s * L::STAGE + DC_A_STAGE;
-                const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
 #pragma unroll
                 for (int m = 0; m < BN / 32; ++m)
                     tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, full(s));
@@ -214,7 +256,24 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const float* __res
                 while (globaltimer_ns() - t0 < 200000ull) { }
             }
         }
-    } else {
+    } else if (warp == DC_X_WARP) {
+        // ------------------------------ x tile prefetch ------------------------------
+        if (lane == 0 && use_x_tma) {
+            bool alive = true;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int xslot = kb % nxs;
+                const uint32_t xph = (uint32_t)((kb / nxs) & 1);
+                if (!mbar_wait(xempty(xslot), xph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
+                mbar_arrive_expect_tx(xfull(xslot), (uint32_t)(DC_KB * x_box_w * 4));
+                tma_load_2d(smem_base + L::X_OFFSET + xslot * x_slot_bytes, &tmap_x, i0 & ~3,
+                            (int)(b_begin + (int64_t)kb * DC_KB), xfull(xslot));
+            }
+            if (!alive) {
+                const uint64_t t0 = globaltimer_ns();
+                while (globaltimer_ns() - t0 < 200000ull) { }
+            }
+        }
+    } else if (warp == DC_MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
         if (lane == 0) {
             bool alive = true;
@@ -288,6 +347,7 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     DcTcPlan p{};
     const int dp1 = (int)deg + 1;
     p.TI = 128 / dp1;
+    if (p.TI > DC_MAX_TI) p.TI = DC_MAX_TI;
     if (p.TI > in) p.TI = (int)in;
     p.i_tiles = (int)ceil_div(in, p.TI);
     p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : 256);
@@ -313,7 +373,7 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
 }
 
 template <int BN>
-int launch_dc(const CUtensorMap& tmap, const float* x, float* dst, int64_t B, int in, int out, int dp1,
+int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
               const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s) {
     using L = DcSmem<BN>;
     static bool attr_set[64] = {false};
@@ -326,7 +386,12 @@ int launch_dc(const CUtensorMap& tmap, const float* x, float* dst, int64_t B, in
         attr_set[dev] = true;
     }
     const unsigned grid = (unsigned)((int64_t)p.i_tiles * p.n_tiles * p.splits);
-    dcoeff_tc_kernel<BN><<<grid, DC_THREADS, L::TOTAL, s>>>(tmap, x, dst, B, in, out, dp1, p.TI, p.i_tiles,
+    // x ring: slots of one tile each (128-byte aligned), twice as many as stages when they fit
+    const int x_slot_bytes = (int)round_up((int64_t)DC_KB * x_box_w * 4, 128);
+    int nxs = 2 * L::NS;
+    if (nxs > DC_MAX_XSLOTS) nxs = DC_MAX_XSLOTS;
+    if (nxs * x_slot_bytes > DC_X_REGION) nxs = L::NS;
+    dcoeff_tc_kernel<BN><<<grid, DC_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in, out, dp1, p.TI, p.i_tiles,
                                                            p.n_tiles, p.rows_per_split, split_stride, add, status);
     return check_cuda(cudaGetLastError());
 }
@@ -338,6 +403,7 @@ int launch_dc(const CUtensorMap& tmap, const float* x, float* dst, int64_t B, in
 bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     const int dp1 = (int)deg + 1;
     int TI = 128 / dp1;
+    if (TI > DC_MAX_TI) TI = DC_MAX_TI;
     if (TI > in) TI = (int)in;
     return B > 0 && (out % 4) == 0 && dp1 <= 128 && TI * 8 <= 32 * DC_MAX_ROUNDS;
 }
@@ -365,12 +431,27 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    // x[B][in] as a TMA tensor when its row pitch allows (in % 4 == 0): a K block's x tile is 32 rows by
+    // TI inputs; the box starts at the 16-byte boundary below the tile's first input and is wide enough
+    // to cover the tile from there (rows and columns outside x read as zeros)
+    CUtensorMap tmap_x = tmap;
+    const int use_x_tma = (in % 4 == 0) ? 1 : 0;
+    const int x_box_w = (int)round_up(p.TI + 3, 4);
+    if (use_x_tma) {
+        const cuuint64_t xdims[2] = {(cuuint64_t)in, (cuuint64_t)B};
+        const cuuint64_t xstrides[1] = {(cuuint64_t)(in * 4)};
+        const cuuint32_t xbox[2] = {(cuuint32_t)x_box_w, (cuuint32_t)DC_KB};
+        const CUresult rx = encode(&tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(x), xdims, xstrides,
+                                   xbox, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rx != CUDA_SUCCESS) { set_last_cuda_error((int)rx); return CHEBYKAN_ECUDA; }
+    }
     float* dst = direct ? dc : reinterpret_cast<float*>(ws);
     const int add = direct && accumulate;
     int rc;
-    if (p.bn == 64) rc = launch_dc<64>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else if (p.bn == 128) rc = launch_dc<128>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else rc = launch_dc<256>(tmap, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    if (p.bn == 64) rc = launch_dc<64>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else if (p.bn == 128) rc = launch_dc<128>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else rc = launch_dc<256>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
     if (rc) return rc;
     if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
     return rc;

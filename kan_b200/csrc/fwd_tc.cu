@@ -266,19 +266,25 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                         tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
                 }
-                if (use_x_tma) {
-                    // the tile is in registers now: hand the buffer back for the next prefetch
+                // Hand the x buffer back for the next prefetch only after a shared-memory store whose
+                // data derives from the tile has been issued: an mbarrier arrive does not wait for this
+                // thread's outstanding ld.shared, the store (and everything after it) does.
+                bool x_held = use_x_tma != 0;
+                auto release_x = [&]() {
                     __syncwarp();
                     if (lane == 0) mbar_arrive(x_empty_bar);
-                }
+                    x_held = false;
+                };
                 // degree 0: T_0 = 1 (ta); then degrees alternate between tb and ta
                 if (!emit(ta)) { alive = false; break; }
+                if (x_held && dp1 == 1) release_x();      // degree 0 only: the tile's values are never used
                 for (int d = 1; d < dp1; d += 2) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j)
 #pragma unroll
                         for (int e = 0; e < CH; ++e) tb[j][e] = fmaf(tt[j][e], ta[j][e], -tb[j][e]);
                     if (!emit(tb)) { alive = false; break; }
+                    if (x_held) release_x();
                     if (d + 1 < dp1) {
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
