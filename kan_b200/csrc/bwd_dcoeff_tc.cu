@@ -32,7 +32,7 @@ constexpr int DC_TMA_WARP = 8;
 constexpr int DC_MMA_WARP = 9;
 constexpr int DC_X_WARP = 10;             // prefetches x tiles by TMA
 constexpr int DC_THREADS = 11 * 32;
-constexpr int DC_A_STAGE = 128 * 128;     // 128 slots x 32 tf32
+constexpr int DC_A_TILE = 128 * 128;      // one M tile of A: 128 slots x 32 tf32
 constexpr int DC_KB = 32;                 // batch rows per K block
 constexpr int DC_MAX_ROUNDS = 8;          // (input, 4-row chunk) pairs per lane per K block: TI*8/32
 constexpr int DC_MAX_TI = 28;             // inputs per tile: TI + 3 columns of x fit the 32-float x buffer
@@ -41,18 +41,22 @@ constexpr int DC_MAX_XSLOTS = 16;         // ring depth: twice the stage count w
 
 enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_EPILOGUE = 15 };
 
+// A CTA owns MT M tiles (MT*128 slots): every dY tile loaded feeds MT groups of MMAs, and the cost
+// of a stage hand-over is spread over MT times more work.  Narrow outputs (tiny MMAs) take MT = 4.
 template <int BN>
 struct DcSmem {
+    static constexpr int MT = (BN == 64) ? 4 : (BN == 128 ? 2 : 1);
+    static constexpr int A_STAGE = MT * DC_A_TILE;
     static constexpr int B_STAGE = BN * 128;                 // 32 rows x BN fp32
-    static constexpr int STAGE = DC_A_STAGE + B_STAGE;
+    static constexpr int STAGE = A_STAGE + B_STAGE;
     // NS divides the 8 producer warps: 8/NS warps share one stage and split its pairs, and a
     // warp only ever fills its own stage, so it is never more than one mbarrier phase ahead
-    static constexpr int NS = (BN == 64) ? 8 : 4;
+    static constexpr int NS = (BN == 64) ? 2 : 4;
     static constexpr int X_OFFSET = NS * STAGE;
     static constexpr int BAR_OFFSET = X_OFFSET + DC_X_REGION;
     static constexpr int NUM_BARS = 2 * NS + 2 * DC_MAX_XSLOTS + 2;   // full, empty, xfull, xempty, acc_full, drain
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
-    static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    static constexpr uint32_t TMEM_COLS = MT * BN < 32 ? 32 : MT * BN;
 };
 
 // MN-major tf32 operand.  32-bit MN-major operands exist only in the "128B swizzle with 32-byte
@@ -208,6 +212,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[e]) : "f"(v[e]));
+                        // slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart)
                         const uint32_t dsta = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                      ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
@@ -246,7 +251,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
                 const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
                 mbar_arrive_expect_tx(full(s), L::B_STAGE);
-                const uint32_t b_stage = smem_base + s * L::STAGE + DC_A_STAGE;
+                const uint32_t b_stage = smem_base + s * L::STAGE + L::A_STAGE;
 #pragma unroll
                 for (int m = 0; m < BN / 32; ++m)
                     tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, full(s));
@@ -283,12 +288,16 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                 if (!mbar_wait(full(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + s * L::STAGE;
-                const uint64_t a_desc = make_smem_desc(a_addr);
-                const uint64_t b_desc = make_smem_desc_mn(a_addr + DC_A_STAGE);
+                const uint64_t b_desc = make_smem_desc_mn(a_addr + L::A_STAGE);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)   // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
-                    umma<CHEBYKAN_MODE_TF32>(tmem_base, a_desc + 2 * k, b_desc + 64 * k, IDESC,
-                                             (uint32_t)((kb | k) != 0));
+                for (int mt = 0; mt < L::MT; ++mt) {
+                    if (mt * 128 >= ti * dp1) break;          // M tiles past the CTA's last slot stay unused
+                    const uint64_t a_desc = make_smem_desc(a_addr + mt * DC_A_TILE);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)   // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
+                        umma<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN, a_desc + 2 * k, b_desc + 64 * k, IDESC,
+                                                 (uint32_t)((kb | k) != 0));
+                }
                 umma_commit(empty(s));
             }
             if (alive) umma_commit(acc_full_bar);
@@ -305,27 +314,33 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
         const bool ok = nkb == 0 ? true : mbar_wait(acc_full_bar, 0, abort_flag, status, DST_EPILOGUE);
         if (__all_sync(0xffffffffu, ok)) {
             tc_fence_after();
-            const int kk = warp * 32 + lane;                 // slot = TMEM lane
-            const bool valid = kk < ti * dp1;
-            const int ii = kk / dp1, d = kk % dp1;
-            float* base = dst + (int64_t)split * split_stride + ((int64_t)(i0 + ii) * out) * dp1 + d;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                if (n0 + c0 >= out) break;
-                uint32_t r[32];
-                if (nkb > 0) { tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + c0, r); tmem_ld_wait(); }
-                else {
+            for (int mt = 0; mt < L::MT; ++mt) {
+                if (mt * 128 >= ti * dp1) break;
+                const int kk = mt * 128 + warp * 32 + lane;      // slot: M tile mt, TMEM lane warp*32+lane
+                const bool valid = kk < ti * dp1;
+                const int ii = kk / dp1, d = kk % dp1;
+                float* base = dst + (int64_t)split * split_stride + ((int64_t)(i0 + ii) * out) * dp1 + d;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= out) break;
+                    uint32_t r[32];
+                    if (nkb > 0) {
+                        tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(mt * BN + c0), r);
+                        tmem_ld_wait();
+                    } else {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) r[e] = 0u;
-                }
-                if (valid) {
+                        for (int e = 0; e < 32; ++e) r[e] = 0u;
+                    }
+                    if (valid) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const int col = n0 + c0 + e;
-                        if (col < out) {
-                            float* q = base + (int64_t)col * dp1;
-                            const float v = __uint_as_float(r[e]);
-                            *q = add_to_dst ? (*q + v) : v;
+                        for (int e = 0; e < 32; ++e) {
+                            const int col = n0 + c0 + e;
+                            if (col < out) {
+                                float* q = base + (int64_t)col * dp1;
+                                const float v = __uint_as_float(r[e]);
+                                *q = add_to_dst ? (*q + v) : v;
+                            }
                         }
                     }
                 }
@@ -341,16 +356,25 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
     }
 }
 
+// inputs per CTA: as many as fit the CTA's MT*128 slots, the x tile buffer and the producers' registers
+int dc_tile_inputs(int64_t in, int dp1, int bn) {
+    const int mt = bn == 64 ? 4 : (bn == 128 ? 2 : 1);
+    const int g = bn == 64 ? 4 : 2;                        // producer warps per stage (8 / NS)
+    int ti = mt * 128 / dp1;
+    if (ti > DC_MAX_TI) ti = DC_MAX_TI;
+    if (ti * 8 > 32 * g * DC_MAX_ROUNDS) ti = 4 * g * DC_MAX_ROUNDS;
+    if (ti > in) ti = (int)in;
+    return ti;
+}
+
 struct DcTcPlan { int TI, i_tiles, bn, n_tiles, splits; int64_t rows_per_split; };
 
 DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     DcTcPlan p{};
     const int dp1 = (int)deg + 1;
-    p.TI = 128 / dp1;
-    if (p.TI > DC_MAX_TI) p.TI = DC_MAX_TI;
-    if (p.TI > in) p.TI = (int)in;
-    p.i_tiles = (int)ceil_div(in, p.TI);
     p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : 256);
+    p.TI = dc_tile_inputs(in, dp1, p.bn);
+    p.i_tiles = (int)ceil_div(in, p.TI);
     p.n_tiles = (int)ceil_div(out, p.bn);
     const int64_t base = (int64_t)p.i_tiles * p.n_tiles;
     // Split the batch so that the CTAs fill whole waves of the 148 SMs: among the candidate split
@@ -402,10 +426,7 @@ int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma,
 // lane must hold its (input, chunk) pairs in registers (TI*8 <= 32*DC_MAX_ROUNDS)
 bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     const int dp1 = (int)deg + 1;
-    int TI = 128 / dp1;
-    if (TI > DC_MAX_TI) TI = DC_MAX_TI;
-    if (TI > in) TI = (int)in;
-    return B > 0 && (out % 4) == 0 && dp1 <= 128 && TI * 8 <= 32 * DC_MAX_ROUNDS;
+    return B > 0 && (out % 4) == 0 && dp1 <= 128;
 }
 
 int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg) {
