@@ -10,8 +10,8 @@
 //            rounded to tf32), K-major tile [256 slots][32 outputs], TMA, 128B swizzle.
 //   D (G):   128 x 256 fp32 in TMEM, two buffers: the epilogue of one tile overlaps the
 //            MMAs of the next.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
-//   warp 0 TMA, warp 1 MMA, warps 2-9 epilogue (two warps per TMEM lane quarter, each
-//   taking half of the tile's inputs; a thread owns one batch row).
+//   warp 0 TMA, warp 1 MMA, warps 2-17 epilogue (four warps per TMEM lane quarter, each
+//   taking a quarter of the tile's inputs; a thread owns one batch row).
 // Every mbarrier wait is bounded, as in the forward kernel.
 #include "tc_common.cuh"
 
@@ -23,7 +23,8 @@ using namespace tc;
 constexpr int DX_TMA_WARP = 0;
 constexpr int DX_MMA_WARP = 1;
 constexpr int DX_EPI_WARP0 = 2;
-constexpr int DX_EPI_WARPS = 8;
+constexpr int DX_EPI_WARPS = 16;
+constexpr int DX_EPI_PARTS = DX_EPI_WARPS / 4;      // warps per TMEM lane quarter: each takes a share of the inputs
 constexpr int DX_THREADS = (2 + DX_EPI_WARPS) * 32;
 constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;
 constexpr int DX_A_STAGE = DX_BM * 128;
@@ -155,15 +156,15 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
     } else {
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3;                          // TMEM lane quarter
-        const int half = (warp - DX_EPI_WARP0) >> 2;     // which half of the tile's inputs
+        const int part = (warp - DX_EPI_WARP0) >> 2;     // which share of the tile's inputs
         int acc = 0; uint32_t acc_ph = 0;
         bool alive = true;
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const int64_t row = (tile / i_tiles) * DX_BM + q * 32 + lane;
             const int i0 = (int)(tile % i_tiles) * TI;
             const int ti = min(TI, in - i0);
-            const int per = (ti + 1) >> 1;
-            const int ii_begin = half * per, ii_end = min(ti, ii_begin + per);
+            const int per = (ti + DX_EPI_PARTS - 1) / DX_EPI_PARTS;
+            const int ii_begin = min(ti, part * per), ii_end = min(ti, ii_begin + per);
             const bool row_ok = row < B;
             const float* xrow = x + (row_ok ? row : 0) * in + i0;
             float* dxrow = dx + (row_ok ? row : 0) * in + i0;
