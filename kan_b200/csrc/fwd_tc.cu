@@ -20,6 +20,15 @@
 //               producer ever waits on a global load (when in % 4 != 0 the tile is
 //               not TMA-addressable and the producers load x themselves).
 //
+// With 512 or more (padded) outputs and more than 128 rows the kernel runs as CTA pairs (cluster of 2,
+// tcgen05 cta_group::2): each CTA generates the basis tile of its own 128 rows and stages half of
+// every W tile; one thread of the even CTA issues M=256 MMAs that read both CTAs' shared memory and
+// write both CTAs' TMEM.  The odd CTA's producers and epilogue arrive on the even CTA's barriers
+// (mapa + mbarrier.arrive.shared::cluster), both W halves count on the even CTA's full barrier
+// (cp.async.bulk.tensor with .cta_group::2, no multicast), and tcgen05.commit multicasts the
+// "stage free" / "accumulator ready" arrivals to both CTAs.  Halving the W bytes per CTA frees
+// shared memory for an 8-deep A ring.
+//
 // A CTA tile is 128 rows x (NSUB*BN) outputs.  Each generated A stage feeds
 // NSUB MMAs groups (one per BN-wide sub-accumulator), so with BN=256, NSUB=2
 // all 512 TMEM columns hold one tile's accumulators and every basis value is
@@ -55,12 +64,13 @@ constexpr int A_STAGE_BYTES = BM * 128;
 enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6, ST_X_LOAD = 7,
        ST_X_WAIT = 8 };
 
-template <int BN, int NSUB>
+template <int BN, int NSUB, int CG = 1>
 struct Smem {
-    static constexpr int NSA = 4;                         // A ring depth
-    static constexpr int NSB = (BN == 256) ? 4 : 8;       // B ring depth
+    // A ring depth / B ring depth (a CTA of a pair stages half of each W tile, which frees room for more A stages)
+    static constexpr int NSA = (CG == 2) ? 8 : 4;
+    static constexpr int NSB = (CG == 2 || BN == 256) ? 4 : 8;
     static constexpr int NACC = (NSUB * BN <= 256) ? 2 : 1;
-    static constexpr int B_STAGE_BYTES = BN * 128;
+    static constexpr int B_STAGE_BYTES = BN * 128 / CG;   // a CTA of a pair holds half of the tile's W rows
     static constexpr int A_OFFSET = 0;
     static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
     static constexpr int X_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;   // x tile: 128 rows x 128 bytes... x 2
@@ -74,20 +84,20 @@ struct Smem {
     static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
-template <int MODE, int BN, int NSUB, bool LN>
+template <int MODE, int BN, int NSUB, bool LN, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
               int64_t num_tiles, int32_t* status, LnFusion ln) {
-    using L = Smem<BN, NSUB>;
+    using L = Smem<BN, NSUB, CG>;
     constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC;
     constexpr int BNT = BN * NSUB;                              // outputs per CTA tile
     constexpr int IB = (MODE == CHEBYKAN_MODE_BF16) ? 64 : 32;  // inputs per K block
     constexpr int CH = (MODE == CHEBYKAN_MODE_BF16) ? 8 : 4;    // elements per 16-byte chunk
     constexpr uint32_t FMT = (MODE == CHEBYKAN_MODE_BF16) ? 1u : 2u;
     constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BN >> 3) << 17) |
-                               ((uint32_t)(BM >> 4) << 24);
+                               ((uint32_t)((BM * CG) >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -107,13 +117,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // CTA pair: the even CTA (rank 0) issues every MMA; each CTA owns 128 of the pair's 256 rows
+    const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const int64_t unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+    const int64_t nunits = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
     const int n_iblk = (in + IB - 1) / IB;
     const int nkb = n_iblk * dp1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NSA; ++s) { mbar_init(fullA(s), NUM_PRODUCER_WARPS); mbar_init(emptyA(s), 1); }
+        for (int s = 0; s < NSA; ++s) { mbar_init(fullA(s), NUM_PRODUCER_WARPS * CG); mbar_init(emptyA(s), 1); }
         for (int s = 0; s < NSB; ++s) { mbar_init(fullB(s), 1); mbar_init(emptyB(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4 * 32); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4 * 32 * CG); }
         mbar_init(drain_bar, 1);
         mbar_init(x_full_bar, 1);
         mbar_init(x_empty_bar, NUM_PRODUCER_WARPS);
@@ -121,12 +135,19 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == MMA_WARP) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();      // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -173,13 +194,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                              ::"r"(dst + j * 4096), "r"(w[j][0]), "r"(w[j][1]), "r"(w[j][2]), "r"(w[j][3]) : "memory");
             fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(fullA(s));
+            if (lane == 0) {
+                if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(fullA(s), 0));
+                else mbar_arrive(fullA(s));
+            }
             if (++s == NSA) { s = 0; ph ^= 1u; }
             return true;
         };
 
-        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            const int64_t m0 = (tile / n_tiles) * BM;
+        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+            const int64_t m0 = (tile / n_tiles) * (BM * CG) + rank * BM;
             // fused LayerNorm of the input rows: per-row mean and 1/std from the previous layer's sums
             float ln_mean[4], ln_rstd[4];
             if (LN && ln.stats_in != nullptr) {
@@ -300,15 +324,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 const int n0 = (int)(tile % n_tiles) * BNT;
                 for (int kb = 0; kb < nkb && alive; ++kb) {
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub) {
                         if (!mbar_wait(emptyB(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
-                        mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES);
-                        tma_load_2d(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
-                                    n0 + sub * BN, fullB(s));
+                        if (CG == 2) {
+                            // both halves count on the even CTA's barrier, which expects the whole tile
+                            if (rank == 0) mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES * 2);
+                            tma_load_2d_pair(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
+                                             n0 + sub * BN + (int)rank * (BN / 2), mapa_cluster(fullB(s), 0));
+                        } else {
+                            mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES);
+                            tma_load_2d(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
+                                        n0 + sub * BN, fullB(s));
+                        }
                         if (++s == NSB) { s = 0; ph ^= 1u; }
                     }
                 }
@@ -324,8 +355,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (lane == 0 && use_x_tma) {
             uint32_t xph = 0;
             bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                const int m0 = (int)((tile / n_tiles) * BM);
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+                const int m0 = (int)((tile / n_tiles) * (BM * CG) + rank * BM);
                 for (int ib = 0; ib < n_iblk; ++ib) {
                     if (!mbar_wait(x_empty_bar, xph ^ 1u, abort_flag, status, ST_X_LOAD)) { alive = false; break; }
                     if (LN && ln.stats_in != nullptr) {
@@ -349,12 +380,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             int sa = 0; uint32_t pha = 0;
             int sb = 0; uint32_t phb = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BNT);
@@ -367,21 +398,24 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                         tc_fence_after();
                         const uint64_t b_desc = make_smem_desc(smem_base + L::B_OFFSET + sb * L::B_STAGE_BYTES);
 #pragma unroll
-                        for (int k = 0; k < 4; ++k)   // 4 x 32 bytes of K per 128-byte row
-                            umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                       (uint32_t)((kb | k) != 0));
-                        umma_commit(emptyB(sb));
+                        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
+                            if (CG == 2) umma2<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                     (uint32_t)((kb | k) != 0));
+                            else umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                            (uint32_t)((kb | k) != 0));
+                        }
+                        if (CG == 2) umma2_commit_both(emptyB(sb)); else umma_commit(emptyB(sb));
                         if (++sb == NSB) { sb = 0; phb ^= 1u; }
                     }
-                    umma_commit(emptyA(sa));
+                    if (CG == 2) umma2_commit_both(emptyA(sa)); else umma_commit(emptyA(sa));
                     if (++sa == NSA) { sa = 0; pha ^= 1u; }
                 }
-                if (alive) umma_commit(acc_full_bar(acc));
+                if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
             }
             if (!alive) {
                 // wait (bounded) until the MMAs already issued have retired
-                umma_commit(drain_bar);
+                if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
@@ -429,8 +463,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 }
             }
         };
-        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            const int64_t row = (tile / n_tiles) * BM + q * 32 + lane;
+        auto arrive_acc_empty = [&](int a) {
+            if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(acc_empty_bar(a), 0));
+            else mbar_arrive(acc_empty_bar(a));
+        };
+        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+            const int64_t row = (tile / n_tiles) * (BM * CG) + rank * BM + q * 32 + lane;
             const int n0 = (int)(tile % n_tiles) * BNT;
             // tcgen05.ld is warp-collective: leave the loop only as a whole warp
             const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, ST_EPILOGUE);
@@ -448,12 +486,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             for (int ch = 0; ch < nchunks; ch += 2) {
                 tmem_ld_wait();
                 if (ch + 1 < nchunks) tmem_ld32(taddr + (ch + 1) * 32, rb);
-                else { tc_fence_before(); mbar_arrive(acc_empty_bar(acc)); }   // accumulator fully read
+                else { tc_fence_before(); arrive_acc_empty(acc); }   // accumulator fully read
                 store32(ra, row, n0 + ch * 32);
                 if (ch + 1 < nchunks) {
                     tmem_ld_wait();
                     if (ch + 2 < nchunks) tmem_ld32(taddr + (ch + 2) * 32, ra);
-                    else { tc_fence_before(); mbar_arrive(acc_empty_bar(acc)); }
+                    else { tc_fence_before(); arrive_acc_empty(acc); }
                     store32(rb, row, n0 + (ch + 1) * 32);
                 }
             }
@@ -470,47 +508,74 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
     tc_fence_before();
     __syncthreads();
+    // neither CTA of a pair leaves (or frees TMEM) while the other may still arrive on its barriers
+    if (CG == 2) cluster_sync_all();
     if (warp == MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+        if (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
     }
 }
 
-template <int MODE, int BN, int NSUB, bool LN>
+template <int MODE, int BN, int NSUB, bool LN, int CG>
 int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
-    using L = Smem<BN, NSUB>;
+    using L = Smem<BN, NSUB, CG>;
     static bool attr_set[64] = {false};
+    static int max_units[64] = {0};       // CTAs (or CTA pairs) that can be resident at once
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(fwd_tc_kernel<MODE, BN, NSUB, LN>,
-                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+    if (dev < 0 || dev >= 64) return CHEBYKAN_EINVAL;
+    auto kernel = fwd_tc_kernel<MODE, BN, NSUB, LN, CG>;
+    if (!attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
+        int sms = 148;
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        max_units[dev] = sms / CG;
+        if (CG == 2) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3((unsigned)(sms & ~1)); q.blockDim = dim3(NUM_THREADS); q.dynamicSmemBytes = L::TOTAL;
+            cudaLaunchAttribute qa[1];
+            qa[0].id = cudaLaunchAttributeClusterDimension;
+            qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+            q.attrs = qa; q.numAttrs = 1;
+            int nclusters = 0;
+            rc = check_cuda(cudaOccupancyMaxActiveClusters(&nclusters, kernel, &q));
+            if (rc) return rc;
+            if (nclusters < 1) return CHEBYKAN_ECUDA;
+            if (nclusters < max_units[dev]) max_units[dev] = nclusters;
+        }
         attr_set[dev] = true;
     }
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     const int n_tiles = (int)ceil_div(n_pad, BN * NSUB);
-    const int64_t num_tiles = ceil_div(B, BM) * n_tiles;
-    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    fwd_tc_kernel<MODE, BN, NSUB, LN><<<grid, NUM_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x, y, B, in, out,
-                                                                      dp1, n_tiles, num_tiles, status, ln);
-    return check_cuda(cudaGetLastError());
+    const int64_t num_tiles = ceil_div(B, BM * CG) * n_tiles;
+    const unsigned units = (unsigned)(num_tiles < max_units[dev] ? num_tiles : max_units[dev]);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units * CG); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_tiles,
+                                         num_tiles, status, ln));
 }
 
 // the LayerNorm-fused variant is a separate instantiation, so the plain kernel carries none of its registers
-template <int MODE, int BN, int NSUB>
+template <int MODE, int BN, int NSUB, int CG = 1>
 int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
     if (ln.stats_in != nullptr || ln.stats_out != nullptr)
-        return launch_one_ln<MODE, BN, NSUB, true>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
-    return launch_one_ln<MODE, BN, NSUB, false>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+        return launch_one_ln<MODE, BN, NSUB, true, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    return launch_one_ln<MODE, BN, NSUB, false, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
 }
 
 template <int MODE>
-int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, const float* x, float* y,
+int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, int cg, const float* x, float* y,
                 int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+    if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
@@ -525,12 +590,13 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     if (!encode) return CHEBYKAN_ECUDA;
     // tile width: 2 x 256 outputs (all of TMEM) when there are that many, else 256 or 128
     int bn = 128, nsub = 1;
-    if (p.n_pad >= 384) { bn = 256; nsub = 2; }
+    int cg = 1;
+    if (p.n_pad >= 384) { bn = 256; nsub = 2; cg = (B > BM) ? 2 : 1; }
     else if (p.n_pad == 256) { bn = 256; }
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
     const cuuint64_t strides[1] = {(cuuint64_t)(p.k_pad * p.elem)};
-    const cuuint32_t box[2] = {(cuuint32_t)p.ib, (cuuint32_t)bn};
+    const cuuint32_t box[2] = {(cuuint32_t)p.ib, (cuuint32_t)(bn / cg)};
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = (mode == CHEBYKAN_MODE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                                 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -553,9 +619,9 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     }
     const int dp1 = (int)deg + 1;
     if (mode == CHEBYKAN_MODE_BF16)
-        return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
+        return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
                                                (int)p.n_pad, status, s, ln);
-    return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, x, y, B, (int)in, (int)out, dp1,
+    return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
                                            (int)p.n_pad, status, s, ln);
 }
 
