@@ -24,6 +24,12 @@ SHAPES = [
     (1000, 96, 300, 8, "normal"),         # ragged rows and three N tiles of 128
     (129, 32, 256, 0, "normal"),          # degree 0
     (20000, 128, 256, 2, "normal"),       # more tiles than SMs: persistent loop, both accumulators
+    # 512 or more padded outputs and more than 128 rows: CTA pairs (cta_group::2)
+    (130, 64, 512, 3, "normal"),          # the pair's odd CTA holds 2 real rows
+    (257, 100, 640, 4, "normal"),         # second pair: only the even CTA has rows; ragged second N tile
+    (1000, 45, 520, 5, "normal"),         # in not a multiple of 4 (no x prefetch) with pairs
+    (40000, 64, 512, 1, "normal"),        # more pairs than SM pairs: persistent loop over pair tiles
+    (128, 64, 512, 3, "normal"),          # exactly 128 rows: single-CTA kernel on a wide layer
 ]
 
 
@@ -263,7 +269,8 @@ def test_forward_host_pipelined(mode, tol):
 
 
 @pytest.mark.parametrize("mode", ["bf16", "tf32"])
-@pytest.mark.parametrize("widths,deg,B", [((256, 256, 256, 256), 4, 1000), ((200, 136, 72), 3, 333), ((64, 512, 64), 8, 4096)])
+@pytest.mark.parametrize("widths,deg,B", [((256, 256, 256, 256), 4, 1000), ((200, 136, 72), 3, 333), ((64, 512, 64), 8, 4096),
+                                          ((64, 512, 1024, 64), 3, 700)])   # CTA pairs with both fusion sides
 def test_fused_layernorm_stack(mode, widths, deg, B):
     """Sequential(Cheby, LN, Cheby, LN, ...) with the LayerNorms folded into the kernels: same output as the
     unfused modules (tight), and within the tensor-core tolerance per layer of the CPU oracle model."""
