@@ -43,15 +43,19 @@ enum { DST_PRODUCER = 11, DST_TMA = 12, DST_MMA_A = 13, DST_EPILOGUE = 15 };
 
 // A CTA owns MT M tiles (MT*128 slots): every dY tile loaded feeds MT groups of MMAs, and the cost
 // of a stage hand-over is spread over MT times more work.  Narrow outputs (tiny MMAs) take MT = 4.
-template <int BN>
+// BN = 512 is two 256-wide accumulators (all of TMEM) fed by the same generated A tile, which halves
+// the basis generation per MMA on wide layers.
+template <int BN, int CG = 1>
 struct DcSmem {
     static constexpr int MT = (BN == 64) ? 4 : (BN == 128 ? 2 : 1);
+    static constexpr int BNI = BN > 256 ? 256 : BN;          // N of one MMA
+    static constexpr int NSUB = BN / BNI;
     static constexpr int A_STAGE = MT * DC_A_TILE;
-    static constexpr int B_STAGE = BN * 128;                 // 32 rows x BN fp32
+    static constexpr int B_STAGE = BN * 128 / CG;            // 32 rows x BN fp32; a CTA of a pair stages half
     static constexpr int STAGE = A_STAGE + B_STAGE;
     // NS divides the 8 producer warps: 8/NS warps share one stage and split its pairs, and a
     // warp only ever fills its own stage, so it is never more than one mbarrier phase ahead
-    static constexpr int NS = (BN == 64) ? 2 : 4;
+    static constexpr int NS = (BN == 64 || (BN == 512 && CG == 1)) ? 2 : 4;
     static constexpr int X_OFFSET = NS * STAGE;
     static constexpr int BAR_OFFSET = X_OFFSET + DC_X_REGION;
     static constexpr int NUM_BARS = 2 * NS + 2 * DC_MAX_XSLOTS + 2;   // full, empty, xfull, xempty, acc_full, drain
@@ -73,18 +77,18 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t addr) {
     return d;
 }
 
-template <int BN>
+template <int BN, int CG>
 __global__ void __launch_bounds__(DC_THREADS, 1)
 dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
                  int use_x_tma, int x_box_w, int nxs, int x_slot_bytes, const float* __restrict__ x,
                  float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
                  int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
                  int32_t* status) {
-    using L = DcSmem<BN>;
+    using L = DcSmem<BN, CG>;
     constexpr int NS = L::NS;
-    // tf32 x tf32 -> f32, A K-major, B MN-major, M = 128, N = BN
-    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) |
-                               ((uint32_t)(128 >> 4) << 24);
+    // tf32 x tf32 -> f32, A K-major, B MN-major, M = 128 per CTA, N = BNI
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | (1u << 16) | ((uint32_t)(L::BNI >> 3) << 17) |
+                               ((uint32_t)((128 * CG) >> 4) << 24);
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -103,19 +107,23 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    int bid = blockIdx.x;
+    // CTA pair (CG == 2): two neighbouring input tiles share every dY tile; the even CTA issues the
+    // pair's M = 256 MMAs.  i_tiles is even then, and a tile past the last input has ti = 0.
+    const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+    int bid = (CG == 2) ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
     const int n_t = bid % n_tiles; bid /= n_tiles;
-    const int i_t = bid % i_tiles; bid /= i_tiles;
+    const int i_t = (CG == 2) ? (bid % (i_tiles / 2)) * 2 + (int)rank : bid % i_tiles;
+    bid /= (CG == 2) ? (i_tiles / 2) : i_tiles;
     const int split = bid;
     const int i0 = i_t * TI, n0 = n_t * BN;
-    const int ti = min(TI, in - i0);
+    const int ti = max(0, min(TI, in - i0));
     const int64_t b_begin = (int64_t)split * rows_per_split;      // a multiple of 32
     const int64_t b_end = min(B, b_begin + rows_per_split);
     const int nkb = (int)((b_end - b_begin + DC_KB - 1) / DC_KB);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) {
-            mbar_init(full(s), DC_PRODUCER_WARPS / NS + 1); mbar_init(empty(s), 1);
+            mbar_init(full(s), CG * DC_PRODUCER_WARPS / NS + 1); mbar_init(empty(s), 1);
         }
         for (int xs = 0; xs < DC_MAX_XSLOTS; ++xs) {
             mbar_init(xfull(xs), 1); mbar_init(xempty(xs), DC_PRODUCER_WARPS / NS);
@@ -126,12 +134,19 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == DC_MMA_WARP) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();      // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -235,7 +250,8 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                mbar_arrive(full(s));
+                if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(full(s), 0));
+                else mbar_arrive(full(s));
                 // every x value of this stage has been consumed by now (the loads' results were used
                 // above), so the slot can take the tile of K block kb + NS
                 if (use_x_tma) mbar_arrive(xempty(kb % nxs));
@@ -250,11 +266,22 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                 const uint32_t ph = (uint32_t)((kb / NS) & 1);
                 if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, DST_TMA)) { alive = false; break; }
                 const int row0 = (int)(b_begin + (int64_t)kb * DC_KB);
-                mbar_arrive_expect_tx(full(s), L::B_STAGE);
                 const uint32_t b_stage = smem_base + s * L::STAGE + L::A_STAGE;
+                if (CG == 2) {
+                    // this CTA stages outputs [128 rank, 128 rank + 128) of each 256-wide half; every byte
+                    // counts on the even CTA's barrier, which expects the whole dY tile
+                    if (rank == 0) mbar_arrive_expect_tx(full(s), L::B_STAGE * 2);
+                    const uint32_t bar0 = mapa_cluster(full(s), 0);
 #pragma unroll
-                for (int m = 0; m < BN / 32; ++m)
-                    tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, full(s));
+                    for (int m = 0; m < BN / 64; ++m)
+                        tma_load_2d_pair(b_stage + m * 4096, &tmap_dy,
+                                         n0 + (m / 4) * L::BNI + (int)rank * (L::BNI / 2) + 32 * (m % 4), row0, bar0);
+                } else {
+                    mbar_arrive_expect_tx(full(s), L::B_STAGE);
+#pragma unroll
+                    for (int m = 0; m < BN / 32; ++m)
+                        tma_load_2d(b_stage + m * 4096, &tmap_dy, n0 + 32 * m, row0, full(s));
+                }
             }
             if (!alive) {
                 const uint64_t t0 = globaltimer_ns();
@@ -280,29 +307,40 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
         }
     } else if (warp == DC_MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             bool alive = true;
+            // slots of the pair: the odd CTA's tile may hold fewer (or no) inputs, its MMAs run all the same
             for (int kb = 0; kb < nkb; ++kb) {
                 const int s = kb % NS;
                 const uint32_t ph = (uint32_t)((kb / NS) & 1);
                 if (!mbar_wait(full(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t a_addr = smem_base + s * L::STAGE;
-                const uint64_t b_desc = make_smem_desc_mn(a_addr + L::A_STAGE);
 #pragma unroll
                 for (int mt = 0; mt < L::MT; ++mt) {
                     if (mt * 128 >= ti * dp1) break;          // M tiles past the CTA's last slot stay unused
                     const uint64_t a_desc = make_smem_desc(a_addr + mt * DC_A_TILE);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)   // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
-                        umma<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN, a_desc + 2 * k, b_desc + 64 * k, IDESC,
-                                                 (uint32_t)((kb | k) != 0));
+                    for (int sub = 0; sub < L::NSUB; ++sub) {
+                        if (sub > 0 && n0 + sub * L::BNI >= out) break;   // no real outputs in this half
+                        // column blocks of 32 outputs are 4096 B apart
+                        const uint64_t b_desc = make_smem_desc_mn(a_addr + L::A_STAGE + sub * (L::BNI / 32 / CG) * 4096);
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) { // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
+                            if (CG == 2)
+                                umma2<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN + sub * L::BNI, a_desc + 2 * k,
+                                                          b_desc + 64 * k, IDESC, (uint32_t)((kb | k) != 0));
+                            else
+                                umma<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN + sub * L::BNI, a_desc + 2 * k,
+                                                         b_desc + 64 * k, IDESC, (uint32_t)((kb | k) != 0));
+                        }
+                    }
                 }
-                umma_commit(empty(s));
+                if (CG == 2) umma2_commit_both(empty(s)); else umma_commit(empty(s));
             }
-            if (alive) umma_commit(acc_full_bar);
+            if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar); else umma_commit(acc_full_bar); }
             else {
-                umma_commit(drain_bar);
+                if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
@@ -350,16 +388,21 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
 
     tc_fence_before();
     __syncthreads();
+    // neither CTA of a pair leaves (or frees TMEM) while the other may still arrive on its barriers
+    if (CG == 2) cluster_sync_all();
     if (warp == DC_MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+        if (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
     }
 }
 
 // inputs per CTA: as many as fit the CTA's MT*128 slots, the x tile buffer and the producers' registers
 int dc_tile_inputs(int64_t in, int dp1, int bn) {
     const int mt = bn == 64 ? 4 : (bn == 128 ? 2 : 1);
-    const int g = bn == 64 ? 4 : 2;                        // producer warps per stage (8 / NS)
+    const int g = (bn == 64 || bn == 512) ? 4 : 2;         // producer warps per stage (8 / NS)
     int ti = mt * 128 / dp1;
     if (ti > DC_MAX_TI) ti = DC_MAX_TI;
     if (ti * 8 > 32 * g * DC_MAX_ROUNDS) ti = 4 * g * DC_MAX_ROUNDS;
@@ -367,14 +410,17 @@ int dc_tile_inputs(int64_t in, int dp1, int bn) {
     return ti;
 }
 
-struct DcTcPlan { int TI, i_tiles, bn, n_tiles, splits; int64_t rows_per_split; };
+struct DcTcPlan { int TI, i_tiles, bn, cg, n_tiles, splits; int64_t rows_per_split; };
 
 DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     DcTcPlan p{};
     const int dp1 = (int)deg + 1;
-    p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : 256);
+    p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : (out <= 256 ? 256 : 512));
     p.TI = dc_tile_inputs(in, dp1, p.bn);
     p.i_tiles = (int)ceil_div(in, p.TI);
+    // wide layers run as CTA pairs over neighbouring input tiles (an odd count gets one empty tile)
+    p.cg = (p.bn == 512 && p.i_tiles >= 2) ? 2 : 1;
+    if (p.cg == 2) p.i_tiles = (int)round_up(p.i_tiles, 2);
     p.n_tiles = (int)ceil_div(out, p.bn);
     const int64_t base = (int64_t)p.i_tiles * p.n_tiles;
     // Split the batch so that the CTAs fill whole waves of the 148 SMs: among the candidate split
@@ -396,16 +442,16 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     return p;
 }
 
-template <int BN>
+template <int BN, int CG = 1>
 int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
               const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s) {
-    using L = DcSmem<BN>;
+    using L = DcSmem<BN, CG>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
+    auto kernel = dcoeff_tc_kernel<BN, CG>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(dcoeff_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                 L::TOTAL));
+        int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
         attr_set[dev] = true;
     }
@@ -415,9 +461,15 @@ int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma,
     int nxs = 2 * L::NS;
     if (nxs > DC_MAX_XSLOTS) nxs = DC_MAX_XSLOTS;
     if (nxs * x_slot_bytes > DC_X_REGION) nxs = L::NS;
-    dcoeff_tc_kernel<BN><<<grid, DC_THREADS, L::TOTAL, s>>>(tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in, out, dp1, p.TI, p.i_tiles,
-                                                           p.n_tiles, p.rows_per_split, split_stride, add, status);
-    return check_cuda(cudaGetLastError());
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(DC_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in,
+                                         out, dp1, p.TI, p.i_tiles, p.n_tiles, p.rows_per_split, split_stride, add,
+                                         status));
 }
 
 }  // namespace
@@ -472,7 +524,9 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
     int rc;
     if (p.bn == 64) rc = launch_dc<64>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
     else if (p.bn == 128) rc = launch_dc<128>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else rc = launch_dc<256>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else if (p.bn == 256) rc = launch_dc<256>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else if (p.cg == 2) rc = launch_dc<512, 2>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
+    else rc = launch_dc<512>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
     if (rc) return rc;
     if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
     return rc;
