@@ -144,6 +144,11 @@ DC_SHAPES = [
     (5000, 40, 132, 5, "normal"),        # BN = 256 with a ragged N tile
     (40000, 8, 8, 7, "normal"),          # batch split over many CTAs (workspace + reduction)
     (1, 4, 4, 2, "normal"),              # single row
+    # more than 256 outputs: 512-column tiles, CTA pairs over neighbouring input tiles
+    (700, 45, 300, 2, "normal"),         # 28 inputs per tile: two tiles = one pair; second half-tile ragged
+    (3000, 70, 520, 8, "normal"),        # 14 per tile: five tiles padded to six (an empty tile); two N tiles
+    (20000, 20, 512, 6, "normal"),       # pairs with the batch split over CTAs (workspace + reduction)
+    (500, 10, 260, 20, "normal"),        # a single input tile with 512-column tiles: no pair
 ]
 
 
