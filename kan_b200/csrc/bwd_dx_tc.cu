@@ -12,6 +12,9 @@
 //            MMAs of the next.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
 //   warp 0 TMA, warp 1 MMA, warps 2-17 epilogue (four warps per TMEM lane quarter, each
 //   taking a quarter of the tile's inputs; a thread owns one batch row).
+// With more than 128 rows the kernel runs as CTA pairs (cluster of 2, cta_group::2): the pair
+// covers 256 rows, each CTA loads the dY tile of its own 128 rows and half of the Wd tile, and
+// the even CTA issues M = 256 MMAs, so every coefficient byte is fetched once per 256 rows.
 // Every mbarrier wait is bounded, as in the forward kernel.
 #include "tc_common.cuh"
 
@@ -29,11 +32,16 @@ constexpr int DX_THREADS = (2 + DX_EPI_WARPS) * 32;
 constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;
 constexpr int DX_A_STAGE = DX_BM * 128;
 constexpr int DX_B_STAGE = DX_BN * 128;
-constexpr int DX_STAGE = DX_A_STAGE + DX_B_STAGE;
-constexpr int DX_NS = 4;
-constexpr int DX_BAR_OFFSET = DX_NS * DX_STAGE;
-constexpr int DX_NUM_BARS = 2 * DX_NS + 5;     // full, empty, acc_full[2], acc_empty[2], drain
-constexpr int DX_SMEM = DX_BAR_OFFSET + DX_NUM_BARS * 8 + 16 + 1024;
+// a CTA of a pair stages half of every Wd tile (a ring deeper than 4 stages measured no faster)
+template <int CG>
+struct DxSmem {
+    static constexpr int NS = 4;
+    static constexpr int NUM_BARS = 2 * NS + 5;     // full, empty, acc_full[2], acc_empty[2], drain
+    static constexpr int B_STAGE = DX_B_STAGE / CG;
+    static constexpr int STAGE = DX_A_STAGE + B_STAGE;
+    static constexpr int BAR_OFFSET = NS * STAGE;
+    static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
+};
 
 enum { XST_TMA = 21, XST_MMA_FULL = 22, XST_MMA_ACC = 23, XST_EPILOGUE = 24 };
 
@@ -62,13 +70,16 @@ pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, i
     }
 }
 
+template <int CG>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
              const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
              int i_tiles, int64_t num_tiles, int32_t* status) {
-    constexpr int NS = DX_NS;
+    using L = DxSmem<CG>;
+    constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS;
+    constexpr int DX_STAGE = L::STAGE, DX_BAR_OFFSET = L::BAR_OFFSET;
     constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(DX_BN >> 3) << 17) |
-                               ((uint32_t)(DX_BM >> 4) << 24);
+                               ((uint32_t)((DX_BM * CG) >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
@@ -83,21 +94,32 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (out + DX_KB - 1) / DX_KB;
+    // CTA pair: a tile is 256 rows, this CTA owns rows [128 rank, 128 rank + 128) of it
+    const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const int64_t unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
+    const int64_t nunits = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), DX_EPI_WARPS); }
+        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), DX_EPI_WARPS * CG); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == DX_MMA_WARP) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(smem_u32((const void*)tmem_slot)), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                         ::"r"(smem_u32((const void*)tmem_slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (CG == 2) cluster_sync_all();      // the peer's barriers exist before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -105,15 +127,23 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                const int m0 = (int)((tile / i_tiles) * DX_BM);
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+                const int m0 = (int)((tile / i_tiles) * (DX_BM * CG) + rank * DX_BM);
                 const int slot0 = (int)(tile % i_tiles) * TI * dp1;
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, XST_TMA)) { alive = false; break; }
-                    mbar_arrive_expect_tx(full_bar(s), DX_STAGE);
                     const uint32_t st = smem_base + s * DX_STAGE;
-                    tma_load_2d(st, &tmap_dy, kb * DX_KB, m0, full_bar(s));
-                    tma_load_2d(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0, full_bar(s));
+                    if (CG == 2) {
+                        // both CTAs' bytes count on the even CTA's barrier
+                        if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * DX_STAGE);
+                        const uint32_t bar0 = mapa_cluster(full_bar(s), 0);
+                        tma_load_2d_pair(st, &tmap_dy, kb * DX_KB, m0, bar0);
+                        tma_load_2d_pair(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0 + (int)rank * (DX_BN / 2), bar0);
+                    } else {
+                        mbar_arrive_expect_tx(full_bar(s), DX_STAGE);
+                        tma_load_2d(st, &tmap_dy, kb * DX_KB, m0, full_bar(s));
+                        tma_load_2d(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0, full_bar(s));
+                    }
                     if (++s == NS) { s = 0; ph ^= 1u; }
                 }
             }
@@ -123,11 +153,11 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             }
         }
     } else if (warp == DX_MMA_WARP) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
-            for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, XST_MMA_ACC)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * DX_BN);
@@ -138,17 +168,20 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     const uint64_t a_desc = make_smem_desc(a_addr);
                     const uint64_t b_desc = make_smem_desc(a_addr + DX_A_STAGE);
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        umma<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                 (uint32_t)((kb | k) != 0));
-                    umma_commit(empty_bar(s));
+                    for (int k = 0; k < 4; ++k) {
+                        if (CG == 2) umma2<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                               (uint32_t)((kb | k) != 0));
+                        else umma<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                      (uint32_t)((kb | k) != 0));
+                    }
+                    if (CG == 2) umma2_commit_both(empty_bar(s)); else umma_commit(empty_bar(s));
                     if (++s == NS) { s = 0; ph ^= 1u; }
                 }
-                if (alive) umma_commit(acc_full_bar(acc));
+                if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
                 if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
             }
             if (!alive) {
-                umma_commit(drain_bar);
+                if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
@@ -159,8 +192,8 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
         const int part = (warp - DX_EPI_WARP0) >> 2;     // which share of the tile's inputs
         int acc = 0; uint32_t acc_ph = 0;
         bool alive = true;
-        for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            const int64_t row = (tile / i_tiles) * DX_BM + q * 32 + lane;
+        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+            const int64_t row = (tile / i_tiles) * (DX_BM * CG) + rank * DX_BM + q * 32 + lane;
             const int i0 = (int)(tile % i_tiles) * TI;
             const int ti = min(TI, in - i0);
             const int per = (ti + DX_EPI_PARTS - 1) / DX_EPI_PARTS;
@@ -217,16 +250,24 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty_bar(acc));
+            if (lane == 0) {
+                if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(acc_empty_bar(acc), 0));
+                else mbar_arrive(acc_empty_bar(acc));
+            }
             if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
         }
     }
 
     tc_fence_before();
     __syncthreads();
+    // neither CTA of a pair leaves (or frees TMEM) while the other may still arrive on its barriers
+    if (CG == 2) cluster_sync_all();
     if (warp == DX_MMA_WARP) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if (CG == 2)
+            asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else
+            asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -240,6 +281,39 @@ bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
 int64_t dx_tc_workspace_bytes(int64_t in, int64_t out, int64_t deg) {
     return in * (deg + 1) * round_up(out, 32) * 4;
 }
+
+namespace {
+template <int CG>
+int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
+                     int in, int out, int dp1, int32_t* status, cudaStream_t s) {
+    using L = DxSmem<CG>;
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    auto kernel = dx_tc_kernel<CG>;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        if (rc) return rc;
+        attr_set[dev] = true;
+    }
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int TI = DX_BN / dp1;
+    if (TI > in) TI = in;
+    const int i_tiles = (int)ceil_div(in, TI);
+    const int64_t num_tiles = ceil_div(B, DX_BM * CG) * i_tiles;
+    const int64_t max_units = sms / CG;
+    const unsigned units = (unsigned)(num_tiles < max_units ? num_tiles : max_units);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(units * CG); cfg.blockDim = dim3(DX_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
+    cudaLaunchAttribute attrs[1];
+    attrs[0].id = cudaLaunchAttributeClusterDimension;
+    attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 1;
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, dp1, TI, i_tiles, num_tiles,
+                                         status));
+}
+}  // namespace
 
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
                  int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s) {
@@ -257,6 +331,7 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
         int rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
     }
+    const int cg = B > DX_BM ? 2 : 1;
     CUtensorMap tmap_dy, tmap_w;
     const cuuint32_t estr[2] = {1, 1};
     {
@@ -271,30 +346,14 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     {
         const cuuint64_t dims[2] = {(cuuint64_t)out_pad, (cuuint64_t)slots};
         const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 4)};
-        const cuuint32_t box[2] = {DX_KB, DX_BN};
+        const cuuint32_t box[2] = {DX_KB, (cuuint32_t)(DX_BN / cg)};
         const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ws, dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
     }
-    static bool attr_set[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        int rc = check_cuda(cudaFuncSetAttribute(dx_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DX_SMEM));
-        if (rc) return rc;
-        attr_set[dev] = true;
-    }
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int TI = DX_BN / dp1;
-    if (TI > in) TI = (int)in;
-    const int i_tiles = (int)ceil_div(in, TI);
-    const int64_t num_tiles = ceil_div(B, DX_BM) * i_tiles;
-    const unsigned grid = (unsigned)(num_tiles < sms ? num_tiles : sms);
-    dx_tc_kernel<<<grid, DX_THREADS, DX_SMEM, s>>>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, TI, i_tiles,
-                                                   num_tiles, status);
-    return check_cuda(cudaGetLastError());
+    if (cg == 2) return launch_dx_kernel<2>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, status, s);
+    return launch_dx_kernel<1>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, status, s);
 }
 
 }  // namespace chebykan
