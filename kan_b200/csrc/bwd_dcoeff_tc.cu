@@ -217,16 +217,19 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                 if (r < rounds && pair < npairs) {
                     const int ii = pair >> 3, c = pair & 7;
                     float t2[4], ta[4], tb[4];
+                    bool finite = true;           // a NaN input makes every degree NaN: no rounding add then
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const float t = tanh_fast(xc[r][e]);
+                        finite = finite && (t == t);
                         t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
                     }
+                    const uint32_t inc = finite ? TF32_HALF_ULP : 0u;
                     // one 16-byte chunk (4 batch rows) per degree; ta / tb alternate as the newest value
                     auto store4 = [&](int row, const float (&v)[4]) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[e]) : "f"(v[e]));
+                        for (int e = 0; e < 4; ++e) w[e] = tf32_rna(v[e], inc);
                         // slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart)
                         const uint32_t dsta = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"

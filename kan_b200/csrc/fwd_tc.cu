@@ -165,6 +165,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         const uint32_t st_off = (uint32_t)(r0 * 128 + ((c ^ (r0 & 7)) << 4));  // (r0+32j)&7 == r0&7
         // recurrence state: ta/tb alternate as (T_{d-1}, T_{d-2}); tt = 2t
         float tt[4][CH], ta[4][CH], tb[4][CH];
+        uint32_t inc[4];        // tf32 rounding increment per row: 0 where the row's inputs of this block hold a NaN
         int s = 0; uint32_t ph = 0;
         uint32_t xph = 0;
         bool alive = true;
@@ -183,7 +184,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int q = 0; q < 4; ++q)
-                        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w[j][q]) : "f"(v[j][q % CH]));
+                        w[j][q] = tf32_rna(v[j][q % CH], inc[j]);
                 }
             }
             if (!mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) return false;
@@ -284,11 +285,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                         for (int e = 0; e < CH; ++e)
                             v[e] = fmaf(fmaf(v[e], ln_rstd[j], ln_mean[j]), ln_g[e], ln_b[e]);
                     }
+                    bool finite = true;
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
                         const float t = tanh_fast(v[e]);
+                        finite = finite && (t == t);
                         tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
+                    inc[j] = finite ? TF32_HALF_ULP : 0u;
                 }
                 // Hand the x buffer back for the next prefetch only after a shared-memory store whose
                 // data derives from the tile has been issued: an mbarrier arrive does not wait for this

@@ -114,6 +114,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// fp32 -> tf32, round to nearest with ties away from zero: adding half a tf32 ulp (0x1000) to the
+// bit pattern and letting the tensor pipe ignore the low 13 bits is exactly cvt.rna.tf32.f32 for
+// finite values (the carry into the exponent is the correct round-up), in one integer add instead
+// of the multi-instruction cvt.  A NaN (0x7fffffff) would wrap around to a tiny number, so callers
+// pass inc = 0 for values that derive from a NaN input (TF32_HALF_ULP otherwise): the NaN then
+// reaches the tensor pipe unchanged.
+constexpr uint32_t TF32_HALF_ULP = 0x1000u;
+__device__ __forceinline__ uint32_t tf32_rna(float v, uint32_t inc) { return __float_as_uint(v) + inc; }
+
 // ---- CTA pairs (cta_group::2): one thread of the even CTA issues MMAs that span both CTAs ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

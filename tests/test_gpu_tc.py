@@ -317,3 +317,27 @@ def test_fused_layernorm_stack(mode, widths, deg, B):
     assert err_fused <= 1.5 * TC_TOL * (len(widths) - 1)
     # parameters are shared, not copied
     assert fused.layers[0].cheby_coeffs is model[0].cheby_coeffs
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+def test_tc_nan_input_propagates(mode):
+    """A NaN input poisons exactly its own row of y and its own input's coefficient gradients (degrees >= 1; T_0 is
+    the constant 1 here), as a NaN does in the reference's tanh -> acos -> cos chain; everything else is untouched.
+    The tf32 paths round finite basis values with an integer add and must not turn the NaN into a finite number."""
+    B, n_in, n_out, deg = 300, 40, 520, 5
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, seed=91)
+    clean = run_fwd(x, coeffs, mode)
+    xn = x.clone()
+    xn[7, 3] = float("nan")
+    y = ops.forward(xn.cuda(), ops.pack_coeffs(coeffs.cuda(), mode), n_in, n_out, deg, mode).cpu()
+    ops.check_status()
+    assert bool(torch.isnan(y[7]).all())
+    keep = torch.ones(B, dtype=torch.bool)
+    keep[7] = False
+    assert torch.equal(y[keep], clean[keep])
+    dC = ops.bwd_dcoeff(xn.cuda(), dy.cuda(), n_in, n_out, deg, mode).cpu()
+    ops.check_status()
+    assert bool(torch.isnan(dC[3, :, 1:]).all())
+    others = torch.ones(n_in, dtype=torch.bool)
+    others[3] = False
+    assert bool(torch.isfinite(dC[others]).all())
