@@ -58,7 +58,7 @@ constexpr int X_WARP = 14;
 constexpr int NUM_THREADS = 16 * 32;
 constexpr int PRODUCER_REGS = 168;
 constexpr int OTHER_REGS = 88;
-constexpr int A_STAGE_BYTES = BM * 128;
+constexpr int A_PANEL_BYTES = BM * 128;     // one K block of A: 128 rows x 128 bytes
 
 // status codes recorded by a wait that gave up
 enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6, ST_X_LOAD = 7,
@@ -67,10 +67,16 @@ enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, 
 template <int BN, int NSUB, int CG = 1>
 struct Smem {
     // A ring depth / B ring depth (a CTA of a pair stages half of each W tile, which frees room for more A stages)
-    static constexpr int NSA = (CG == 2) ? 8 : 4;
-    static constexpr int NSB = (CG == 2 || BN == 256) ? 4 : 8;
+    // K blocks per stage.  On narrow layers (one tile of 128 or 64 outputs) an MMA is so small that the
+    // hand-over of a stage (barrier waits, proxy fence, arrive, commit) costs more than its math: three
+    // or four K blocks share one hand-over there, in rings of two stages.
+    static constexpr int KP = (BN == 128 && NSUB == 1) ? 3 : (BN == 64 ? 4 : 1);
+    static constexpr int NSA = (KP > 1) ? 2 : ((CG == 2) ? 8 : 4);
+    static constexpr int NSB = (KP > 1) ? 2 : ((CG == 2 || BN == 256) ? 4 : 8);
     static constexpr int NACC = (NSUB * BN <= 256) ? 2 : 1;
-    static constexpr int B_STAGE_BYTES = BN * 128 / CG;   // a CTA of a pair holds half of the tile's W rows
+    static constexpr int B_PANEL_BYTES = BN * 128 / CG;   // a CTA of a pair holds half of the tile's W rows
+    static constexpr int A_STAGE_BYTES = KP * A_PANEL_BYTES;
+    static constexpr int B_STAGE_BYTES = KP * B_PANEL_BYTES;
     static constexpr int A_OFFSET = 0;
     static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
     static constexpr int X_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;   // x tile: 128 rows x 128 bytes... x 2
@@ -91,7 +97,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
               int64_t num_tiles, int32_t* status, LnFusion ln) {
     using L = Smem<BN, NSUB, CG>;
-    constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC;
+    constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC, KP = L::KP;
+    constexpr int A_STAGE_BYTES = L::A_STAGE_BYTES;
     constexpr int BNT = BN * NSUB;                              // outputs per CTA tile
     constexpr int IB = (MODE == CHEBYKAN_MODE_BF16) ? 64 : 32;  // inputs per K block
     constexpr int CH = (MODE == CHEBYKAN_MODE_BF16) ? 8 : 4;    // elements per 16-byte chunk
@@ -167,10 +174,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         float tt[4][CH], ta[4][CH], tb[4][CH];
         uint32_t inc[4];        // tf32 rounding increment per row: 0 where the row's inputs of this block hold a NaN
         int s = 0; uint32_t ph = 0;
+        int kpos = 0;           // K block inside the current stage
+        int kb_left = 0;        // K blocks of the current tile not yet emitted
         uint32_t xph = 0;
         bool alive = true;
 
-        // pack one stage's values, wait for the slot, store, publish
+        // pack one K block's values, wait for the stage (at its first K block), store, publish (at its last)
         auto emit = [&](const float (&v)[4][CH]) -> bool {
             uint32_t w[4][4];
 #pragma unroll
@@ -187,12 +196,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                         w[j][q] = tf32_rna(v[j][q % CH], inc[j]);
                 }
             }
-            if (!mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) return false;
-            const uint32_t dst = smem_base + L::A_OFFSET + s * A_STAGE_BYTES + st_off;
+            if (kpos == 0 && !mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) return false;
+            const uint32_t dst = smem_base + L::A_OFFSET + s * A_STAGE_BYTES + kpos * A_PANEL_BYTES + st_off;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                              ::"r"(dst + j * 4096), "r"(w[j][0]), "r"(w[j][1]), "r"(w[j][2]), "r"(w[j][3]) : "memory");
+            --kb_left;
+            if (KP > 1 && kpos + 1 < KP && kb_left > 0) { ++kpos; return true; }   // the stage takes another K block
+            kpos = 0;
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
@@ -205,6 +217,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
         for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
             const int64_t m0 = (tile / n_tiles) * (BM * CG) + rank * BM;
+            kb_left = nkb;
             // fused LayerNorm of the input rows: per-row mean and 1/std from the previous layer's sums
             float ln_mean[4], ln_rstd[4];
             if (LN && ln.stats_in != nullptr) {
@@ -330,19 +343,23 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             bool alive = true;
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 const int n0 = (int)(tile % n_tiles) * BNT;
-                for (int kb = 0; kb < nkb && alive; ++kb) {
+                for (int kb = 0; kb < nkb && alive; kb += KP) {
+                    const int np = (nkb - kb < KP) ? nkb - kb : KP;     // K blocks in this stage
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub) {
                         if (!mbar_wait(emptyB(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
+                        const uint32_t dst = smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES;
                         if (CG == 2) {
                             // both halves count on the even CTA's barrier, which expects the whole tile
-                            if (rank == 0) mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES * 2);
-                            tma_load_2d_pair(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
-                                             n0 + sub * BN + (int)rank * (BN / 2), mapa_cluster(fullB(s), 0));
+                            if (rank == 0) mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * L::B_PANEL_BYTES * 2));
+                            const uint32_t bar0 = mapa_cluster(fullB(s), 0);
+                            for (int p = 0; p < np; ++p)
+                                tma_load_2d_pair(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p) * IB,
+                                                 n0 + sub * BN + (int)rank * (BN / 2), bar0);
                         } else {
-                            mbar_arrive_expect_tx(fullB(s), L::B_STAGE_BYTES);
-                            tma_load_2d(smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES, &tmap_w, kb * IB,
-                                        n0 + sub * BN, fullB(s));
+                            mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * L::B_PANEL_BYTES));
+                            for (int p = 0; p < np; ++p)
+                                tma_load_2d(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, n0 + sub * BN, fullB(s));
                         }
                         if (++s == NSB) { s = 0; ph ^= 1u; }
                     }
@@ -393,20 +410,27 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BNT);
-                for (int kb = 0; kb < nkb && alive; ++kb) {
+                for (int kb = 0; kb < nkb && alive; kb += KP) {
+                    const int np = (nkb - kb < KP) ? nkb - kb : KP;     // K blocks in this stage
                     if (!mbar_wait(fullA(sa), pha, abort_flag, status, ST_MMA_A)) { alive = false; break; }
-                    const uint64_t a_desc = make_smem_desc(smem_base + L::A_OFFSET + sa * A_STAGE_BYTES);
+                    const uint32_t a_addr = smem_base + L::A_OFFSET + sa * A_STAGE_BYTES;
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub) {
                         if (!mbar_wait(fullB(sb), phb, abort_flag, status, ST_MMA_B)) { alive = false; break; }
                         tc_fence_after();
-                        const uint64_t b_desc = make_smem_desc(smem_base + L::B_OFFSET + sb * L::B_STAGE_BYTES);
+                        const uint32_t b_addr = smem_base + L::B_OFFSET + sb * L::B_STAGE_BYTES;
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
-                            if (CG == 2) umma2<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                     (uint32_t)((kb | k) != 0));
-                            else umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                            (uint32_t)((kb | k) != 0));
+                        for (int p = 0; p < KP; ++p) {
+                            if (p >= np) break;
+                            const uint64_t a_desc = make_smem_desc(a_addr + p * A_PANEL_BYTES);
+                            const uint64_t b_desc = make_smem_desc(b_addr + p * L::B_PANEL_BYTES);
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
+                                if (CG == 2) umma2<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                         (uint32_t)((kb | p | k) != 0));
+                                else umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
+                                                (uint32_t)((kb | p | k) != 0));
+                            }
                         }
                         if (CG == 2) umma2_commit_both(emptyB(sb)); else umma_commit(emptyB(sb));
                         if (++sb == NSB) { sb = 0; phb ^= 1u; }
@@ -554,7 +578,7 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
         }
         attr_set[dev] = true;
     }
-    const int n_tiles = (int)ceil_div(n_pad, BN * NSUB);
+    const int n_tiles = (int)ceil_div(out, BN * NSUB);      // n_pad is out rounded up to a divisor of the tile
     const int64_t num_tiles = ceil_div(B, BM * CG) * n_tiles;
     const unsigned units = (unsigned)(num_tiles < max_units[dev] ? num_tiles : max_units[dev]);
     cudaLaunchConfig_t cfg = {};
@@ -579,6 +603,7 @@ int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma
 template <int MODE>
 int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, int cg, const float* x, float* y,
                 int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+    if (bn == 64) return launch_one<MODE, 64, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
     if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
@@ -596,6 +621,7 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     int bn = 128, nsub = 1;
     int cg = 1;
     if (p.n_pad >= 384) { bn = 256; nsub = 2; cg = (B > BM) ? 2 : 1; }
+    else if (out <= 64) { bn = 64; }     // smallest tile that holds the outputs: smaller W panels, more K blocks per stage
     else if (p.n_pad == 256) { bn = 256; }
     CUtensorMap tmap;
     const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
