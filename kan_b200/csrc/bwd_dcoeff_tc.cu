@@ -226,26 +226,28 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     }
                     const uint32_t inc = finite ? TF32_HALF_ULP : 0u;
                     // one 16-byte chunk (4 batch rows) per degree; ta / tb alternate as the newest value
-                    auto store4 = [&](int row, const float (&v)[4]) {
+                    // Slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart): its chunk c sits
+                    // at lin = a_stage + row * 128 + c * 16 with the 16-byte chunk index XORed by row % 8, and
+                    // since a_stage is 1024-byte aligned, row % 8 is bits 7-9 of lin itself.
+                    uint32_t lin = a_stage + (uint32_t)(ii * dp1) * 128u + ((uint32_t)c << 4);
+                    auto store4 = [&](const float (&v)[4]) {
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) w[e] = tf32_rna(v[e], inc);
-                        // slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart)
-                        const uint32_t dsta = a_stage + row * 128 + ((c ^ (row & 7)) << 4);
+                        const uint32_t dsta = lin ^ ((lin >> 3) & 0x70u);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                      ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+                        lin += 128u;
                     };
-                    int row = ii * dp1;
-                    store4(row, ta);                                   // degree 0
-                    ++row;
-                    for (int d = 1; d < dp1; d += 2, row += 2) {
+                    store4(ta);                                        // degree 0
+                    for (int d = 1; d < dp1; d += 2) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
-                        store4(row, tb);
+                        store4(tb);
                         if (d + 1 < dp1) {
 #pragma unroll
                             for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
-                            store4(row + 1, ta);
+                            store4(ta);
                         }
                     }
                 }

@@ -51,6 +51,25 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t (&r)[8]) {
                  : "r"(taddr) : "memory");
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld2(uint32_t taddr, uint32_t (&r)[2]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x2.b32 {%0, %1}, [%2];"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t& r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+}
+
 // Wd[(i,d)][out_pad] <- tf32(d * C[i][o][d]); columns o >= out are zero.  The degree factor of
 // T_d' = d U_{d-1} is folded in here so that the epilogue only needs U_{d-1} * G per value.
 __global__ void __launch_bounds__(256)
@@ -215,36 +234,44 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 // give the d = 0 column (whose coefficients are 0 * C) weight zero without a branch
                 float ua = 0.f, ub = -1.f, sum = 0.f;
                 const uint32_t col0 = taddr + (uint32_t)(ii * dp1);
+                // two columns: sum += U_{d-1} G_d, advance U, twice (ua / ub swap roles)
+                auto fold2 = [&](uint32_t g0, uint32_t g1) {
+                    sum = fmaf(ua, __uint_as_float(g0), sum);
+                    ub = fmaf(t2, ua, -ub);
+                    sum = fmaf(ub, __uint_as_float(g1), sum);
+                    ua = fmaf(t2, ub, -ua);
+                };
                 int c = 0;
-                for (; c + 8 <= dp1; c += 8) {
-                    uint32_t r[8];
-                    tmem_ld8(col0 + c, r);
+                for (; c + 32 <= dp1; c += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(col0 + c, r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 8; e += 2) {
-                        sum = fmaf(ua, __uint_as_float(r[e]), sum);
-                        ub = fmaf(t2, ua, -ub);
-                        sum = fmaf(ub, __uint_as_float(r[e + 1]), sum);
-                        ua = fmaf(t2, ub, -ua);
-                    }
+                    for (int e = 0; e < 32; e += 2) fold2(r[e], r[e + 1]);
                 }
-                if (c < dp1) {
-                    // last, partial group of 8 columns; the read is shifted left where it would reach
-                    // past the 256 columns of this accumulator buffer
-                    const int over = ii * dp1 + c + 8 - DX_BN;
-                    const int shift = over > 0 ? over : 0;
-                    uint32_t r[8];
-                    tmem_ld8(col0 + c - shift, r);
+                // the last 1-31 columns: one load of 16, 8, 4, 2 and 1 columns each as the count's bits say
+                // (all issued before a single wait), so no lane touches a column of the next input
+                const int rem = dp1 - c;
+                if (rem > 0) {
+                    uint32_t r16[16], r8[8], r4[4], r2[2], r1 = 0u;
+                    int cc = c;
+                    if (rem & 16) { tmem_ld16(col0 + cc, r16); cc += 16; }
+                    if (rem & 8) { tmem_ld8(col0 + cc, r8); cc += 8; }
+                    if (rem & 4) { tmem_ld4(col0 + cc, r4); cc += 4; }
+                    if (rem & 2) { tmem_ld2(col0 + cc, r2); cc += 2; }
+                    if (rem & 1) tmem_ld1(col0 + cc, r1);
                     tmem_ld_wait();
+                    if (rem & 16) {
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        const int d = c - shift + e;
-                        if (d >= c && d < dp1) {
-                            sum = fmaf(ua, __uint_as_float(r[e]), sum);
-                            const float u = fmaf(t2, ua, -ub);
-                            ub = ua; ua = u;
-                        }
+                        for (int e = 0; e < 16; e += 2) fold2(r16[e], r16[e + 1]);
                     }
+                    if (rem & 8) {
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) fold2(r8[e], r8[e + 1]);
+                    }
+                    if (rem & 4) { fold2(r4[0], r4[1]); fold2(r4[2], r4[3]); }
+                    if (rem & 2) fold2(r2[0], r2[1]);
+                    if (rem & 1) sum = fmaf(ua, __uint_as_float(r1), sum);
                 }
                 if (row_ok) dxrow[ii] = fmaf(-t, t, 1.f) * sum;
             }
