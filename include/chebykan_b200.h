@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 2
+#define CHEBYKAN_ABI_VERSION 3
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -214,6 +214,27 @@ int chebykan_fwd_host(const float* x_host, const float* coeffs_host,
                       float* y_host, void* device_scratch,
                       int64_t scratch_bytes, int64_t B, int64_t in,
                       int64_t out, int64_t deg, int mode, void* stream);
+
+/*
+ * Forward with HOST x and y and device-resident packed coefficients,
+ * pipelined: the batch is cut into blocks of chunk_rows rows; block k+1 is
+ * copied to the device while block k is computed and block k-1 is copied
+ * back, on two copy streams the library creates per device at first use, so
+ * both directions of the host link work at the same time.  x_host and y_host
+ * should be page-locked (the copies are synchronous otherwise).  Synchronous:
+ * returns once y_host is complete.  The caller lends device scratch of at
+ * least chebykan_fwd_host_packed_scratch_bytes(chunk_rows, in, out) bytes
+ * (two x blocks, two y blocks, a status word).  Calls that overlap on one
+ * device serialise on the library's copy streams.  Same replaced reference
+ * lines as chebykan_fwd.
+ */
+int64_t chebykan_fwd_host_packed_scratch_bytes(int64_t chunk_rows, int64_t in,
+                                               int64_t out);
+int chebykan_fwd_host_packed(const float* x_host, const void* packed,
+                             float* y_host, void* device_scratch,
+                             int64_t scratch_bytes, int64_t B, int64_t in,
+                             int64_t out, int64_t deg, int mode,
+                             int64_t chunk_rows, void* stream);
 
 #ifdef __cplusplus
 }

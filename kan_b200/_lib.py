@@ -45,6 +45,9 @@ SIGNATURES = {
     "chebykan_fwd_host_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "chebykan_fwd_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                   c_int64, c_int64, c_int, c_void_p]),
+    "chebykan_fwd_host_packed_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64]),
+    "chebykan_fwd_host_packed": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                         c_int64, c_int64, c_int, c_int64, c_void_p]),
 }
 
 _lib = None
@@ -64,7 +67,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 2:
+    if lib.chebykan_abi_version() != 3:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -1,5 +1,6 @@
 // C ABI of the library: argument validation and dispatch to the kernels.
 #include <math.h>
+#include <mutex>
 #include "common.cuh"
 
 namespace chebykan {
@@ -249,6 +250,97 @@ int chebykan_fwd_host(const float* x_host, const float* coeffs_host, float* y_ho
     int32_t st_host = 0;
     if ((rc = check_cuda(cudaMemcpyAsync(&st_host, st, 4, cudaMemcpyDeviceToHost, s)))) return rc;
     if ((rc = check_cuda(cudaStreamSynchronize(s)))) return rc;
+    return st_host ? CHEBYKAN_ETIMEOUT : CHEBYKAN_OK;
+}
+
+// ---- pipelined host-buffer forward ----------------------------------------------------
+namespace {
+struct HostPipe {
+    bool ready = false;
+    cudaStream_t s_in = nullptr, s_out = nullptr;
+    cudaEvent_t e_start = nullptr, e_in[2] = {}, e_cmp[2] = {}, e_free_x[2] = {}, e_free_y[2] = {};
+};
+HostPipe g_pipes[64];
+std::mutex g_pipe_mutex;
+
+int pipe_for_device(int dev, HostPipe** out) {
+    if (dev < 0 || dev >= 64) return CHEBYKAN_EINVAL;
+    HostPipe& p = g_pipes[dev];
+    if (!p.ready) {
+        int rc;
+        if ((rc = check_cuda(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking)))) return rc;
+        if ((rc = check_cuda(cudaStreamCreateWithFlags(&p.s_out, cudaStreamNonBlocking)))) return rc;
+        cudaEvent_t* evs[] = {&p.e_start, &p.e_in[0], &p.e_in[1], &p.e_cmp[0], &p.e_cmp[1],
+                              &p.e_free_x[0], &p.e_free_x[1], &p.e_free_y[0], &p.e_free_y[1]};
+        for (cudaEvent_t* e : evs)
+            if ((rc = check_cuda(cudaEventCreateWithFlags(e, cudaEventDisableTiming)))) return rc;
+        p.ready = true;
+    }
+    *out = &p;
+    return CHEBYKAN_OK;
+}
+}  // namespace
+
+int64_t chebykan_fwd_host_packed_scratch_bytes(int64_t chunk_rows, int64_t in, int64_t out) {
+    if (chunk_rows <= 0 || in <= 0 || out <= 0) return CHEBYKAN_EINVAL;
+    return 2 * a256(chunk_rows * in * 4) + 2 * a256(chunk_rows * out * 4) + 256;
+}
+
+int chebykan_fwd_host_packed(const float* x_host, const void* packed, float* y_host, void* device_scratch,
+                             int64_t scratch_bytes, int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
+                             int64_t chunk_rows, void* stream) {
+    if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !packed || !device_scratch || chunk_rows <= 0)
+        return CHEBYKAN_EINVAL;
+    if (B == 0) return CHEBYKAN_OK;
+    if (!x_host || !y_host) return CHEBYKAN_EINVAL;
+    if (!aligned16(device_scratch) || !aligned16(packed)) return CHEBYKAN_EALIGN;
+    if (chunk_rows > B) chunk_rows = B;
+    if (scratch_bytes < chebykan_fwd_host_packed_scratch_bytes(chunk_rows, in, out)) return CHEBYKAN_EWORKSPACE;
+    int rc = check_device();
+    if (rc) return rc;
+    int dev = 0;
+    if ((rc = check_cuda(cudaGetDevice(&dev)))) return rc;
+    std::lock_guard<std::mutex> lock(g_pipe_mutex);
+    HostPipe* p = nullptr;
+    if ((rc = pipe_for_device(dev, &p))) return rc;
+
+    cudaStream_t cur = (cudaStream_t)stream;
+    char* base = reinterpret_cast<char*>(device_scratch);
+    float* xd[2]; float* yd[2];
+    for (int k = 0; k < 2; ++k) { xd[k] = reinterpret_cast<float*>(base); base += a256(chunk_rows * in * 4); }
+    for (int k = 0; k < 2; ++k) { yd[k] = reinterpret_cast<float*>(base); base += a256(chunk_rows * out * 4); }
+    int32_t* st = reinterpret_cast<int32_t*>(base);
+
+#define CK(call) do { if ((rc = check_cuda(call))) return rc; } while (0)
+    CK(cudaMemsetAsync(st, 0, 4, cur));
+    // the copy streams start after whatever the caller has queued on its stream (the packed coefficients, say)
+    CK(cudaEventRecord(p->e_start, cur));
+    CK(cudaStreamWaitEvent(p->s_in, p->e_start, 0));
+    CK(cudaStreamWaitEvent(p->s_out, p->e_start, 0));
+    const int64_t n_chunks = ceil_div(B, chunk_rows);
+    for (int64_t k = 0; k < n_chunks; ++k) {
+        const int64_t b = k * chunk_rows;
+        const int64_t rows = (B - b < chunk_rows) ? B - b : chunk_rows;
+        const int slot = (int)(k & 1);
+        if (k >= 2) CK(cudaStreamWaitEvent(p->s_in, p->e_free_x[slot], 0));    // block k-2 has been computed from this buffer
+        CK(cudaMemcpyAsync(xd[slot], x_host + b * in, rows * in * 4, cudaMemcpyHostToDevice, p->s_in));
+        CK(cudaEventRecord(p->e_in[slot], p->s_in));
+        CK(cudaStreamWaitEvent(cur, p->e_in[slot], 0));
+        if (k >= 2) CK(cudaStreamWaitEvent(cur, p->e_free_y[slot], 0));        // block k-2 has been copied back from this buffer
+        if ((rc = chebykan_fwd(xd[slot], packed, yd[slot], rows, in, out, deg, mode, st, stream))) return rc;
+        CK(cudaEventRecord(p->e_cmp[slot], cur));
+        CK(cudaEventRecord(p->e_free_x[slot], cur));
+        CK(cudaStreamWaitEvent(p->s_out, p->e_cmp[slot], 0));
+        CK(cudaMemcpyAsync(y_host + b * out, yd[slot], rows * out * 4, cudaMemcpyDeviceToHost, p->s_out));
+        CK(cudaEventRecord(p->e_free_y[slot], p->s_out));
+    }
+    // the caller's stream ends after the last copy back
+    CK(cudaStreamWaitEvent(cur, p->e_free_y[(n_chunks - 1) & 1], 0));
+    if (n_chunks >= 2) CK(cudaStreamWaitEvent(cur, p->e_free_y[(n_chunks - 2) & 1], 0));
+    int32_t st_host = 0;
+    CK(cudaMemcpyAsync(&st_host, st, 4, cudaMemcpyDeviceToHost, cur));
+    CK(cudaStreamSynchronize(cur));
+#undef CK
     return st_host ? CHEBYKAN_ETIMEOUT : CHEBYKAN_OK;
 }
 

@@ -185,58 +185,24 @@ def make_chebykan_layer_class(base_cls, basis_cls, name: str = "ChebyKANLayer"):
             """Inference with HOST tensors in and out, copies overlapped with compute.
 
             The batch is cut into blocks of `chunk_rows` rows; block k+1 is copied to the GPU
-            while block k is computed and block k-1 is copied back, on three streams, so the
-            two directions of the PCIe link work at the same time.  `x_host` and `out` should
-            be pinned (the copies are synchronous otherwise); returns `out` ([rows, output_dim],
-            pinned if it had to be allocated) after all work has finished.
+            while block k is computed and block k-1 is copied back (the library's two copy
+            streams plus the current stream), so the two directions of the PCIe link work at the
+            same time.  `x_host` and `out` should be pinned (the copies are synchronous otherwise);
+            returns `out` ([rows, output_dim], pinned if it had to be allocated) after all work
+            has finished.
             """
             if x_host.is_cuda:
                 raise RuntimeError("forward_host takes a host tensor; call the layer itself for CUDA tensors")
             if x_host.dtype != torch.float32:
                 raise RuntimeError(f"expected scalar type Float but found {str(x_host.dtype).replace('torch.', '').capitalize()}")
-            x_host = x_host.view(-1, self.input_dim)
             dev = self.cheby_coeffs.device
             if dev.type != "cuda":
                 raise RuntimeError("move the layer to a CUDA device first")
-            B = x_host.shape[0]
-            if out is None:
-                out = torch.empty(B, self.output_dim, dtype=torch.float32, pin_memory=True)
             packed = self._packed.get(self.cheby_coeffs, self.math_mode)
-            st = self.__dict__.setdefault("_host_pipe", None)
-            rows = max(128, min(int(chunk_rows), max(B, 1)))
-            if st is None or st["rows"] != rows or st["dev"] != dev:
-                st = {"rows": rows, "dev": dev,
-                      "xd": [torch.empty(rows, self.input_dim, device=dev) for _ in range(2)],
-                      "yd": [torch.empty(rows, self.output_dim, device=dev) for _ in range(2)],
-                      "s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
-                      "e_in": [torch.cuda.Event() for _ in range(2)], "e_cmp": [torch.cuda.Event() for _ in range(2)],
-                      "e_free_x": [torch.cuda.Event() for _ in range(2)], "e_free_y": [torch.cuda.Event() for _ in range(2)]}
-                self.__dict__["_host_pipe"] = st
-            cur = torch.cuda.current_stream(dev)
-            st["s_in"].wait_stream(cur)
-            st["s_out"].wait_stream(cur)
-            n_chunks = (B + rows - 1) // rows
-            for k in range(n_chunks):
-                b, e = k * rows, min(B, (k + 1) * rows)
-                slot = k & 1
-                with torch.cuda.stream(st["s_in"]):
-                    if k >= 2:
-                        st["s_in"].wait_event(st["e_free_x"][slot])     # compute of block k-2 has read this buffer
-                    st["xd"][slot][: e - b].copy_(x_host[b:e], non_blocking=True)
-                    st["e_in"][slot].record(st["s_in"])
-                cur.wait_event(st["e_in"][slot])
-                if k >= 2:
-                    cur.wait_event(st["e_free_y"][slot])                # copy-back of block k-2 has drained this buffer
-                ops.forward(st["xd"][slot][: e - b], packed, self.input_dim, self.output_dim, self.degree,
-                            self.math_mode, out=st["yd"][slot][: e - b])
-                st["e_cmp"][slot].record(cur)
-                st["e_free_x"][slot].record(cur)
-                with torch.cuda.stream(st["s_out"]):
-                    st["s_out"].wait_event(st["e_cmp"][slot])
-                    out[b:e].copy_(st["yd"][slot][: e - b], non_blocking=True)
-                    st["e_free_y"][slot].record(st["s_out"])
-            cur.wait_stream(st["s_out"])
-            cur.synchronize()
+            out, scratch = ops.forward_host_packed(x_host, packed, self.input_dim, self.output_dim, self.degree,
+                                                   self.math_mode, out=out, chunk_rows=chunk_rows,
+                                                   scratch=self.__dict__.get("_host_scratch"))
+            self.__dict__["_host_scratch"] = scratch
             return out
 
         @torch.no_grad()

@@ -275,3 +275,35 @@ def forward_host(x_host: torch.Tensor, coeffs_host: torch.Tensor, mode, scratch:
                                    torch.cuda.current_stream(scratch.device).cuda_stream)
     _lib.check(rc, "chebykan_fwd_host")
     return out, scratch
+
+
+def forward_host_packed(x_host: torch.Tensor, packed: torch.Tensor, n_in: int, n_out: int, degree: int, mode,
+                        out: torch.Tensor | None = None, chunk_rows: int = 8192,
+                        scratch: torch.Tensor | None = None):
+    """Pipelined forward with HOST x / y and device-resident packed coefficients (chebykan_fwd_host_packed):
+    blocks of `chunk_rows` rows are copied in, computed and copied back concurrently.  Returns (y_host, scratch);
+    `scratch` is a reusable device byte buffer.  Synchronous."""
+    if x_host.is_cuda:
+        raise RuntimeError("forward_host_packed takes a host tensor")
+    if x_host.dtype != torch.float32:
+        raise RuntimeError("expected scalar type Float")
+    if not packed.is_cuda:
+        raise RuntimeError("packed coefficients must live on the GPU")
+    x2 = x_host.view(-1, n_in)
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    B = x2.shape[0]
+    rows = max(1, min(int(chunk_rows), max(B, 1)))
+    lib = _lib.load()
+    need = lib.chebykan_fwd_host_packed_scratch_bytes(rows, n_in, n_out)
+    _lib.check(need, "chebykan_fwd_host_packed_scratch_bytes")
+    if scratch is None or scratch.numel() < need or scratch.device != packed.device:
+        scratch = torch.empty(need, dtype=torch.uint8, device=packed.device)
+    if out is None:
+        out = torch.empty(B, n_out, dtype=torch.float32, pin_memory=True)
+    with torch.cuda.device(packed.device):
+        rc = lib.chebykan_fwd_host_packed(x2.data_ptr(), packed.data_ptr(), out.data_ptr(), scratch.data_ptr(),
+                                          scratch.numel(), B, n_in, n_out, degree, _mode(mode), rows,
+                                          torch.cuda.current_stream(packed.device).cuda_stream)
+    _lib.check(rc, "chebykan_fwd_host_packed")
+    return out, scratch
