@@ -268,6 +268,17 @@ def test_forward_host_pipelined(mode, tol):
     assert o.rel_l2(y, o.forward(x, c.bfloat16().float() if mode == "bf16" else c)) <= tol
     out = torch.empty(5000, 72).pin_memory()
     assert layer.forward_host(x, out=out, chunk_rows=100000) is out and torch.equal(out, y)
+    # pageable (not pinned) host memory and a block size that does not divide anything: still the same bits
+    xp = x[:777].clone()
+    assert not xp.is_pinned()
+    assert torch.equal(layer.forward_host(xp, out=torch.empty(777, 72), chunk_rows=250), y[:777])
+    # the C entry point refuses scratch that is too small instead of writing past it
+    lib = kan_b200._lib.load()
+    packed = ops.pack_coeffs(layer.cheby_coeffs.detach(), mode)
+    small = torch.empty(1024, dtype=torch.uint8, device="cuda")
+    rc = lib.chebykan_fwd_host_packed(x.data_ptr(), packed.data_ptr(), out.data_ptr(), small.data_ptr(), small.numel(),
+                                      5000, 96, 72, 5, ops.MODES[mode], 1024, torch.cuda.current_stream().cuda_stream)
+    assert rc == -6                    # CHEBYKAN_EWORKSPACE
     with pytest.raises(RuntimeError):
         layer.forward_host(x.cuda())
     ops.check_status()
