@@ -240,7 +240,21 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                         lin += 128u;
                     };
                     store4(ta);                                        // degree 0
-                    for (int d = 1; d < dp1; d += 2) {
+                    int d = 1;
+                    // eight degrees per trip: the loop's branches, not its arithmetic, were what the
+                    // producers waited on
+                    for (; d + 7 < dp1; d += 8) {
+#pragma unroll
+                        for (int h = 0; h < 4; ++h) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
+                            store4(tb);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
+                            store4(ta);
+                        }
+                    }
+                    for (; d < dp1; d += 2) {
 #pragma unroll
                         for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
                         store4(tb);
