@@ -250,6 +250,8 @@ def run_ours(args):
         achieved = flops / (ms_step * 1e-3) / 1e12
         if mode == "fp32":
             peak, peak_note = 148 * 128 * 2 * 1.965e9 / 1e12, "nominal FFMA peak (148 SM x 128 lanes x 2 x 1.965 GHz)"
+        elif mode == "fp32x3" and args.op == "fwd":
+            peak, peak_note = peaks["bf16_tflops"] / 6, f"a sixth of the {peaks['source']} bf16 burst peak (three tf32 products per multiply)"
         elif mode == "tf32":
             peak, peak_note = peaks["bf16_tflops"] / 2, f"half of the {peaks['source']} bf16 burst peak"
         else:
@@ -258,7 +260,7 @@ def run_ours(args):
             "metric": METRIC if args.op == "fwd" else f"chebykan_layer_{args.op}_samples_per_s", "value": value,
             "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode],
+            "vs_baseline": None, "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32", "fp32x3": "tf32x3"}[mode],
             "data": "synthetic",
             "config": dict(CFG if not args.shape else {"workload": f"layer {args.op}, shape {args.shape}"},
                            batch_per_gpu=B, input_dim=n_in, output_dim=n_out, degree=deg, op=args.op,
@@ -384,7 +386,7 @@ def run_model_config(args):
     else:
         for p in model.parameters():
             p.requires_grad_(False)
-        runner = kan_b200.fuse_layernorm(model) if (args.fuse_ln and mode != "fp32") else model
+        runner = kan_b200.fuse_layernorm(model) if (args.fuse_ln and mode not in ("fp32", "fp32x3")) else model
 
         def step():
             with torch.no_grad():
@@ -429,11 +431,11 @@ def run_model_config(args):
             "metric": "chebykan_%s_samples_per_s" % ("train_step" if train else "stack_fwd"), "value": value,
             "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
             "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32"}[mode], "data": "synthetic",
+            "dtype": {"bf16": "bf16", "tf32": "tf32", "fp32": "f32", "fp32x3": "tf32x3"}[mode], "data": "synthetic",
             "config": {"workload": f"{cfg.name}: layers {list(cfg.layers)}, batch {B} per GPU, "
                                    f"{'fwd+bwd+' + cfg.optimizer if train else 'forward'}",
                        "global_batch": world * B, "math_mode": mode, "cuda_graph": bool(args.graph and train),
-                       "layernorm_fused": bool(args.fuse_ln and not train and mode != "fp32"),
+                       "layernorm_fused": bool(args.fuse_ln and not train and mode not in ("fp32", "fp32x3")),
                        "parallelism": f"dp{world}" + (" (flat-buffer all-reduce of the gradients)" if train and world > 1 else "")},
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": None, "flops_per_step": flops},
@@ -450,7 +452,7 @@ def run_model_config(args):
 
 # DRAM bytes (read + write) of one forward launch taken from an ncu capture; None until one exists.
 # bf16/tf32/fp32: captured at 32768 rows (profiles/), x and y traffic doubled for the full 65536-row launch.
-TRAFFIC_BYTES = {"bf16": 583.3e6, "tf32": 759.7e6, "fp32": 592.4e6}
+TRAFFIC_BYTES = {"bf16": 583.3e6, "tf32": 759.7e6, "fp32": 592.4e6, "fp32x3": None}
 
 
 def main():
@@ -459,7 +461,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32", "fp32"])
+    ap.add_argument("--mode", default="bf16", choices=["bf16", "tf32", "fp32", "fp32x3"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--batch", type=int, default=0, help="rows per GPU (default: the configuration's batch)")

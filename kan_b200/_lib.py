@@ -13,8 +13,8 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_void_p
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libchebykan_b200.so")
 
-MODE_FP32, MODE_TF32, MODE_BF16 = 0, 1, 2
-MODES = {"fp32": MODE_FP32, "tf32": MODE_TF32, "bf16": MODE_BF16}
+MODE_FP32, MODE_TF32, MODE_BF16, MODE_FP32X3 = 0, 1, 2, 3
+MODES = {"fp32": MODE_FP32, "tf32": MODE_TF32, "bf16": MODE_BF16, "fp32x3": MODE_FP32X3}
 OP_FWD, OP_BWD_DCOEFF, OP_BWD_DX = 0, 1, 2
 
 # name -> (restype, argtypes); every symbol declared in include/chebykan_b200.h

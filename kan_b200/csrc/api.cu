@@ -41,7 +41,12 @@ static bool shape_ok(int64_t B, int64_t in, int64_t out, int64_t deg) {
            in * (deg + 1) <= (int64_t)1 << 24;
 }
 static bool mode_ok(int mode) {
-    return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16;
+    return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16 ||
+           mode == CHEBYKAN_MODE_FP32X3;
+}
+// modes whose backward kernels are the fp32 ones
+static bool fp32_backward(int mode) {
+    return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_FP32X3;
 }
 }  // namespace chebykan
 
@@ -71,7 +76,7 @@ int chebykan_last_cuda_error(void) { return g_last_cuda_error; }
 int64_t chebykan_packed_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
     if (!shape_ok(0, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
     const PackedDims p = packed_dims(in, out, deg, mode);
-    return p.k_pad * p.n_pad * p.elem;
+    return p.k_pad * p.n_pad * p.elem * p.planes;
 }
 
 int chebykan_pack_coeffs(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg,
@@ -89,7 +94,7 @@ int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int
         case CHEBYKAN_OP_FWD: return 0;
         case CHEBYKAN_OP_BWD_DCOEFF: return B == 0 ? 0 : dcoeff_workspace_bytes(B, in, out, deg, mode);
         case CHEBYKAN_OP_BWD_DX:
-            return (mode != CHEBYKAN_MODE_FP32 && dx_tc_supported(B, in, out, deg)) ? dx_tc_workspace_bytes(in, out, deg) : 0;
+            return (!fp32_backward(mode) && dx_tc_supported(B, in, out, deg)) ? dx_tc_workspace_bytes(in, out, deg) : 0;
         default: return CHEBYKAN_EINVAL;
     }
 }
@@ -113,7 +118,7 @@ int chebykan_fwd_ln(const float* x, const void* packed, float* y, int64_t B, int
                     int64_t deg, int mode, const float* ln_stats_in, const float* ln_gamma,
                     const float* ln_beta, float ln_eps, float* ln_stats_out, int32_t* status, void* stream) {
     if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !packed || !status) return CHEBYKAN_EINVAL;
-    if (mode == CHEBYKAN_MODE_FP32) return CHEBYKAN_EUNSUPPORTED;   // fusion lives in the tensor-core kernel
+    if (fp32_backward(mode)) return CHEBYKAN_EUNSUPPORTED;   // fusion lives in the bf16 / tf32 tensor-core kernels
     if (ln_stats_in && (!ln_gamma || !ln_beta)) return CHEBYKAN_EINVAL;
     if (B == 0) return CHEBYKAN_OK;
     if (!x || !y) return CHEBYKAN_EINVAL;
@@ -141,7 +146,7 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* w
     if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
     // tf32 and bf16 modes: tcgen05 kind::tf32 (bf16 operands would miss the 2e-3 tolerance for this
     // product); shapes it does not cover, and fp32 mode, accumulate in fp32 on the FFMA pipe
-    if (mode != CHEBYKAN_MODE_FP32 && dcoeff_tc_supported(B, in, out, deg)) {
+    if (!fp32_backward(mode) && dcoeff_tc_supported(B, in, out, deg)) {
         if (!status) return CHEBYKAN_EINVAL;
         return launch_dcoeff_tc(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate,
                                 status, s);
@@ -161,7 +166,7 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float*
     int rc = check_device();
     if (rc) return rc;
     // tf32 and bf16 modes: tcgen05 kind::tf32 with the coefficients repacked into the workspace
-    if (mode != CHEBYKAN_MODE_FP32 && dx_tc_supported(B, in, out, deg)) {
+    if (!fp32_backward(mode) && dx_tc_supported(B, in, out, deg)) {
         if (!status) return CHEBYKAN_EINVAL;
         return launch_dx_tc(x, dy, coeffs, dx, workspace, workspace_bytes, B, in, out, deg, status,
                             (cudaStream_t)stream);

@@ -31,6 +31,7 @@ struct PackedDims {
     int64_t n_pad;   // padded outputs
     int64_t elem;    // bytes per element
     bool    k_major; // true: [N_pad][K_pad]; false: [K_pad][N_pad]
+    int64_t planes;  // matrices stored back to back (FP32X3: tf32 head, then tf32 tail)
 };
 
 inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64_t deg, int mode) {
@@ -42,6 +43,7 @@ inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64
     } else {
         p.ib = TF32_IB; p.elem = 4; p.k_major = true; p.n_pad = round_up(out, TC_NPAD);
     }
+    p.planes = (mode == CHEBYKAN_MODE_FP32X3) ? 2 : 1;
     p.in_pad = round_up(in, p.ib);
     p.k_pad = p.in_pad * (deg + 1);
     return p;

@@ -64,19 +64,22 @@ constexpr int A_PANEL_BYTES = BM * 128;     // one K block of A: 128 rows x 128 
 enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6, ST_X_LOAD = 7,
        ST_X_WAIT = 8 };
 
-template <int BN, int NSUB, int CG = 1>
+// PP = 2: every K block is staged twice, as a tf32 head and a tf32 tail (the fp32-grade FP32X3 mode)
+template <int BN, int NSUB, int CG = 1, int PP = 1>
 struct Smem {
     // A ring depth / B ring depth (a CTA of a pair stages half of each W tile, which frees room for more A stages)
     // K blocks per stage.  On narrow layers (one tile of 128 or 64 outputs) an MMA is so small that the
     // hand-over of a stage (barrier waits, proxy fence, arrive, commit) costs more than its math: three
     // or four K blocks share one hand-over there, in rings of two stages.
-    static constexpr int KP = (BN == 128 && NSUB == 1) ? 3 : (BN == 64 ? 4 : 1);
-    static constexpr int NSA = (KP > 1) ? 2 : ((CG == 2) ? 8 : 4);
-    static constexpr int NSB = (KP > 1) ? 2 : ((CG == 2 || BN == 256) ? 4 : 8);
+    static constexpr int KP = (PP == 2) ? 1 : ((BN == 128 && NSUB == 1) ? 3 : (BN == 64 ? 4 : 1));
+    static constexpr int NSA = (PP == 2) ? ((BN == 256) ? (CG == 2 ? 3 : 2) : (BN == 128 ? 3 : 4))
+                                         : ((KP > 1) ? 2 : ((CG == 2) ? 8 : 4));
+    static constexpr int NSB = (PP == 2) ? ((BN == 256) ? (CG == 2 ? 3 : 2) : (BN == 128 ? 3 : 4))
+                                         : ((KP > 1) ? 2 : ((CG == 2 || BN == 256) ? 4 : 8));
     static constexpr int NACC = (NSUB * BN <= 256) ? 2 : 1;
     static constexpr int B_PANEL_BYTES = BN * 128 / CG;   // a CTA of a pair holds half of the tile's W rows
-    static constexpr int A_STAGE_BYTES = KP * A_PANEL_BYTES;
-    static constexpr int B_STAGE_BYTES = KP * B_PANEL_BYTES;
+    static constexpr int A_STAGE_BYTES = KP * PP * A_PANEL_BYTES;
+    static constexpr int B_STAGE_BYTES = KP * PP * B_PANEL_BYTES;
     static constexpr int A_OFFSET = 0;
     static constexpr int B_OFFSET = NSA * A_STAGE_BYTES;
     static constexpr int X_OFFSET = B_OFFSET + NSB * B_STAGE_BYTES;   // x tile: 128 rows x 128 bytes... x 2
@@ -95,8 +98,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
-              int64_t num_tiles, int32_t* status, LnFusion ln) {
-    using L = Smem<BN, NSUB, CG>;
+              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad) {
+    constexpr bool X3 = MODE == CHEBYKAN_MODE_FP32X3;
+    constexpr int PP = X3 ? 2 : 1;
+    using L = Smem<BN, NSUB, CG, PP>;
     constexpr int NSA = L::NSA, NSB = L::NSB, NACC = L::NACC, KP = L::KP;
     constexpr int A_STAGE_BYTES = L::A_STAGE_BYTES;
     constexpr int BNT = BN * NSUB;                              // outputs per CTA tile
@@ -130,6 +135,11 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const int64_t nunits = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
     const int n_iblk = (in + IB - 1) / IB;
     const int nkb = n_iblk * dp1;
+    // FP32X3: the tensor pipe's fp32 accumulation truncates, a bias that grows with the number of MMAs added
+    // into one accumulator (6e-5 after 3456 of them).  So an accumulator takes only X3_CHUNK K blocks (192 MMAs);
+    // the epilogue adds the chunks' partial sums into y with ordinary fp32 additions.
+    constexpr int X3_CHUNK = 16;
+    const int kb_chunk = X3 ? X3_CHUNK : nkb;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSA; ++s) { mbar_init(fullA(s), NUM_PRODUCER_WARPS * CG); mbar_init(emptyA(s), 1); }
@@ -182,9 +192,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         // pack one K block's values, wait for the stage (at its first K block), store, publish (at its last)
         auto emit = [&](const float (&v)[4][CH]) -> bool {
             uint32_t w[4][4];
+            uint32_t wl[X3 ? 4 : 1][4];       // tails (FP32X3)
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                if (MODE == CHEBYKAN_MODE_BF16) {
+                if (X3) {
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        // head = value truncated to tf32; tail = the rest, exact in fp32
+                        const uint32_t hi = __float_as_uint(v[j][q % CH]) & 0xFFFFE000u;
+                        w[j][q] = hi;
+                        wl[X3 ? j : 0][q] = __float_as_uint(v[j][q % CH] - __uint_as_float(hi));
+                    }
+                } else if (MODE == CHEBYKAN_MODE_BF16) {
 #pragma unroll
                     for (int q = 0; q < 4; ++q) {
                         const __nv_bfloat162 h = __floats2bfloat162_rn(v[j][(2 * q) % CH], v[j][(2 * q + 1) % CH]);
@@ -197,11 +216,18 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 }
             }
             if (kpos == 0 && !mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, ST_PRODUCER)) return false;
-            const uint32_t dst = smem_base + L::A_OFFSET + s * A_STAGE_BYTES + kpos * A_PANEL_BYTES + st_off;
+            const uint32_t dst = smem_base + L::A_OFFSET + s * A_STAGE_BYTES + kpos * (PP * A_PANEL_BYTES) + st_off;
 #pragma unroll
             for (int j = 0; j < 4; ++j)
                 asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                              ::"r"(dst + j * 4096), "r"(w[j][0]), "r"(w[j][1]), "r"(w[j][2]), "r"(w[j][3]) : "memory");
+            if (X3) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
+                                 ::"r"(dst + A_PANEL_BYTES + j * 4096), "r"(wl[X3 ? j : 0][0]), "r"(wl[X3 ? j : 0][1]),
+                                   "r"(wl[X3 ? j : 0][2]), "r"(wl[X3 ? j : 0][3]) : "memory");
+            }
             --kb_left;
             if (KP > 1 && kpos + 1 < KP && kb_left > 0) { ++kpos; return true; }   // the stage takes another K block
             kpos = 0;
@@ -301,7 +327,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     bool finite = true;
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
-                        const float t = tanh_fast(v[e]);
+                        const float t = X3 ? tanh_exact(v[e]) : tanh_fast(v[e]);
                         finite = finite && (t == t);
                         tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
@@ -351,15 +377,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                         const uint32_t dst = smem_base + L::B_OFFSET + s * L::B_STAGE_BYTES;
                         if (CG == 2) {
                             // both halves count on the even CTA's barrier, which expects the whole tile
-                            if (rank == 0) mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * L::B_PANEL_BYTES * 2));
+                            if (rank == 0) mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * PP * L::B_PANEL_BYTES * 2));
                             const uint32_t bar0 = mapa_cluster(fullB(s), 0);
-                            for (int p = 0; p < np; ++p)
-                                tma_load_2d_pair(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p) * IB,
-                                                 n0 + sub * BN + (int)rank * (BN / 2), bar0);
+                            for (int p = 0; p < np * PP; ++p)      // FP32X3: the tails' rows start at row n_pad
+                                tma_load_2d_pair(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p / PP) * IB,
+                                                 n0 + sub * BN + (int)rank * (BN / 2) + (p % PP) * n_pad, bar0);
                         } else {
-                            mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * L::B_PANEL_BYTES));
-                            for (int p = 0; p < np; ++p)
-                                tma_load_2d(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, n0 + sub * BN, fullB(s));
+                            mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * PP * L::B_PANEL_BYTES));
+                            for (int p = 0; p < np * PP; ++p)
+                                tma_load_2d(dst + p * L::B_PANEL_BYTES, &tmap_w, (kb + p / PP) * IB,
+                                            n0 + sub * BN + (p % PP) * n_pad, fullB(s));
                         }
                         if (++s == NSB) { s = 0; ph ^= 1u; }
                     }
@@ -407,11 +434,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+              for (int kb0 = 0; kb0 < nkb && alive; kb0 += kb_chunk) {     // one accumulator per chunk of K blocks
+                const int kb_end = (nkb - kb0 < kb_chunk) ? nkb : kb0 + kb_chunk;
                 if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BNT);
-                for (int kb = 0; kb < nkb && alive; kb += KP) {
-                    const int np = (nkb - kb < KP) ? nkb - kb : KP;     // K blocks in this stage
+                for (int kb = kb0; kb < kb_end && alive; kb += KP) {
+                    const int np = (kb_end - kb < KP) ? kb_end - kb : KP;     // K blocks in this stage
                     if (!mbar_wait(fullA(sa), pha, abort_flag, status, ST_MMA_A)) { alive = false; break; }
                     const uint32_t a_addr = smem_base + L::A_OFFSET + sa * A_STAGE_BYTES;
 #pragma unroll
@@ -422,14 +451,22 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 #pragma unroll
                         for (int p = 0; p < KP; ++p) {
                             if (p >= np) break;
-                            const uint64_t a_desc = make_smem_desc(a_addr + p * A_PANEL_BYTES);
-                            const uint64_t b_desc = make_smem_desc(b_addr + p * L::B_PANEL_BYTES);
+                            const uint64_t a_desc = make_smem_desc(a_addr + p * (PP * A_PANEL_BYTES));
+                            const uint64_t b_desc = make_smem_desc(b_addr + p * (PP * L::B_PANEL_BYTES));
+                            auto mma = [&](uint64_t ad, uint64_t bd, uint32_t accumulate) {
+                                if (CG == 2) umma2<MODE>(d_tmem + sub * BN, ad, bd, IDESC, accumulate);
+                                else umma<MODE>(d_tmem + sub * BN, ad, bd, IDESC, accumulate);
+                            };
 #pragma unroll
                             for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
-                                if (CG == 2) umma2<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                         (uint32_t)((kb | p | k) != 0));
-                                else umma<MODE>(d_tmem + sub * BN, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                (uint32_t)((kb | p | k) != 0));
+                                mma(a_desc + 2 * k, b_desc + 2 * k, (uint32_t)(((kb - kb0) | p | k) != 0));
+                                if (X3) {
+                                    // head x tail and tail x head (tail x tail is below fp32 rounding); descriptors
+                                    // address 16-byte units
+                                    const uint64_t a_lo = a_desc + (A_PANEL_BYTES >> 4), b_lo = b_desc + (L::B_PANEL_BYTES >> 4);
+                                    mma(a_desc + 2 * k, b_lo + 2 * k, 1u);
+                                    mma(a_lo + 2 * k, b_desc + 2 * k, 1u);
+                                }
                             }
                         }
                         if (CG == 2) umma2_commit_both(emptyB(sb)); else umma_commit(emptyB(sb));
@@ -440,6 +477,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 }
                 if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
+              }
             }
             if (!alive) {
                 // wait (bounded) until the MMAs already issued have retired
@@ -457,8 +495,28 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         const bool vec8 = (out & 7) == 0 && (reinterpret_cast<uintptr_t>(y) & 31u) == 0;
         // one row's 32 consecutive outputs from registers to y
         float ln_s1 = 0.f, ln_s2 = 0.f;    // this row's sum and sum of squares over the tile (fused LayerNorm)
-        auto store32 = [&](const uint32_t (&r)[32], int64_t row, int col0) {
+        auto store32 = [&](uint32_t (&r)[32], int64_t row, int col0, bool add) {
             if (row >= B) return;
+            if (X3 && add) {
+                // later chunk of the K range: y already holds the earlier chunks' sum
+                const float* src = y + row * out + col0;
+                if (vec4 && col0 + 32 <= out) {
+                    float4 p[8];
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) p[g] = *reinterpret_cast<const float4*>(src + 4 * g);
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        r[4 * g] = __float_as_uint(__uint_as_float(r[4 * g]) + p[g].x);
+                        r[4 * g + 1] = __float_as_uint(__uint_as_float(r[4 * g + 1]) + p[g].y);
+                        r[4 * g + 2] = __float_as_uint(__uint_as_float(r[4 * g + 2]) + p[g].z);
+                        r[4 * g + 3] = __float_as_uint(__uint_as_float(r[4 * g + 3]) + p[g].w);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (col0 + e < out) r[e] = __float_as_uint(__uint_as_float(r[e]) + src[e]);
+                }
+            }
             if (LN && ln.stats_out != nullptr) {
 #pragma unroll
                 for (int e = 0; e < 32; ++e)
@@ -496,6 +554,8 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             else mbar_arrive(acc_empty_bar(a));
         };
         for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+          for (int kb0 = 0; kb0 < nkb && alive; kb0 += kb_chunk) {
+            const bool add = kb0 > 0;
             const int64_t row = (tile / n_tiles) * (BM * CG) + rank * BM + q * 32 + lane;
             const int n0 = (int)(tile % n_tiles) * BNT;
             // tcgen05.ld is warp-collective: leave the loop only as a whole warp
@@ -515,12 +575,12 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 tmem_ld_wait();
                 if (ch + 1 < nchunks) tmem_ld32(taddr + (ch + 1) * 32, rb);
                 else { tc_fence_before(); arrive_acc_empty(acc); }   // accumulator fully read
-                store32(ra, row, n0 + ch * 32);
+                store32(ra, row, n0 + ch * 32, add);
                 if (ch + 1 < nchunks) {
                     tmem_ld_wait();
                     if (ch + 2 < nchunks) tmem_ld32(taddr + (ch + 2) * 32, ra);
                     else { tc_fence_before(); arrive_acc_empty(acc); }
-                    store32(rb, row, n0 + (ch + 1) * 32);
+                    store32(rb, row, n0 + (ch + 1) * 32, add);
                 }
             }
             if (LN && ln.stats_out != nullptr) {
@@ -531,6 +591,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 ln_s1 = 0.f; ln_s2 = 0.f;
             }
             if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
+          }
         }
     }
 
@@ -550,7 +611,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 template <int MODE, int BN, int NSUB, bool LN, int CG>
 int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
-    using L = Smem<BN, NSUB, CG>;
+    using L = Smem<BN, NSUB, CG, (MODE == CHEBYKAN_MODE_FP32X3) ? 2 : 1>;
     static bool attr_set[64] = {false};
     static int max_units[64] = {0};       // CTAs (or CTA pairs) that can be resident at once
     int dev = 0;
@@ -588,15 +649,17 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_tiles,
-                                         num_tiles, status, ln));
+                                         num_tiles, status, ln, n_pad));
 }
 
 // the LayerNorm-fused variant is a separate instantiation, so the plain kernel carries none of its registers
 template <int MODE, int BN, int NSUB, int CG = 1>
 int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
-    if (ln.stats_in != nullptr || ln.stats_out != nullptr)
-        return launch_one_ln<MODE, BN, NSUB, true, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    if constexpr (MODE != CHEBYKAN_MODE_FP32X3) {   // no LayerNorm fusion in the FP32X3 mode (the entry point refuses it)
+        if (ln.stats_in != nullptr || ln.stats_out != nullptr)
+            return launch_one_ln<MODE, BN, NSUB, true, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    }
     return launch_one_ln<MODE, BN, NSUB, false, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
 }
 
@@ -620,11 +683,12 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     // tile width: 2 x 256 outputs (all of TMEM) when there are that many, else 256 or 128
     int bn = 128, nsub = 1;
     int cg = 1;
-    if (p.n_pad >= 384) { bn = 256; nsub = 2; cg = (B > BM) ? 2 : 1; }
+    if (p.n_pad >= 384 && mode == CHEBYKAN_MODE_FP32X3) { bn = 256; }   // two accumulators: a chunk drains while the next one runs
+    else if (p.n_pad >= 384) { bn = 256; nsub = 2; cg = (B > BM) ? 2 : 1; }
     else if (out <= 64) { bn = 64; }     // smallest tile that holds the outputs: smaller W panels, more K blocks per stage
     else if (p.n_pad == 256) { bn = 256; }
     CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
+    const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)(p.n_pad * p.planes)};
     const cuuint64_t strides[1] = {(cuuint64_t)(p.k_pad * p.elem)};
     const cuuint32_t box[2] = {(cuuint32_t)p.ib, (cuuint32_t)(bn / cg)};
     const cuuint32_t estr[2] = {1, 1};
@@ -648,6 +712,9 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
         if (rx != CUDA_SUCCESS) { set_last_cuda_error((int)rx); return CHEBYKAN_ECUDA; }
     }
     const int dp1 = (int)deg + 1;
+    if (mode == CHEBYKAN_MODE_FP32X3)
+        return launch_mode<CHEBYKAN_MODE_FP32X3>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
+                                                 (int)p.n_pad, status, s, ln);
     if (mode == CHEBYKAN_MODE_BF16)
         return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
                                                (int)p.n_pad, status, s, ln);

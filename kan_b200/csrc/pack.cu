@@ -24,6 +24,12 @@ pack_kernel(const float* __restrict__ c, void* __restrict__ packed, int in, int 
         if (i < in && n < out) v = c[(i * out + n) * dp1 + d];
         if (MODE == CHEBYKAN_MODE_FP32) {
             reinterpret_cast<float*>(packed)[e] = v;
+        } else if (MODE == CHEBYKAN_MODE_FP32X3) {
+            // head = the value truncated to tf32, tail = what is left (exact in fp32; the tensor pipe
+            // reads its top 11 bits): head + tail carries 22 bits of the coefficient
+            const uint32_t hi = __float_as_uint(v) & 0xFFFFE000u;
+            reinterpret_cast<uint32_t*>(packed)[e] = hi;
+            reinterpret_cast<float*>(packed)[total + e] = v - __uint_as_float(hi);
         } else if (MODE == CHEBYKAN_MODE_TF32) {
             uint32_t r;
             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -43,6 +49,8 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
     const int dp1 = (int)deg + 1;
     if (mode == CHEBYKAN_MODE_FP32)
         pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+    else if (mode == CHEBYKAN_MODE_FP32X3)
+        pack_kernel<CHEBYKAN_MODE_FP32X3><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
     else if (mode == CHEBYKAN_MODE_TF32)
         pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
     else

@@ -36,7 +36,7 @@ class FusedChebyKANStack(nn.Module):
         a, b = m[k - 1], m[k + 1]
         if not (_is_cheby(a) and _is_cheby(b)):
             return False
-        if a.math_mode == "fp32" or b.math_mode == "fp32":
+        if a.math_mode in ("fp32", "fp32x3") or b.math_mode in ("fp32", "fp32x3"):
             return False
         return tuple(m[k].normalized_shape) == (a.output_dim,) and b.input_dim == a.output_dim
 

@@ -352,3 +352,43 @@ def test_tc_nan_input_propagates(mode):
     others = torch.ones(n_in, dtype=torch.bool)
     others[3] = False
     assert bool(torch.isfinite(dC[others]).all())
+
+
+X3_SHAPES = [
+    (256, 64, 128, 4, "normal"),          # one 128-wide tile
+    (4096, 1024, 1024, 8, "normal"),      # configuration 3 at reduced batch: CTA pairs, 512-column tiles
+    (2048, 512, 256, 4, "normal"),        # 256-wide tile, two accumulators
+    (8192, 64, 64, 32, "uniform3"),       # configuration 5 layer: 64-wide tile, degree 32
+    (100, 13, 7, 3, "normal"),            # in not a multiple of 4: scalar loads
+    (1000, 96, 300, 8, "normal"),         # ragged rows, padded outputs
+    (130, 64, 512, 3, "normal"),          # pair whose odd CTA holds 2 real rows
+    (128, 64, 512, 3, "normal"),          # single-CTA kernel on a wide layer
+    (129, 32, 256, 0, "normal"),          # degree 0
+]
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", X3_SHAPES)
+def test_fp32x3_forward_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
+    """'fp32x3': three tf32 tensor-core products of head/tail splits; same 1e-5 bound as the FFMA mode."""
+    x, coeffs, _ = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    y = run_fwd(x, coeffs, "fp32x3")
+    err = o.rel_l2(y, o.forward(x, coeffs))
+    assert err <= 1e-5, err
+
+
+def test_fp32x3_layer_trains_with_fp32_backward():
+    torch.manual_seed(5)
+    layer = kan_b200.ChebyKANLayer(96, 520, 6, math_mode="fp32x3").cuda()
+    x = torch.randn(700, 96, device="cuda", requires_grad=True)
+    y = layer(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    ops.check_status()
+    y_ref, dC_ref, dx_ref = o.forward_backward(x.detach().cpu(), layer.cheby_coeffs.detach().cpu(), dy.cpu())
+    assert o.rel_l2(y.detach().cpu(), y_ref) <= 1e-5
+    assert o.rel_l2(layer.cheby_coeffs.grad.cpu(), dC_ref) <= 1e-5
+    assert o.rel_l2(x.grad.cpu(), dx_ref) <= 1e-5
+    # LayerNorm fusion is a bf16 / tf32 feature: the C entry point refuses this mode
+    with pytest.raises(RuntimeError):
+        ops.forward_ln(x.detach(), ops.pack_coeffs(layer.cheby_coeffs.detach(), "fp32x3"), 96, 520, 6, "fp32x3",
+                       stats_out=torch.zeros(700, 2, device="cuda"))
