@@ -46,8 +46,8 @@ extern "C" {
 #define CHEBYKAN_MODE_BF16 2  /* tcgen05 kind::f16 (bf16 x bf16), fp32 accumulate  */
 /* fp32-grade forward on the tensor cores: basis values and coefficients are each
  * split into a tf32 head and a tf32 tail and three tcgen05 kind::tf32 products
- * (head*head, head*tail, tail*head) are accumulated in fp32, with the correctly
- * rounded tanh of the fp32 mode.  Same 1e-5 tolerance as CHEBYKAN_MODE_FP32; the
+ * (head*head, head*tail, tail*head) are accumulated in fp32, with the library's
+ * single-precision tanh (2 ulp).  Same 1e-5 tolerance as CHEBYKAN_MODE_FP32; the
  * backward entry points run their fp32 kernels in this mode. */
 #define CHEBYKAN_MODE_FP32X3 3
 

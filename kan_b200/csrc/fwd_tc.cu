@@ -327,7 +327,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     bool finite = true;
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
-                        const float t = X3 ? tanh_exact(v[e]) : tanh_fast(v[e]);
+                        const float t = X3 ? tanhf(v[e]) : tanh_fast(v[e]);
                         finite = finite && (t == t);
                         tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
