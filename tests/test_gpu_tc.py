@@ -392,3 +392,33 @@ def test_fp32x3_layer_trains_with_fp32_backward():
     with pytest.raises(RuntimeError):
         ops.forward_ln(x.detach(), ops.pack_coeffs(layer.cheby_coeffs.detach(), "fp32x3"), 96, 520, 6, "fp32x3",
                        stats_out=torch.zeros(700, 2, device="cuda"))
+
+
+def test_cta_pair_kernels_replay_from_a_cuda_graph():
+    """The wide-layer kernels are cluster launches; captured into a CUDA graph they replay with the same bits."""
+    x, coeffs, dy = make_case(600, 48, 520, 4, seed=123)
+    xd, cd, dyd = x.cuda(), coeffs.cuda(), dy.cuda()
+    packed = ops.pack_coeffs(cd, "bf16")
+    y_e = ops.forward(xd, packed, 48, 520, 4, "bf16")
+    dc_e = ops.bwd_dcoeff(xd, dyd, 48, 520, 4, "tf32")
+    dx_e = ops.bwd_dx(xd, dyd, cd, "tf32")
+    y_g, dc_g, dx_g = torch.empty_like(y_e), torch.empty_like(dc_e), torch.empty_like(dx_e)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):                      # warm-up on the capture stream (first-call attribute setup)
+        ops.forward(xd, packed, 48, 520, 4, "bf16", out=y_g)
+        ops.bwd_dcoeff(xd, dyd, 48, 520, 4, "tf32", out=dc_g)
+        ops.bwd_dx(xd, dyd, cd, "tf32", out=dx_g)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        ops.forward(xd, packed, 48, 520, 4, "bf16", out=y_g)
+        ops.bwd_dcoeff(xd, dyd, 48, 520, 4, "tf32", out=dc_g)
+        ops.bwd_dx(xd, dyd, cd, "tf32", out=dx_g)
+    for t in (y_g, dc_g, dx_g):
+        t.fill_(float("nan"))
+    g.replay()
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert torch.equal(y_g, y_e) and torch.equal(dc_g, dc_e) and torch.equal(dx_g, dx_e)
