@@ -451,8 +451,9 @@ def run_model_config(args):
 
 
 # DRAM bytes (read + write) of one forward launch taken from an ncu capture; None until one exists.
-# bf16/tf32/fp32: captured at 32768 rows (profiles/), x and y traffic doubled for the full 65536-row launch.
-TRAFFIC_BYTES = {"bf16": 583.3e6, "tf32": 759.7e6, "fp32": 592.4e6, "fp32x3": None}
+# bf16/tf32/fp32: captured at 32768 rows (profiles/), x and y traffic doubled for the full 65536-row launch;
+# fp32x3: captured at 16384 rows, x and y traffic times four (x is re-read once per 256-column tile).
+TRAFFIC_BYTES = {"bf16": 572.1e6, "tf32": 768.9e6, "fp32": 592.4e6, "fp32x3": 1505.5e6}
 
 
 def main():
