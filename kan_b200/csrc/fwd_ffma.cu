@@ -7,12 +7,38 @@
 // T_d = 2t T_{d-1} - T_{d-2} for its few (row, input) pairs in registers and
 // emits the next basis column straight into shared memory.  The basis tensor
 // never exists in device memory.  W is the packed fp32 matrix Wf[K_pad][N_pad].
+//
+// Small batches leave most SMs without a tile while each tile runs through the whole contraction.
+// The KSPLIT variant launches a thread-block cluster per tile: the CTAs of a cluster split the
+// input blocks among themselves, park their partial tiles in shared memory and add them up through
+// distributed shared memory in rank order (so the result does not depend on timing).
 #include "common.cuh"
 
 namespace chebykan {
 
 // two CTAs per SM (<= 128 registers): the second CTA covers the first one's FFMA and LDS latency
-template <int G_M, int G_N>
+__device__ __forceinline__ uint32_t ffma_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t ffma_cluster_size() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void ffma_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem(const float* local, uint32_t rank) {
+    uint32_t addr = (uint32_t)__cvta_generic_to_shared(local), peer;
+    float v;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(addr), "r"(rank));
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
+template <int G_M, int G_N, bool KSPLIT = false>
 __global__ void __launch_bounds__(256, 2)
 fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float* __restrict__ y,
                 int64_t B, int in, int out, int dp1, int n_pad, int n_tiles) {
@@ -25,14 +51,19 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
 
     const int tid = threadIdx.x;
     const int tx = tid & 15, ty = tid >> 4;
-    const int64_t m0 = (int64_t)(blockIdx.x / n_tiles) * BM;
-    const int n0 = (int)(blockIdx.x % n_tiles) * BN;
+    const uint32_t crank = KSPLIT ? ffma_cluster_rank() : 0u;
+    const uint32_t csize = KSPLIT ? ffma_cluster_size() : 1u;
+    const unsigned tile = KSPLIT ? blockIdx.x / csize : blockIdx.x;
+    const int64_t m0 = (int64_t)(tile / n_tiles) * BM;
+    const int n0 = (int)(tile % n_tiles) * BN;
 
     const int p_ii = tid & 7;   // producer: input inside the block of 8
     const int p_r = tid >> 3;   // producer: first row (then +32 per pair)
 
     const int n_iblk = (in + 7) / 8;
-    const int S = n_iblk * dp1;
+    // stages [S0, S): this CTA's share of the input blocks (all of them without KSPLIT)
+    const int S0 = KSPLIT ? (int)((int64_t)n_iblk * crank / csize) * dp1 : 0;
+    const int S = KSPLIT ? (int)((int64_t)n_iblk * (crank + 1) / csize) * dp1 : n_iblk * dp1;
 
     float acc[4 * G_M][4 * G_N];
 #pragma unroll
@@ -48,7 +79,7 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
 #pragma unroll
         for (int j = 0; j < EPT; ++j) {
             const int64_t row = m0 + p_r + 32 * j;
-            xpre[j] = (row < B && i < in && iblk < n_iblk) ? x[row * in + i] : 0.f;
+            xpre[j] = (row < B && i < in && iblk * dp1 < S) ? x[row * in + i] : 0.f;
         }
     };
     // next basis column of stage s into registers (phi) and its W rows into wreg
@@ -91,12 +122,14 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
         }
     };
 
-    load_x(0);
-    produce(0);
-    commit(0);
+    if (S0 < S) {
+        load_x(S0 / dp1);
+        produce(S0);
+        commit(S0 & 1);
+    }
     __syncthreads();
 
-    for (int s = 0; s < S; ++s) {
+    for (int s = S0; s < S; ++s) {
         const int buf = s & 1;
         if (s + 1 < S) produce(s + 1);
 #pragma unroll
@@ -121,6 +154,29 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
         __syncthreads();
     }
 
+    if (KSPLIT) {
+        // partial tile -> shared memory; every CTA then sums its rows' partials over all ranks in rank
+        // order and writes them; nobody leaves while a peer may still read its shared memory
+        __shared__ float red[BM][BN + 1];
+#pragma unroll
+        for (int r = 0; r < 4 * G_M; ++r)
+#pragma unroll
+            for (int c = 0; c < 4 * G_N; ++c)
+                red[(r / 4) * 64 + ty * 4 + (r & 3)][(c / 4) * 64 + tx * 4 + (c & 3)] = acc[r][c];
+        ffma_cluster_sync();
+        const int rows_per = (BM + (int)csize - 1) / (int)csize;
+        const int r_begin = (int)crank * rows_per, r_end = min(BM, r_begin + rows_per);
+        for (int e = r_begin * BN + tid; e < r_end * BN; e += 256) {
+            const int r = e / BN, c = e % BN;
+            float v = 0.f;
+            for (uint32_t q = 0; q < csize; ++q) v += ld_peer_smem(&red[r][c], q);
+            const int64_t row = m0 + r;
+            const int col = n0 + c;
+            if (row < B && col < out) y[row * out + col] = v;
+        }
+        ffma_cluster_sync();
+        return;
+    }
     const bool vec = (out & 3) == 0;
 #pragma unroll
     for (int g = 0; g < G_M; ++g)
@@ -163,7 +219,22 @@ int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_
         }
     } else {
         const int nt = (int)(p.n_pad / 64);
-        fwd_ffma_kernel<1, 1><<<(unsigned)(ceil_div(B, 64) * nt), 256, 0, s>>>(
+        const int64_t tiles = ceil_div(B, 64) * nt;
+        // few tiles and a long contraction: split the input blocks over a cluster per tile (2, 4 or 8 CTAs)
+        const int64_t n_iblk = ceil_div(in, 8);
+        int ks = 1;
+        while (ks < 8 && tiles * ks * 2 <= 148 && n_iblk >= 4 * ks) ks *= 2;
+        if (ks > 1) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(tiles * ks)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
+            cudaLaunchAttribute attrs[1];
+            attrs[0].id = cudaLaunchAttributeClusterDimension;
+            attrs[0].val.clusterDim.x = (unsigned)ks; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
+            cfg.attrs = attrs; cfg.numAttrs = 1;
+            return check_cuda(cudaLaunchKernelEx(&cfg, fwd_ffma_kernel<1, 1, true>, x, wf, y, B, (int)in, (int)out, dp1,
+                                                 (int)p.n_pad, nt));
+        }
+        fwd_ffma_kernel<1, 1><<<(unsigned)tiles, 256, 0, s>>>(
             x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt);
     }
     return check_cuda(cudaGetLastError());

@@ -307,3 +307,19 @@ def test_jacobian_matches_autograd(B, n_in, n_out, deg):
     assert o.rel_l2(layer.compute_derivatives(x.cuda()).cpu(), J_ref.sum(-1)) <= FP32_TOL
     with pytest.raises(NotImplementedError):
         layer.compute_derivatives(x.cuda(), order=2)
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg", [(256, 784, 64, 4), (64, 200, 10, 8), (100, 1024, 130, 3), (1, 64, 64, 5)])
+def test_small_batch_forward_splits_the_contraction_over_a_cluster(B, n_in, n_out, deg):
+    """Few row tiles and many inputs: the fp32 forward runs one cluster of 2-8 CTAs per tile and adds the partial
+    tiles through distributed shared memory in rank order: within tolerance of the oracle and bitwise repeatable."""
+    x, coeffs, _ = make_case(B, n_in, n_out, deg, seed=B + n_in)
+    xd, cd = x.cuda(), coeffs.cuda()
+    packed = ops.pack_coeffs(cd, "fp32")
+    y, yw = guarded((B, n_out))
+    ops.forward(xd, packed, n_in, n_out, deg, "fp32", out=y)
+    torch.cuda.synchronize()
+    assert_guards_intact(y, yw)
+    assert o.rel_l2(y.cpu(), o.forward(x, coeffs)) <= FP32_TOL
+    y2 = ops.forward(xd, packed, n_in, n_out, deg, "fp32")
+    assert torch.equal(y, y2)

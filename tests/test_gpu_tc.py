@@ -263,15 +263,18 @@ def test_forward_host_pipelined(mode, tol):
     y = layer.forward_host(x, chunk_rows=1024)              # 5 blocks, the last one ragged
     assert y.shape == (5000, 72) and not y.is_cuda
     y_dev = layer(x.cuda()).detach().cpu()
-    assert torch.equal(y, y_dev)
+    # tensor-core kernels give the same bits for any row blocking; the fp32 kernel splits its contraction over a
+    # cluster when a call has few tiles, so there the summation order (not the value) depends on the block size
+    same = (lambda a, b: torch.equal(a, b)) if mode != "fp32" else (lambda a, b: o.rel_l2(a, b) <= 1e-6)
+    assert same(y, y_dev)
     c = layer.cheby_coeffs.detach().cpu()
     assert o.rel_l2(y, o.forward(x, c.bfloat16().float() if mode == "bf16" else c)) <= tol
     out = torch.empty(5000, 72).pin_memory()
-    assert layer.forward_host(x, out=out, chunk_rows=100000) is out and torch.equal(out, y)
+    assert layer.forward_host(x, out=out, chunk_rows=100000) is out and same(out, y)
     # pageable (not pinned) host memory and a block size that does not divide anything: still the same bits
     xp = x[:777].clone()
     assert not xp.is_pinned()
-    assert torch.equal(layer.forward_host(xp, out=torch.empty(777, 72), chunk_rows=250), y[:777])
+    assert same(layer.forward_host(xp, out=torch.empty(777, 72), chunk_rows=250), y[:777])
     # the C entry point refuses scratch that is too small instead of writing past it
     lib = kan_b200._lib.load()
     packed = ops.pack_coeffs(layer.cheby_coeffs.detach(), mode)
