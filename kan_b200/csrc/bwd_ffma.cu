@@ -204,7 +204,7 @@ static DcoeffPlan dcoeff_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
     p.n_tiles = (int)ceil_div(out, 64 * p.g_n);
     const int64_t base = (int64_t)p.i_tiles * p.n_tiles;
     int64_t splits = ceil_div(2 * 148, base);
-    const int64_t max_splits = ceil_div(B, 256);
+    const int64_t max_splits = ceil_div(B, 64);     // a slice as short as 64 rows still amortises the tile setup
     if (splits > max_splits) splits = max_splits;
     if (splits < 1) splits = 1;
     p.rows_per_split = round_up(ceil_div(B, splits), 8);
