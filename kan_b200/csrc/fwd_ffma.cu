@@ -223,7 +223,7 @@ int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_
         // few tiles and a long contraction: split the input blocks over a cluster per tile (2, 4 or 8 CTAs)
         const int64_t n_iblk = ceil_div(in, 8);
         int ks = 1;
-        while (ks < 8 && tiles * ks * 2 <= 148 && n_iblk >= 4 * ks) ks *= 2;
+        while (ks < 8 && tiles * ks * 2 <= 2 * 148 && n_iblk >= 4 * ks) ks *= 2;   // up to two CTAs per SM
         if (ks > 1) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3((unsigned)(tiles * ks)); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = 0; cfg.stream = s;
