@@ -44,6 +44,10 @@ static bool mode_ok(int mode) {
     return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16 ||
            mode == CHEBYKAN_MODE_FP32X3;
 }
+static bool dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (mode == CHEBYKAN_MODE_FP32 || !dx_tc_supported(B, in, out, deg)) return false;
+    return mode != CHEBYKAN_MODE_FP32X3 || x3_dx_on_tensor_cores(B, in, out, deg);
+}
 // modes whose backward kernels are the fp32 ones
 static bool fp32_backward(int mode) {
     return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_FP32X3;
@@ -94,7 +98,8 @@ int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int
         case CHEBYKAN_OP_FWD: return 0;
         case CHEBYKAN_OP_BWD_DCOEFF: return B == 0 ? 0 : dcoeff_workspace_bytes(B, in, out, deg, mode);
         case CHEBYKAN_OP_BWD_DX:
-            return (!fp32_backward(mode) && dx_tc_supported(B, in, out, deg)) ? dx_tc_workspace_bytes(in, out, deg) : 0;
+            return dx_on_tensor_cores(B, in, out, deg, mode)
+                       ? dx_tc_workspace_bytes(B, in, out, deg, mode == CHEBYKAN_MODE_FP32X3) : 0;
         default: return CHEBYKAN_EINVAL;
     }
 }
@@ -151,6 +156,13 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs, void* w
         return launch_dcoeff_tc(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate,
                                 status, s);
     }
+    // FP32X3, large products: the same kernel three times on tf32 heads and tails, short batch slices
+    if (mode == CHEBYKAN_MODE_FP32X3 && dcoeff_tc_supported(B, in, out, deg) &&
+        x3_backward_on_tensor_cores(B, in, out, deg)) {
+        if (!status) return CHEBYKAN_EINVAL;
+        return launch_dcoeff_tc(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate,
+                                status, s, 1);
+    }
     return launch_dcoeff_ffma(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg,
                               accumulate, s);
 }
@@ -166,10 +178,11 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float*
     int rc = check_device();
     if (rc) return rc;
     // tf32 and bf16 modes: tcgen05 kind::tf32 with the coefficients repacked into the workspace
-    if (!fp32_backward(mode) && dx_tc_supported(B, in, out, deg)) {
+    // FP32X3: the same kernel three times on tf32 heads and tails of dY and of the coefficients
+    if (dx_on_tensor_cores(B, in, out, deg, mode)) {
         if (!status) return CHEBYKAN_EINVAL;
         return launch_dx_tc(x, dy, coeffs, dx, workspace, workspace_bytes, B, in, out, deg, status,
-                            (cudaStream_t)stream);
+                            (cudaStream_t)stream, mode == CHEBYKAN_MODE_FP32X3);
     }
     return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream);
 }

@@ -83,7 +83,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                  int use_x_tma, int x_box_w, int nxs, int x_slot_bytes, const float* __restrict__ x,
                  float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
                  int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
-                 int32_t* status) {
+                 int32_t* status, int part, int exact_tanh) {
     using L = DcSmem<BN, CG>;
     constexpr int NS = L::NS;
     // tf32 x tf32 -> f32, A K-major, B MN-major, M = 128 per CTA, N = BNI
@@ -220,7 +220,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     bool finite = true;           // a NaN input makes every degree NaN: no rounding add then
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float t = tanh_fast(xc[r][e]);
+                        const float t = exact_tanh ? tanhf(xc[r][e]) : tanh_fast(xc[r][e]);
                         finite = finite && (t == t);
                         t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
                     }
@@ -233,7 +233,13 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     auto store4 = [&](const float (&v)[4]) {
                         uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) w[e] = tf32_rna(v[e], inc);
+                        for (int e = 0; e < 4; ++e) {
+                            // part 0: rounded to tf32.  Three-product mode: part 1 = head (the tensor pipe drops
+                            // the low 13 bits itself), part 2 = tail, the value minus its head
+                            if (part == 0) w[e] = tf32_rna(v[e], inc);
+                            else if (part == 1) w[e] = __float_as_uint(v[e]);
+                            else w[e] = __float_as_uint(v[e] - __uint_as_float(__float_as_uint(v[e]) & 0xFFFFE000u));
+                        }
                         const uint32_t dsta = lin ^ ((lin >> 3) & 0x70u);
                         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};"
                                      ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
@@ -431,7 +437,11 @@ int dc_tile_inputs(int64_t in, int dp1, int bn) {
 
 struct DcTcPlan { int TI, i_tiles, bn, cg, n_tiles, splits; int64_t rows_per_split; };
 
-DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
+// x3: at most DC_X3_ROWS batch rows (192 MMAs) go into one accumulator, because the tensor pipe's fp32
+// accumulation truncates; the slices' partial sums are added by the reduction kernel in ordinary fp32
+constexpr int64_t DC_X3_ROWS = 1536;
+
+DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0) {
     DcTcPlan p{};
     const int dp1 = (int)deg + 1;
     p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : (out <= 256 ? 256 : 512));
@@ -455,6 +465,7 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
         const int64_t cost = ceil_div(ctas, 148) * (rows + 2048);   // + fixed cost of a CTA (setup, epilogue)
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_s = sp; }
     }
+    if (x3 && best_s < ceil_div(B, DC_X3_ROWS)) best_s = ceil_div(B, DC_X3_ROWS);
     p.rows_per_split = round_up(ceil_div(B, best_s), DC_KB);
     p.splits = (int)ceil_div(B, p.rows_per_split);
     if (p.splits < 1) p.splits = 1;
@@ -463,7 +474,7 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
 
 template <int BN, int CG = 1>
 int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
-              const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s) {
+              const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s, int part, int exact) {
     using L = DcSmem<BN, CG>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -488,7 +499,7 @@ int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma,
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in,
                                          out, dp1, p.TI, p.i_tiles, p.n_tiles, p.rows_per_split, split_stride, add,
-                                         status));
+                                         status, part, exact));
 }
 
 }  // namespace
@@ -500,29 +511,47 @@ bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     return B > 0 && (out % 4) == 0 && dp1 <= 128;
 }
 
-int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg) {
-    const DcTcPlan p = dc_tc_plan(B, in, out, deg);
-    return p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
+    const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
+    const int64_t partials = p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
+    return x3 ? round_up(B * out * 4, 256) + partials : partials;     // x3: the tails of dY come first
 }
 
+// dY minus dY truncated to tf32 (defined next to the dx kernel, which needs the same split)
+int launch_dy_tail(const float* dy, float* lo, int64_t n, cudaStream_t s);
+
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
-                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s) {
-    const DcTcPlan p = dc_tc_plan(B, in, out, deg);
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3) {
+    const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int dp1 = (int)deg + 1;
     const int64_t n = in * out * dp1;
     const bool direct = p.splits == 1;
-    if (!direct && (ws == nullptr || ws_bytes < (int64_t)p.splits * n * 4)) return CHEBYKAN_EWORKSPACE;
+    if (dcoeff_tc_workspace_bytes(B, in, out, deg, x3) > 0 &&
+        (ws == nullptr || ws_bytes < dcoeff_tc_workspace_bytes(B, in, out, deg, x3)))
+        return CHEBYKAN_EWORKSPACE;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
-    CUtensorMap tmap;
-    const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
-    const cuuint64_t strides[1] = {(cuuint64_t)(out * 4)};
-    const cuuint32_t box[2] = {32, (cuuint32_t)DC_KB};
+    float* dy_lo = reinterpret_cast<float*>(ws);
+    float* partials = x3 ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + round_up(B * out * 4, 256))
+                         : reinterpret_cast<float*>(ws);
     const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(dy), dims, strides, box,
-                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    auto map_dy = [&](CUtensorMap* m, const float* ptr) -> int {
+        const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
+        const cuuint64_t strides[1] = {(cuuint64_t)(out * 4)};
+        const cuuint32_t box[2] = {32, (cuuint32_t)DC_KB};
+        const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims, strides, box,
+                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+        return CHEBYKAN_OK;
+    };
+    CUtensorMap tmap, tmap_lo;
+    int rc;
+    if ((rc = map_dy(&tmap, dy))) return rc;
+    if (x3) {
+        if ((rc = launch_dy_tail(dy, dy_lo, B * out, s))) return rc;
+        if ((rc = map_dy(&tmap_lo, dy_lo))) return rc;
+    }
     // x[B][in] as a TMA tensor when its row pitch allows (in % 4 == 0): a K block's x tile is 32 rows by
     // TI inputs; the box starts at the 16-byte boundary below the tile's first input and is wide enough
     // to cover the tile from there (rows and columns outside x read as zeros)
@@ -538,17 +567,24 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rx != CUDA_SUCCESS) { set_last_cuda_error((int)rx); return CHEBYKAN_ECUDA; }
     }
-    float* dst = direct ? dc : reinterpret_cast<float*>(ws);
-    const int add = direct && accumulate;
-    int rc;
-    if (p.bn == 64) rc = launch_dc<64>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else if (p.bn == 128) rc = launch_dc<128>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else if (p.bn == 256) rc = launch_dc<256>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else if (p.cg == 2) rc = launch_dc<512, 2>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    else rc = launch_dc<512>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s);
-    if (rc) return rc;
-    if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
-    return rc;
+    float* dst = direct ? dc : partials;
+    // one pass in the tf32 / bf16 modes; three in the fp32-grade mode: basis heads x dY, basis heads x dY tails,
+    // basis tails x dY (the tensor pipe reads the head of whatever fp32 value it is given), each added into dC
+    const int passes = x3 ? 3 : 1;
+    for (int pass = 0; pass < passes; ++pass) {
+        const CUtensorMap& m = (pass == 1) ? tmap_lo : tmap;
+        const int part = x3 ? (pass == 2 ? 2 : 1) : 0;
+        const int acc = (pass == 0) ? accumulate : 1;
+        const int add = direct && acc;
+        if (p.bn == 64) rc = launch_dc<64>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        else if (p.bn == 128) rc = launch_dc<128>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        else if (p.bn == 256) rc = launch_dc<256>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        else if (p.cg == 2) rc = launch_dc<512, 2>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        else rc = launch_dc<512>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        if (rc) return rc;
+        if (!direct && (rc = launch_dcoeff_reduce(partials, dc, n, p.splits, acc, s))) return rc;
+    }
+    return CHEBYKAN_OK;
 }
 
 }  // namespace chebykan

@@ -72,6 +72,9 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t& r) {
 
 // Wd[(i,d)][out_pad] <- tf32(d * C[i][o][d]); columns o >= out are zero.  The degree factor of
 // T_d' = d U_{d-1} is folded in here so that the epilogue only needs U_{d-1} * G per value.
+// PART 0: rounded to tf32 (the tf32 / bf16 modes).  PART 1: head = the value truncated to tf32, and the tail
+// (value - head, fp32) in a second matrix right behind the first (the fp32-grade three-product mode).
+template <int PART>
 __global__ void __launch_bounds__(256)
 pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad) {
     const int64_t total = (int64_t)in * dp1 * out_pad;
@@ -83,9 +86,24 @@ pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, i
         const int d = (int)(slot % dp1);
         float v = 0.f;
         if (o < out) v = (float)d * c[(i * out + o) * dp1 + d];
-        uint32_t r;
-        asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
-        wd[e] = r;
+        if (PART == 0) {
+            uint32_t r;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+            wd[e] = r;
+        } else {
+            const uint32_t hi = __float_as_uint(v) & 0xFFFFE000u;
+            wd[e] = hi;
+            wd[total + e] = __float_as_uint(v - __uint_as_float(hi));
+        }
+    }
+}
+
+// tail of dY for the three-product mode: dY minus dY truncated to tf32 (what the tensor pipe reads of dY itself)
+__global__ void __launch_bounds__(256)
+dy_tail_kernel(const float* __restrict__ dy, float* __restrict__ lo, int64_t n) {
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+        const float v = dy[e];
+        lo[e] = v - __uint_as_float(__float_as_uint(v) & 0xFFFFE000u);
     }
 }
 
@@ -93,7 +111,7 @@ template <int CG>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
              const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
-             int i_tiles, int64_t num_tiles, int32_t* status) {
+             int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh) {
     using L = DxSmem<CG>;
     constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS;
     constexpr int DX_STAGE = L::STAGE, DX_BAR_OFFSET = L::BAR_OFFSET;
@@ -227,7 +245,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * DX_BN);
             for (int ii = ii_begin; ii < ii_end; ++ii) {
-                const float t = tanh_fast(xnext);
+                const float t = exact_tanh ? tanhf(xnext) : tanh_fast(xnext);
                 if (row_ok && ii + 1 < ii_end) xnext = __ldg(xrow + ii + 1);
                 const float t2 = 2.f * t;
                 // ua / ub alternate as (U_{d-1}, U_{d-2}); U_{-1} = 0, U_{-2} = -1 make U_0 = 1 and
@@ -273,7 +291,10 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     if (rem & 2) fold2(r2[0], r2[1]);
                     if (rem & 1) sum = fmaf(ua, __uint_as_float(r1), sum);
                 }
-                if (row_ok) dxrow[ii] = fmaf(-t, t, 1.f) * sum;
+                if (row_ok) {
+                    const float v = fmaf(-t, t, 1.f) * sum;
+                    dxrow[ii] = accumulate ? dxrow[ii] + v : v;
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -300,19 +321,30 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
 
 }  // namespace
 
+int launch_dy_tail(const float* dy, float* lo, int64_t n, cudaStream_t s) {
+    int64_t blocks = ceil_div(n, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
+    dy_tail_kernel<<<(unsigned)blocks, 256, 0, s>>>(dy, lo, n);
+    return check_cuda(cudaGetLastError());
+}
+
 // dY and Wd rows must be TMA-addressable (16-byte pitch) and one input's degrees must fit a tile
 bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     return B > 0 && (out % 4) == 0 && deg + 1 <= DX_BN && in * (deg + 1) < ((int64_t)1 << 31);
 }
 
-int64_t dx_tc_workspace_bytes(int64_t in, int64_t out, int64_t deg) {
-    return in * (deg + 1) * round_up(out, 32) * 4;
+// tf32 / bf16 modes: the repacked coefficients.  Three-product (fp32-grade) mode: their heads and tails, and the
+// tails of dY.
+int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
+    const int64_t wd = round_up(in * (deg + 1) * round_up(out, 32) * 4, 256);
+    return x3 ? 2 * wd + round_up(B * out * 4, 256) : wd;
 }
 
 namespace {
 template <int CG>
 int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
-                     int in, int out, int dp1, int32_t* status, cudaStream_t s) {
+                     int in, int out, int dp1, int32_t* status, cudaStream_t s, int accumulate = 0, int exact_tanh = 0) {
     using L = DxSmem<CG>;
     static bool attr_set[64] = {false};
     int dev = 0;
@@ -338,49 +370,73 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, dp1, TI, i_tiles, num_tiles,
-                                         status));
+                                         status, accumulate, exact_tanh));
 }
 }  // namespace
 
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
-                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s) {
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3) {
     const int dp1 = (int)deg + 1;
     const int64_t out_pad = round_up(out, 32);
     const int64_t slots = in * dp1;
-    if (ws == nullptr || ws_bytes < slots * out_pad * 4) return CHEBYKAN_EWORKSPACE;
+    if (ws == nullptr || ws_bytes < dx_tc_workspace_bytes(B, in, out, deg, x3)) return CHEBYKAN_EWORKSPACE;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
+    const int64_t wd_bytes = round_up(slots * out_pad * 4, 256);
+    uint32_t* wd_hi = reinterpret_cast<uint32_t*>(ws);
+    uint32_t* wd_lo = wd_hi + slots * out_pad;                       // written right behind the heads by the pack kernel
+    float* dy_lo = reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + 2 * wd_bytes);
     {
         int64_t blocks = ceil_div(slots * out_pad, 256);
         if (blocks > 148 * 16) blocks = 148 * 16;
-        pack_dx_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, reinterpret_cast<uint32_t*>(ws), (int)in, (int)out,
-                                                        dp1, (int)out_pad);
+        if (x3) pack_dx_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad);
+        else pack_dx_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad);
         int rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
+        if (x3) {
+            int64_t b2 = ceil_div(B * out, 256);
+            if (b2 > 148 * 16) b2 = 148 * 16;
+            dy_tail_kernel<<<(unsigned)b2, 256, 0, s>>>(dy, dy_lo, B * out);
+            if ((rc = check_cuda(cudaGetLastError()))) return rc;
+        }
     }
     const int cg = B > DX_BM ? 2 : 1;
-    CUtensorMap tmap_dy, tmap_w;
     const cuuint32_t estr[2] = {1, 1};
-    {
+    auto map_dy = [&](CUtensorMap* m, const float* p) -> int {
         const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
         const cuuint64_t strides[1] = {(cuuint64_t)(out * 4)};
         const cuuint32_t box[2] = {DX_KB, DX_BM};
-        const CUresult r = encode(&tmap_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(dy), dims, strides,
+        const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(p), dims, strides,
                                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
-    }
-    {
+        return CHEBYKAN_OK;
+    };
+    auto map_w = [&](CUtensorMap* m, void* p) -> int {
         const cuuint64_t dims[2] = {(cuuint64_t)out_pad, (cuuint64_t)slots};
         const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 4)};
         const cuuint32_t box[2] = {DX_KB, (cuuint32_t)(DX_BN / cg)};
-        const CUresult r = encode(&tmap_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ws, dims, strides, box, estr,
+        const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p, dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
-    }
-    if (cg == 2) return launch_dx_kernel<2>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, status, s);
-    return launch_dx_kernel<1>(tmap_dy, tmap_w, x, dx, B, (int)in, (int)out, dp1, status, s);
+        return CHEBYKAN_OK;
+    };
+    auto run = [&](const CUtensorMap& mdy, const CUtensorMap& mw, int accumulate) -> int {
+        if (cg == 2) return launch_dx_kernel<2>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
+        return launch_dx_kernel<1>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
+    };
+    CUtensorMap m_dy, m_w;
+    int rc;
+    if ((rc = map_dy(&m_dy, dy)) || (rc = map_w(&m_w, wd_hi))) return rc;
+    if ((rc = run(m_dy, m_w, 0))) return rc;
+    if (!x3) return CHEBYKAN_OK;
+    // dx = fold(dY_head Wd_head) + fold(dY_head Wd_tail) + fold(dY_tail Wd_head): the fold is linear in G, so the
+    // three products are three launches that add into dx (tail x tail is below fp32 rounding)
+    CUtensorMap m_wlo, m_dylo;
+    if ((rc = map_w(&m_wlo, wd_lo)) || (rc = map_dy(&m_dylo, dy_lo))) return rc;
+    if ((rc = run(m_dy, m_wlo, 1))) return rc;
+    return run(m_dylo, m_w, 1);
 }
 
 }  // namespace chebykan

@@ -214,6 +214,9 @@ static DcoeffPlan dcoeff_plan(int64_t B, int64_t in, int64_t out, int64_t deg) {
 }
 
 int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (mode == CHEBYKAN_MODE_FP32X3 && dcoeff_tc_supported(B, in, out, deg) &&
+        x3_backward_on_tensor_cores(B, in, out, deg))
+        return dcoeff_tc_workspace_bytes(B, in, out, deg, 1);
     if (mode != CHEBYKAN_MODE_FP32 && mode != CHEBYKAN_MODE_FP32X3 && dcoeff_tc_supported(B, in, out, deg))
         return dcoeff_tc_workspace_bytes(B, in, out, deg);
     const DcoeffPlan p = dcoeff_plan(B, in, out, deg);

@@ -100,16 +100,25 @@ int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int
                        int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
                        cudaStream_t s);
 int launch_dcoeff_reduce(const float* ws, float* dc, int64_t n, int splits, int accumulate, cudaStream_t s);
+// FP32X3 backward: the tf32 tensor-core kernels run three times on head/tail operands.  Worth it only for
+// large products (three launches and two operand splits against one FFMA launch), and the dx kernel keeps a whole
+// row of outputs in one accumulator, whose truncating accumulation stays inside the tolerance up to 2048 outputs.
+inline bool x3_backward_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    return B * in * (deg + 1) * out >= ((int64_t)1 << 30);
+}
+inline bool x3_dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg) {
+    return out <= 2048 && x3_backward_on_tensor_cores(B, in, out, deg);
+}
 bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
-int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg);
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0);
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
-                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s);
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3 = 0);
 int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
                    int64_t in, int64_t out, int64_t deg, cudaStream_t s);
 bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
-int64_t dx_tc_workspace_bytes(int64_t in, int64_t out, int64_t deg);
+int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3);
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
-                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s);
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3);
 int launch_sgd(float* p, const float* g, int64_t n, float lr, float gs, cudaStream_t s);
 int launch_adam(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1,
                 float b2, float eps, int64_t step, float gs, cudaStream_t s);

@@ -379,6 +379,44 @@ def test_fp32x3_forward_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
     assert err <= 1e-5, err
 
 
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", [
+    (8192, 64, 64, 32, "uniform3"), (4096, 1024, 1024, 8, "normal"), (300, 13, 20, 8, "normal"),
+    (1000, 51, 40, 4, "normal"), (129, 5, 36, 63, "normal"), (2048, 256, 2048, 3, "normal"), (1, 4, 4, 0, "normal")])
+def test_fp32x3_dx_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
+    """dx in 'fp32x3' mode: the tf32 kernel run on heads and tails of dY and of the coefficients (three launches
+    that add into dx), within the 1e-5 bound of the fp32 mode."""
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    _, _, dx_ref = o.forward_backward(x, coeffs, dy)
+    dx, dxw = guarded((B, n_in))
+    ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "fp32x3", out=dx)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dx, dxw)
+    if deg == 0:
+        assert float(dx.abs().max()) == 0.0
+    else:
+        assert o.rel_l2(dx.cpu(), dx_ref) <= 1e-5
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", [
+    (8192, 64, 64, 32, "uniform3"), (4096, 1024, 1024, 8, "normal"), (5000, 40, 132, 5, "normal"),
+    (40000, 24, 64, 7, "normal"), (3000, 70, 520, 8, "normal"), (300, 13, 20, 8, "normal")])
+def test_fp32x3_dcoeff_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
+    """dC in 'fp32x3' mode: the tf32 kernel on basis heads / tails and dY / dY tails over batch slices of at most
+    1536 rows, partial sums added in fp32 (small products stay on the fp32 kernel); also with accumulate."""
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    dC, dCw = guarded((n_in, n_out, deg + 1))
+    ops.bwd_dcoeff(x.cuda(), dy.cuda(), n_in, n_out, deg, "fp32x3", out=dC)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dC, dCw)
+    assert o.rel_l2(dC.cpu(), dC_ref) <= 1e-5
+    acc = dC.clone()
+    ops.bwd_dcoeff(x.cuda(), dy.cuda(), n_in, n_out, deg, "fp32x3", out=acc, accumulate=True)
+    assert o.rel_l2(acc.cpu(), 2 * dC_ref) <= 1e-5
+
+
 def test_fp32x3_layer_trains_with_fp32_backward():
     torch.manual_seed(5)
     layer = kan_b200.ChebyKANLayer(96, 520, 6, math_mode="fp32x3").cuda()
