@@ -47,8 +47,12 @@ extern "C" {
 /* fp32-grade forward on the tensor cores: basis values and coefficients are each
  * split into a tf32 head and a tf32 tail and three tcgen05 kind::tf32 products
  * (head*head, head*tail, tail*head) are accumulated in fp32, with the library's
- * single-precision tanh (2 ulp).  Same 1e-5 tolerance as CHEBYKAN_MODE_FP32; the
- * backward entry points run their fp32 kernels in this mode. */
+ * single-precision tanh (2 ulp).  Same 1e-5 tolerance as CHEBYKAN_MODE_FP32.  The
+ * backward entry points do the same for large products (the tf32 kernels run
+ * three times on heads and tails, over short batch slices for dC; their
+ * workspace then also holds the tails of dY and, for dC, one partial result per
+ * 1536 batch rows) and run their fp32 kernels for small ones and for dx with
+ * more than 2048 outputs. */
 #define CHEBYKAN_MODE_FP32X3 3
 
 /* operations that may need a caller-provided workspace */

@@ -257,9 +257,9 @@ ChebyKANLayerDoc = """KAN layer on Chebyshev polynomials, computed by sm_100a CU
         input_dim, output_dim, degree, use_recurrence, init_scale
     Keyword-only:
         math_mode: 'fp32' (FFMA, rel-L2 <= 1e-5 to the reference), 'fp32x3' (the same
-                   tolerance with the forward on the tensor cores: three tf32 products of
-                   head/tail splits; backward as in 'fp32'), 'tf32' or 'bf16' (tcgen05
-                   tensor cores, rel-L2 <= 2e-3).
+                   tolerance on the tensor cores: three tf32 products of head/tail
+                   splits, forward and - for large layers - backward), 'tf32' or 'bf16'
+                   (tcgen05 tensor cores, rel-L2 <= 2e-3).
     ``use_recurrence`` is kept for API compatibility; the kernels always use
     the three-term recurrence, which agrees with the reference's closed form
     to about 1e-6.
