@@ -400,7 +400,8 @@ def test_fp32x3_dx_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
 
 @pytest.mark.parametrize("B,n_in,n_out,deg,dist", [
     (8192, 64, 64, 32, "uniform3"), (4096, 1024, 1024, 8, "normal"), (5000, 40, 132, 5, "normal"),
-    (40000, 24, 64, 7, "normal"), (3000, 70, 520, 8, "normal"), (300, 13, 20, 8, "normal")])
+    (40000, 24, 64, 7, "normal"), (3000, 70, 520, 8, "normal"), (300, 13, 20, 8, "normal"),
+    (1024, 1024, 1024, 1, "normal")])      # one batch slice: the three passes add straight into dC
 def test_fp32x3_dcoeff_meets_the_fp32_tolerance(B, n_in, n_out, deg, dist):
     """dC in 'fp32x3' mode: the tf32 kernel on basis heads / tails and dY / dY tails over batch slices of at most
     1536 rows, partial sums added in fp32 (small products stay on the fp32 kernel); also with accumulate."""
