@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 3
+#define CHEBYKAN_ABI_VERSION 4
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -140,13 +140,17 @@ int chebykan_bwd_dcoeff(const float* x, const float* dy, float* dcoeffs,
  *     refused with CHEBYKAN_ESTATIC; use chebykan_bwd_dcoeff for those.
  *   - The first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress, with that device current); make that first call
- *     outside any stream capture.  No call allocates or frees anything.
+ *     outside any stream capture.  The lookup is guarded by a mutex, so first
+ *     calls from several host threads are safe.  No call allocates or frees
+ *     anything.  The current device must be compute capability 10.x
+ *     (CHEBYKAN_EDEVICE otherwise), as for every other entry point.
  *   - All calls share the one array.  A call overwrites every byte it later
  *     reads, so leftovers of earlier calls are harmless, but two calls that
  *     may run on the GPU at the same time (different streams, different host
  *     threads) race on it: keep calls on one device in stream order.
- * Arithmetic is fp32 (the only dC path so far) and the result is identical to
- * chebykan_bwd_dcoeff's.
+ * This entry point always runs the fp32 FFMA kernels, whatever modes the
+ * workspace variant offers; its result is bit-identical to
+ * chebykan_bwd_dcoeff(..., CHEBYKAN_MODE_FP32, ...).
  */
 int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float* dcoeffs,
                                int64_t B, int64_t in, int64_t out, int64_t deg,
@@ -177,6 +181,40 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs,
 int chebykan_jacobian(const float* x, const float* coeffs, float* jac,
                       int64_t B, int64_t in, int64_t out, int64_t deg,
                       void* stream);
+
+/*
+ * The basis object's own methods, on flat fp32 arrays of n = B*in elements:
+ *   chebykan_normalize_input   t = tanh(x), correctly rounded
+ *                              (ChebyshevBasis.normalize_input, kan/basis/chebyshev.py:68-78);
+ *   chebykan_basis_functions   phi[e][d] = T_d(clamp(t[e], -1, 1)), d = 0..deg, by the three-term
+ *                              recurrence (ChebyshevBasis.basis_functions, kan/basis/chebyshev.py:103-172);
+ *                              phi has n*(deg+1) elements.
+ * The layer's forward never builds phi; these serve callers that want the basis tensor itself.
+ */
+int chebykan_normalize_input(const float* x, float* t, int64_t n, void* stream);
+int chebykan_basis_functions(const float* t, float* phi, int64_t n, int64_t deg,
+                             void* stream);
+
+/*
+ * Mean-squared-error loss and its gradient in one pass: *loss = sum (y - target)^2 / n_mean and
+ * dy[e] = 2 (y[e] - target[e]) / n_mean * grad_scale, over n elements.  Replaces the
+ * nn.MSELoss() forward and backward of the reference's training loop (README.md:57-69), which
+ * read y and the target three times and write a temporary.  n_mean is the element count the mean
+ * runs over (n on one GPU; the global count when the batch is sharded, so that the summed
+ * gradients of all ranks equal the single-GPU gradient).  `workspace` holds per-block partial
+ * sums (chebykan_mse_workspace_bytes() bytes); they are added in a fixed order, so the loss is
+ * repeatable bit for bit.
+ */
+int64_t chebykan_mse_workspace_bytes(void);
+int chebykan_mse_loss_grad(const float* y, const float* target, float* dy, float* loss,
+                           void* workspace, int64_t workspace_bytes, int64_t n,
+                           int64_t n_mean, float grad_scale, void* stream);
+/*
+ * dy[e] *= *scalar (a device float) unless *scalar == 1, in which case nothing is written: the
+ * chain-rule factor autograd hands to the loss's backward (torch's MseLossBackward multiplies
+ * unconditionally).  No other counterpart in the reference.
+ */
+int chebykan_scale_by_device_scalar(float* dy, const float* scalar, int64_t n, void* stream);
 
 /*
  * Optimizer updates on a flat fp32 parameter of n elements.  Replace

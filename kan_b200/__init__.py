@@ -8,8 +8,9 @@ behind the C ABI of ``include/chebykan_b200.h``; there is no CPU fallback.
 """
 from .layer import ChebyKANLayer, ChebyshevBasis, KANLayer, chebykan_apply, install_into_reference
 from .stack import FusedChebyKANStack, fuse_layernorm
+from .loss import MSELoss, mse_loss
 from . import ops, optim, dp, workloads, graph
 
-__all__ = ["FusedChebyKANStack", "fuse_layernorm", "ChebyKANLayer", "ChebyshevBasis", "KANLayer", "chebykan_apply", "install_into_reference",
+__all__ = ["MSELoss", "mse_loss", "FusedChebyKANStack", "fuse_layernorm", "ChebyKANLayer", "ChebyshevBasis", "KANLayer", "chebykan_apply", "install_into_reference",
            "ops", "optim", "dp", "workloads", "graph"]
 __version__ = "0.1.0"

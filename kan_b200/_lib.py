@@ -36,6 +36,12 @@ SIGNATURES = {
     "chebykan_bwd_dx": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                 c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "chebykan_jacobian": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "chebykan_normalize_input": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "chebykan_basis_functions": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "chebykan_mse_workspace_bytes": (c_int64, []),
+    "chebykan_mse_loss_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                       c_float, c_void_p]),
+    "chebykan_scale_by_device_scalar": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "chebykan_sgd_step": (c_int, [c_void_p, c_void_p, c_int64, c_float, c_float, c_void_p]),
     "chebykan_adam_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                                    c_float, c_float, c_int64, c_float, c_void_p]),
@@ -67,7 +73,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 3:
+    if lib.chebykan_abi_version() != 4:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -10,7 +10,7 @@ void set_last_cuda_error(int e) { g_last_cuda_error = e; }
 // 0 = unknown, 1 = compute capability 10.x, -1 = anything else (per device ordinal)
 static int g_cc_ok[64] = {0};
 
-static int check_device() {
+int check_device() {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) { set_last_cuda_error((int)e); return CHEBYKAN_ECUDA; }

@@ -7,6 +7,7 @@
 // Both kernels index the contraction "input-major" (kk = ii*(deg+1) + d for the
 // TI inputs a CTA owns), which is the coefficient tensor's own memory order, so
 // neither needs a packed copy of the coefficients.
+#include <mutex>
 #include "common.cuh"
 
 namespace chebykan {
@@ -264,14 +265,17 @@ static __device__ __align__(256) unsigned char g_dcoeff_scratch[STATIC_SCRATCH_B
 
 // Device address of g_dcoeff_scratch per device ordinal.  In host code the
 // array's name is only a handle for the runtime, not a device address, so the
-// address is looked up once per device with that device current.
+// address is looked up once per device with that device current.  The cache is
+// guarded by a mutex: first calls may come from several host threads at once.
 static void* g_dcoeff_scratch_addr[64] = {nullptr};
+static std::mutex g_dcoeff_scratch_mutex;
 
 static int static_scratch_address(void** out) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return check_cuda(e);
     if (dev < 0 || dev >= 64) return CHEBYKAN_EDEVICE;
+    std::lock_guard<std::mutex> lock(g_dcoeff_scratch_mutex);
     if (g_dcoeff_scratch_addr[dev] == nullptr) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_dcoeff_scratch);
@@ -425,11 +429,13 @@ extern "C" int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float
     }
     if (!x || !dy) return CHEBYKAN_EINVAL;
     if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
+    int rc = check_device();        // same device rule as every other entry point: compute capability 10.x only
+    if (rc) return rc;
     // the partial sums of every batch slice must fit the fixed array
     const int64_t need = dcoeff_workspace_bytes(B, in, out, deg, CHEBYKAN_MODE_FP32);
     if (need > STATIC_SCRATCH_BYTES) return CHEBYKAN_ESTATIC;
     void* scratch = nullptr;
-    int rc = static_scratch_address(&scratch);
+    rc = static_scratch_address(&scratch);
     if (rc) return rc;
     // Every slice's tile overwrites its whole part of the scratch before the
     // reduction reads it, so nothing left by an earlier call needs clearing.

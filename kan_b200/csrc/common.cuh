@@ -74,6 +74,10 @@ inline int check_cuda(cudaError_t e) {
     return CHEBYKAN_ECUDA;
 }
 
+// CHEBYKAN_OK when the current device is compute capability 10.x (also binds the device's primary context to the
+// calling thread); every entry point that launches a kernel calls it first
+int check_device();
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Optional LayerNorm fusion of the tensor-core forward.  stats_* hold two floats per row (sum and

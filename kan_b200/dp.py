@@ -38,16 +38,36 @@ class FlatGradBuffer:
         dev = self.params[0].device
         sizes = [(p.numel() + 3) // 4 * 4 for p in self.params]   # keep every view 16-byte aligned
         self.flat = torch.zeros(sum(sizes), dtype=torch.float32, device=dev)
+        self._views: List[torch.Tensor] = []
         off = 0
         for p, n in zip(self.params, sizes):
-            p.grad = self.flat[off:off + p.numel()].view_as(p)
+            self._views.append(self.flat[off:off + p.numel()].view_as(p))
             off += n
+        self.attach()
+
+    def attach(self) -> None:
+        """Make every ``p.grad`` the parameter's view of the flat buffer again.
+
+        ``optimizer.zero_grad()`` with ``set_to_none=True`` (torch's default) drops ``p.grad``; the next backward
+        then installs a fresh tensor that the collective would not see.  A gradient found detached is copied into
+        its view (so nothing a backward already produced is lost) and re-attached."""
+        for p, v in zip(self.params, self._views):
+            g = p.grad
+            if g is None:
+                v.zero_()
+                p.grad = v
+            elif g.data_ptr() != v.data_ptr():
+                v.copy_(g)
+                p.grad = v
 
     def zero(self) -> None:
+        """Clear every gradient (use this, or ``zero_grad(set_to_none=False)``, instead of dropping ``p.grad``)."""
         self.flat.zero_()
+        self.attach()
 
     def all_reduce(self, group=None, async_op: bool = False):
         """Sum the gradients over the ranks of `group` (no-op for a single process)."""
+        self.attach()
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
             return None
         return dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)

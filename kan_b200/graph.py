@@ -22,8 +22,10 @@ torch.autograd.graph.set_warn_on_accumulate_grad_stream_mismatch(False)
 
 class GraphedTrainStep:
     def __init__(self, model: torch.nn.Module, loss_fn: Callable, optimizer, x: torch.Tensor, target: torch.Tensor,
-                 warmup: int = 3):
+                 warmup: int = 3, status_every: int = 256):
         """`optimizer` must be graph-capturable (kan_b200.optim.SGD, or Adam(capturable=True))."""
+        self.status_every = int(status_every)
+        self._replays = 0
         if getattr(optimizer, "capturable", True) is False:
             raise ValueError("use kan_b200.optim.Adam(..., capturable=True) for a graphed step")
         self.model, self.loss_fn, self.opt = model, loss_fn, optimizer
@@ -49,6 +51,19 @@ class GraphedTrainStep:
         self.opt.step()
 
     def __call__(self) -> torch.Tensor:
-        """Replay one step; returns the (device) loss tensor of that step."""
+        """Replay one step; returns the (device) loss tensor of that step.
+
+        The replayed kernels write the parameters through raw pointers, so every
+        replay bumps each parameter's autograd version: anything keyed on it (the
+        layers' packed-coefficient caches, which an eager forward between replays
+        consults) sees that the coefficients changed.  Every `status_every`
+        replays (default 256; 0 = never) the device status word of the bounded
+        waits is read back, which synchronises: a kernel that gave up a wait
+        raises here instead of training on unwritten buffers."""
         self.graph.replay()
+        for p in self.grads.params:
+            torch.autograd.graph.increment_version(p)
+        self._replays += 1
+        if self.status_every and self._replays % self.status_every == 0:
+            ops.check_status(self.x.device)
         return self.loss

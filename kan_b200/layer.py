@@ -74,6 +74,28 @@ class ChebyshevBasis:
         x = x.view(-1, coefficients.shape[0])
         return chebykan_apply(x, coefficients, "fp32", None)
 
+    def normalize_input(self, x: torch.Tensor) -> torch.Tensor:
+        """t = tanh(x) (kan/basis/chebyshev.py:68-78)."""
+        return ops.normalize_input(_aligned(x))
+
+    def basis_functions(self, x: torch.Tensor) -> torch.Tensor:
+        """T_0..T_degree at normalised points x in [-1, 1]: shape x.shape + (degree+1,)
+        (kan/basis/chebyshev.py:103-172; both of the reference's evaluation paths give these values)."""
+        return ops.basis_functions(_aligned(x), self.degree)
+
+    def derivative(self, x: torch.Tensor, coefficients: torch.Tensor, order: int = 1) -> torch.Tensor:
+        """d/dx of the expansion summed over the inputs, shape (batch, output_dim); order 0 is ``forward``.
+
+        The reference's method of this name (kan/basis/chebyshev.py:174-267) does not return a derivative of the
+        expansion (its coefficient rule is wrong and it re-applies tanh); this one returns the values autograd
+        gives for sum_i d y_o / d x_i.  Orders above 1 are not implemented."""
+        if order == 0:
+            return self.forward(x, coefficients)
+        if order != 1:
+            raise NotImplementedError("only first derivatives are implemented")
+        x = _aligned(x.view(-1, coefficients.shape[0]))
+        return ops.jacobian(x, _aligned(coefficients.detach())).sum(-1)
+
 
 # ---------------------------------------------------------------------------
 # autograd glue

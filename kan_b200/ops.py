@@ -205,6 +205,65 @@ def jacobian(x: torch.Tensor, coeffs: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def normalize_input(x: torch.Tensor) -> torch.Tensor:
+    """t = tanh(x), the basis object's input normalisation (correctly rounded fp32)."""
+    _require(x, "x")
+    t = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_normalize_input(x.data_ptr(), t.data_ptr(), x.numel(), _stream(x))
+    _lib.check(rc, "chebykan_normalize_input")
+    return t
+
+
+def basis_functions(t: torch.Tensor, degree: int) -> torch.Tensor:
+    """Phi[..., d] = T_d(t) for d = 0..degree; `t` holds normalised inputs in [-1, 1]."""
+    _require(t, "t")
+    phi = torch.empty(*t.shape, degree + 1, dtype=torch.float32, device=t.device)
+    with torch.cuda.device(t.device):
+        rc = _lib.load().chebykan_basis_functions(t.data_ptr(), phi.data_ptr(), t.numel(), degree, _stream(t))
+    _lib.check(rc, "chebykan_basis_functions")
+    return phi
+
+
+_mse_ws = {}  # device index -> per-block partial sums of the loss kernel
+
+
+def mse_loss_grad(y: torch.Tensor, target: torch.Tensor, n_mean: int | None = None, grad_scale: float = 1.0):
+    """(loss, dy): loss = sum (y - target)^2 / n_mean (a device scalar) and dy = 2 (y - target) / n_mean * grad_scale,
+    from one pass over y and target.  n_mean defaults to y.numel()."""
+    _require(y, "y")
+    _require(target, "target")
+    if y.shape != target.shape:
+        raise RuntimeError("y and target must have the same shape")
+    n = y.numel()
+    if n == 0:
+        raise RuntimeError("mse_loss_grad needs at least one element")
+    lib = _lib.load()
+    idx = y.device.index if y.device.index is not None else torch.cuda.current_device()
+    ws = _mse_ws.get(idx)
+    if ws is None:
+        ws = _mse_ws[idx] = torch.empty(lib.chebykan_mse_workspace_bytes(), dtype=torch.uint8, device=y.device)
+    dy = torch.empty_like(y)
+    loss = torch.empty((), dtype=torch.float32, device=y.device)
+    with torch.cuda.device(y.device):
+        rc = lib.chebykan_mse_loss_grad(y.data_ptr(), target.data_ptr(), dy.data_ptr(), loss.data_ptr(), ws.data_ptr(),
+                                        ws.numel(), n, int(n_mean or n), float(grad_scale), _stream(y))
+    _lib.check(rc, "chebykan_mse_loss_grad")
+    return loss, dy
+
+
+def scale_by_device_scalar(dy: torch.Tensor, scalar: torch.Tensor) -> torch.Tensor:
+    """dy *= scalar (a one-element CUDA tensor) in place; a scalar of exactly 1 leaves dy untouched."""
+    _require(dy, "dy")
+    _require(scalar, "scalar")
+    if scalar.numel() != 1:
+        raise RuntimeError("scalar must hold one element")
+    with torch.cuda.device(dy.device):
+        rc = _lib.load().chebykan_scale_by_device_scalar(dy.data_ptr(), scalar.data_ptr(), dy.numel(), _stream(dy))
+    _lib.check(rc, "chebykan_scale_by_device_scalar")
+    return dy
+
+
 def sgd_step(param: torch.Tensor, grad: torch.Tensor, lr: float, grad_scale: float = 1.0) -> None:
     _require(param, "param")
     _require(grad, "grad")

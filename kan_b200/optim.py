@@ -29,8 +29,19 @@ class _Base:
                 raise RuntimeError("kan_b200 optimizers need contiguous fp32 CUDA parameters")
         self.lr = float(lr)
         self.grad_scale = 1.0
+        # opt-in: read the kernels' status word every `check_status_every` steps (a device synchronisation) and
+        # raise if a bounded wait gave up since the last check; 0 = never
+        self.check_status_every = 0
+        self._steps = 0
 
-    def zero_grad(self, set_to_none: bool = True) -> None:
+    def _after_step(self) -> None:
+        self._steps += 1
+        if self.check_status_every and self._steps % self.check_status_every == 0:
+            ops.check_status(self.params[0].device)
+
+    def zero_grad(self, set_to_none: bool = False) -> None:
+        """Zero the gradients in place by default (torch's optimizers drop them): a gradient that aliases a
+        ``dp.FlatGradBuffer`` stays attached to it."""
         for p in self.params:
             if p.grad is not None:
                 if set_to_none:
@@ -50,6 +61,7 @@ class SGD(_Base):
                 continue
             ops.sgd_step(p.data, p.grad.contiguous(), self.lr, self.grad_scale)
             _bump(p)
+        self._after_step()
 
 
 class Adam(_Base):
@@ -90,3 +102,4 @@ class Adam(_Base):
                 ops.adam_step(p.data, p.grad.contiguous(), st["exp_avg"], st["exp_avg_sq"], st["step"], self.lr,
                               self.betas[0], self.betas[1], self.eps, self.grad_scale)
             _bump(p)
+        self._after_step()

@@ -64,9 +64,14 @@ def test_fwd_bwd_vs_oracle(B, n_in, n_out, deg, dist):
     x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
     y_ref, dC_ref, dx_ref = o.forward_backward(x, coeffs, dy)
     y, dC, dx = run_all(x, coeffs, dy)
-    assert o.rel_l2(y, y_ref) <= FP32_TOL
-    assert o.rel_l2(dC, dC_ref) <= FP32_TOL
-    assert o.rel_l2(dx, dx_ref) <= FP32_TOL
+    for name, got, ref in (("y", y, y_ref), ("dC", dC, dC_ref), ("dx", dx, dx_ref)):
+        err = o.rel_l2(got, ref)
+        if not err <= FP32_TOL:
+            d = (got.double() - ref.double()).abs().reshape(got.shape[0], -1)
+            r, c = divmod(int(d.argmax()), d.shape[1])
+            pytest.fail(f"{name}: rel-L2 {err:.3e} > {FP32_TOL}; worst element [{r}, {c}]: "
+                        f"{float(got.reshape(got.shape[0], -1)[r, c])!r} vs {float(ref.reshape(ref.shape[0], -1)[r, c])!r}; "
+                        f"{int((d > 1e-3 * float(ref.abs().max())).sum())} elements off by more than 1e-3 of the largest value")
 
 
 def test_bitwise_repeatable():
@@ -75,6 +80,81 @@ def test_bitwise_repeatable():
     b = run_all(x, coeffs, dy)
     for u, v in zip(a, b):
         assert torch.equal(u, v)
+
+
+# 128-row forward tiles: launch_fwd_ffma picks fwd_ffma_kernel<2,2> (outputs padded to a multiple of 128) or
+# <2,1> (64-wide layers) once ceil(B/128) * column tiles reaches two CTAs per SM (296); every full-size fp32
+# run uses them
+LARGE_TILE_SHAPES = [
+    (5000, 64, 1024, 2, "normal"),       # <2,2>: 40 x 8 tiles
+    (6000, 1024, 1024, 8, "normal"),     # <2,2>: configuration 3's layer, ragged last row tile
+    (2432, 2048, 2048, 4, "normal"),     # <2,2>: configuration 4's layer, 19 x 16 tiles
+    (40000, 16, 64, 2, "normal"),        # <2,1>: 313 x 1 tiles
+    (40000, 64, 64, 32, "uniform3"),     # <2,1>: configuration 5's layer
+    (37999, 30, 70, 5, "normal"),        # <2,2> with ragged rows, inputs and outputs (70 -> 128 padded columns)
+]
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", LARGE_TILE_SHAPES)
+def test_forward_128_row_tiles_vs_oracle(B, n_in, n_out, deg, dist):
+    import math
+    n_pad = math.ceil(n_out / 64) * 64
+    col_tiles = n_pad // 128 if n_pad % 128 == 0 else n_pad // 64
+    assert math.ceil(B / 128) * col_tiles >= 296, "shape no longer reaches the 128-row tiles"
+    x, coeffs, _ = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    xd, cd = x.cuda(), coeffs.cuda()
+    packed = ops.pack_coeffs(cd, "fp32")
+    y, yw = guarded((B, n_out))
+    ops.forward(xd, packed, n_in, n_out, deg, "fp32", out=y)
+    torch.cuda.synchronize()
+    assert_guards_intact(y, yw)
+    assert o.rel_l2(y.cpu(), o.forward(x, coeffs)) <= FP32_TOL
+    y2 = ops.forward(xd, packed, n_in, n_out, deg, "fp32")
+    assert torch.equal(y, y2)
+
+
+def _first_mismatch(name, a, b, tile_rows, tile_cols):
+    """Where two runs of the same kernel differ: the message of the repeat test below."""
+    diff = (a != b) & ~(torch.isnan(a) & torch.isnan(b))
+    idx = diff.reshape(a.shape[0], -1).nonzero()
+    r, c = int(idx[0, 0]), int(idx[0, 1])
+    mx = float((a.double() - b.double()).abs().max())
+    return (f"{name}: {int(diff.sum())} of {a.numel()} elements differ between two runs; first at [{r}, {c}] "
+            f"(tile {r // tile_rows}, {c // tile_cols}): {float(a.reshape(a.shape[0], -1)[r, c])!r} vs "
+            f"{float(b.reshape(a.shape[0], -1)[r, c])!r}; max abs difference {mx:.3e}")
+
+
+# one launch plan per case: (4096, 1024, 1024, 8) = 1024 plain 64x64 forward tiles at two CTAs per SM, the dC kernel
+# writing straight into dC (592 tiles, no batch split) and the 64-row dx tiles; (1024, 2048, 2048, 4) the same kernels on
+# configuration 4's layer; (20000, 8, 8, 4) the batch-split dC path with its fixed-order reduction
+@pytest.mark.parametrize("B,n_in,n_out,deg,reps", [(4096, 1024, 1024, 8, 40), (1024, 2048, 2048, 4, 10),
+                                                   (20000, 8, 8, 4, 40), (6000, 1024, 1024, 8, 10)])
+def test_fp32_kernels_repeat_bit_for_bit(B, n_in, n_out, deg, reps):
+    """The fp32 kernels have a fixed summation order: `reps` runs in one process give identical bits."""
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, seed=B + n_in + deg)
+    xd, cd, dyd = x.cuda(), coeffs.cuda(), dy.cuda()
+    packed = ops.pack_coeffs(cd, "fp32")
+
+    def run():
+        y = torch.full((B, n_out), float("nan"), device="cuda")
+        dC = torch.full((n_in, n_out, deg + 1), float("nan"), device="cuda")
+        dx = torch.full((B, n_in), float("nan"), device="cuda")
+        ops.forward(xd, packed, n_in, n_out, deg, "fp32", out=y)
+        ops.bwd_dcoeff(xd, dyd, n_in, n_out, deg, "fp32", out=dC)
+        ops.bwd_dx(xd, dyd, cd, "fp32", out=dx)
+        return y, dC, dx
+
+    first = run()
+    y_ref, dC_ref, dx_ref = o.forward_backward(x, coeffs, dy)
+    for name, got, ref in zip(("y", "dC", "dx"), first, (y_ref, dC_ref, dx_ref)):
+        err = o.rel_l2(got.cpu(), ref)
+        assert err <= FP32_TOL, f"{name}: rel-L2 {err:.3e} against the oracle"
+    tiles = {"y": (64, 64), "dC": (128 // (deg + 1), 128 * (deg + 1)), "dx": (64, 128 // (deg + 1))}
+    for rep in range(1, reps):
+        again = run()
+        for name, a, b in zip(("y", "dC", "dx"), first, again):
+            if not torch.equal(a, b):
+                pytest.fail(f"run {rep}: " + _first_mismatch(name, a, b, *tiles[name]))
 
 
 def test_dcoeff_accumulate_and_split_batch():

@@ -141,6 +141,15 @@ def _dp_worker(rank, world, port, results):
         _, dC_full, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
         ok = o.rel_l2(p1.grad, dC_full) < 1e-6 and torch.allclose(p2.grad, torch.full((5,), 3.0))
         assert dp.world_info() == (rank, world)
+        # zero_grad(set_to_none=True) drops the aliases; backward then installs fresh tensors: the next
+        # all_reduce must still cover them
+        p1.grad = None
+        p2.grad = None
+        p1.grad = dC_local.clone()
+        p2.grad = torch.full((5,), float(rank + 1))
+        buf.all_reduce()
+        ok = ok and o.rel_l2(p1.grad, dC_full) < 1e-6 and torch.allclose(p2.grad, torch.full((5,), 3.0))
+        ok = ok and p1.grad.data_ptr() == buf.flat.data_ptr()
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -158,3 +167,44 @@ def test_flat_grad_allreduce_gloo_world2():
             p.join(timeout=180)
             assert p.exitcode == 0
         assert dict(results) == {0: True, 1: True}
+
+
+def test_ref_loader_search_order(tmp_path, monkeypatch):
+    """$KAN_REF first, then baseline/_ref/ under the repository, then the container's read-only mount."""
+    fake = tmp_path / "ref"
+    (fake / "kan" / "layers").mkdir(parents=True)
+    (fake / "kan" / "layers" / "chebykan.py").write_text("# marker\n")
+    monkeypatch.setenv("KAN_REF", str(fake))
+    cands = ref_loader.candidate_roots()
+    assert cands[0] == str(fake)
+    assert cands[1].endswith(os.path.join("baseline", "_ref")) and cands[2] == ref_loader.DEFAULT_MOUNT
+    assert ref_loader.reference_root() == str(fake)
+    monkeypatch.setenv("KAN_REF", str(tmp_path / "missing"))
+    assert ref_loader.reference_root() in (None, cands[1], cands[2])
+
+
+def test_status_word_raises_and_clears(monkeypatch):
+    """A non-zero status word (a bounded device-side wait that gave up) becomes a RuntimeError at the next check."""
+    from kan_b200 import ops
+    word = torch.tensor([3], dtype=torch.int32)          # a CPU stand-in for the device word
+    monkeypatch.setattr(ops, "_status", {0: word})
+    with pytest.raises(RuntimeError, match="role code 3"):
+        ops.check_status()
+    assert int(word) == 0                                  # cleared, so that the next check starts clean
+    ops.check_status()                                     # nothing pending: no error
+
+
+def test_flat_grad_buffer_survives_zero_grad_set_to_none():
+    """zero_grad(set_to_none=True) drops p.grad; the buffer re-attaches its views, keeping what backward produced."""
+    p1 = torch.nn.Parameter(torch.randn(3, 5))
+    p2 = torch.nn.Parameter(torch.randn(7))
+    buf = dp.FlatGradBuffer([p1, p2])
+    torch.optim.SGD([p1, p2], lr=0.1).zero_grad()          # torch's default: set_to_none=True
+    assert p1.grad is None and p2.grad is None
+    (p1.sum() * 2 + p2.sum() * 3).backward()               # installs fresh tensors that do not alias the buffer
+    assert p1.grad.data_ptr() != buf.flat.data_ptr()
+    buf.all_reduce()                                       # single process: no collective, but the views are re-attached
+    assert p1.grad.data_ptr() == buf.flat.data_ptr()
+    assert torch.equal(buf.flat[:15], torch.full((15,), 2.0)) and torch.equal(p2.grad, torch.full((7,), 3.0))
+    buf.zero()
+    assert float(buf.flat.abs().sum()) == 0.0 and p2.grad.data_ptr() == buf.flat[16:].data_ptr()
