@@ -1,6 +1,6 @@
-"""Two-GPU data-parallel checks over NCCL (skipped on a single-GPU box):
-sharded inference reproduces the single-GPU rows bit for bit, and the
-all-reduced coefficient gradient matches the full-batch gradient."""
+"""Data-parallel checks over NCCL on every GPU of the box (skipped on a single-GPU box): sharded inference
+reproduces the single-GPU rows bit for bit, the all-reduced coefficient gradient matches the full-batch
+gradient, and one sharded training step leaves identical coefficients on every rank."""
 import os
 
 import pytest
@@ -19,37 +19,78 @@ def _worker(rank, world, port, results):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     try:
         import kan_b200
-        from kan_b200 import dp
+        from kan_b200 import dp, ops
         from oracle import chebykan_oracle as o
+        ok = True
+        # --- fp32: gradient of the full batch = sum of the shards' gradients
         torch.manual_seed(0)
         layer = kan_b200.ChebyKANLayer(64, 48, 8).cuda()
         g = torch.Generator().manual_seed(1)
-        x = torch.randn(4096, 64, generator=g)
-        dy = torch.randn(4096, 48, generator=g)
-        b, e = dp.shard_rows(4096, rank, world)
+        B = 4096 + 8                                    # not a multiple of the world size: shards differ by one row
+        x = torch.randn(B, 64, generator=g)
+        dy = torch.randn(B, 48, generator=g)
+        b, e = dp.shard_rows(B, rank, world)
         buf = dp.FlatGradBuffer(layer.parameters())
         y = layer(x[b:e].cuda())
         y.backward(dy[b:e].cuda())
         buf.all_reduce()
         torch.cuda.synchronize()
         y_ref, dC_ref, _ = o.forward_backward(x, layer.cheby_coeffs.detach().cpu(), dy, need_dx=False)
-        ok_y = o.rel_l2(y.detach().cpu(), y_ref[b:e]) <= 1e-5
-        ok_g = o.rel_l2(layer.cheby_coeffs.grad.cpu(), dC_ref) <= 1e-5
-        results[rank] = bool(ok_y and ok_g)
+        ok = ok and o.rel_l2(y.detach().cpu(), y_ref[b:e]) <= 1e-5
+        ok = ok and o.rel_l2(layer.cheby_coeffs.grad.cpu(), dC_ref) <= 1e-5
+        # --- tensor-core forward: the shards' rows, concatenated, equal the single-GPU result bit for bit
+        # (a row's value does not depend on which tile or which GPU computes it)
+        for mode in ("bf16", "tf32"):
+            torch.manual_seed(2)
+            wide = kan_b200.ChebyKANLayer(256, 640, 4, math_mode=mode).cuda()
+            Bw = 2048 * world
+            xw = torch.randn(Bw, 256, generator=torch.Generator().manual_seed(3)).cuda()
+            with torch.no_grad():
+                full = wide(xw)
+                mine = wide(xw[rank * 2048:(rank + 1) * 2048].contiguous())
+            parts = [torch.empty_like(mine) for _ in range(world)]
+            dist.all_gather(parts, mine)
+            ok = ok and torch.equal(torch.cat(parts), full)
+        # --- one sharded SGD step (tf32): every rank ends with the same coefficients, equal to the oracle's step
+        torch.manual_seed(5)
+        model = kan_b200.ChebyKANLayer(32, 16, 6, math_mode="tf32").cuda()
+        start = model.cheby_coeffs.detach().cpu().clone()
+        Bt = 1024 * world
+        gt = torch.Generator().manual_seed(7)
+        xt, tt = torch.randn(Bt, 32, generator=gt), torch.randn(Bt, 16, generator=gt)
+        bt, et = dp.shard_rows(Bt, rank, world)
+        gbuf = dp.FlatGradBuffer(model.parameters())
+        opt = kan_b200.optim.SGD(list(model.parameters()), lr=0.5)
+        gbuf.zero()
+        loss = kan_b200.mse_loss(model(xt[bt:et].cuda()), tt[bt:et].cuda(), n_mean=Bt * 16)
+        loss.backward()
+        gbuf.all_reduce()
+        opt.step()
+        ops.check_status()
+        mine = model.cheby_coeffs.detach()
+        allw = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allw, mine)
+        ok = ok and all(torch.equal(allw[0], w) for w in allw)
+        cr = start.clone().requires_grad_(True)
+        torch.nn.functional.mse_loss(o.forward(xt, cr), tt).backward()
+        expect = start - 0.5 * cr.grad
+        ok = ok and o.rel_l2(mine.cpu() - start, expect - start) <= 2e-3
+        results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_data_parallel():
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_data_parallel_on_all_gpus():
+    world = min(torch.cuda.device_count(), 8)
     ctx = mp.get_context("spawn")
     with ctx.Manager() as mgr:
         results = mgr.dict()
         port = 29600 + os.getpid() % 2000
-        procs = [ctx.Process(target=_worker, args=(r, 2, port, results)) for r in range(2)]
+        procs = [ctx.Process(target=_worker, args=(r, world, port, results)) for r in range(world)]
         for p in procs:
             p.start()
         for p in procs:
             p.join(timeout=600)
             assert p.exitcode == 0
-        assert dict(results) == {0: True, 1: True}
+        assert dict(results) == {r: True for r in range(world)}
