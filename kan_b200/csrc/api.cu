@@ -1,5 +1,7 @@
 // C ABI of the library: argument validation and dispatch to the kernels.
 #include <math.h>
+#include <stdlib.h>
+#include <string.h>
 #include <mutex>
 #include "common.cuh"
 
@@ -47,6 +49,15 @@ static bool mode_ok(int mode) {
 static bool dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
     if (mode == CHEBYKAN_MODE_FP32 || !dx_tc_supported(B, in, out, deg)) return false;
     return mode != CHEBYKAN_MODE_FP32X3 || x3_dx_on_tensor_cores(B, in, out, deg);
+}
+// CHEBYKAN_NARROW_FWD=smem in the environment keeps narrow layers on the shared-memory-operand kernel (A/B timing
+// of the two forward kernels; read once)
+static bool narrow_forward_in_shared_memory() {
+    static const bool v = [] {
+        const char* e = getenv("CHEBYKAN_NARROW_FWD");
+        return e != nullptr && strcmp(e, "smem") == 0;
+    }();
+    return v;
 }
 // modes whose backward kernels are the fp32 ones
 static bool fp32_backward(int mode) {
@@ -116,6 +127,8 @@ int chebykan_fwd(const float* x, const void* packed, float* y, int64_t B, int64_
         return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg,
                                (cudaStream_t)stream);
     if (!status) return CHEBYKAN_EINVAL;
+    if (fwd_ts_supported(B, in, out, deg, mode) && !narrow_forward_in_shared_memory())
+        return launch_fwd_ts(x, reinterpret_cast<const void*>(packed), y, B, in, out, deg, mode, status, (cudaStream_t)stream);
     return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream);
 }
 

@@ -99,6 +99,10 @@ int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_
                     int64_t deg, cudaStream_t s);
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
                   int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion());
+// narrow layers (<= 128 outputs): the basis tile lives in tensor memory (fwd_ts.cu)
+bool fwd_ts_supported(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
+int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
+                  int32_t* status, cudaStream_t s);
 int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
 int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
                        int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,

@@ -62,6 +62,55 @@ def test_tc_forward_vs_oracle(mode, B, n_in, n_out, deg, dist):
         assert err > 1e-6
 
 
+# Narrow layers (at most 128 outputs, inputs a multiple of 4) run the kernel that keeps the generated basis tile in
+# tensor memory (tcgen05.st by the producers, tcgen05.mma with the A operand in TMEM): 64- and 128-column accumulators,
+# one (bf16) or two (tf32) row sub-tiles of 128 rows per CTA, x tiles by 128B-swizzled TMA boxes of 32 inputs.
+NARROW_SHAPES = [
+    # B, in, out, deg, dist
+    (1, 4, 16, 1, "normal"),              # a single row, one chunk of inputs
+    (127, 64, 64, 32, "uniform3"),        # less than one sub-tile
+    (129, 64, 64, 32, "uniform3"),        # second sub-tile holds one row
+    (257, 32, 64, 7, "normal"),           # third sub-tile (second CTA tile in tf32 mode)
+    (1000, 100, 65, 5, "normal"),         # ragged input block (100 = 3 x 32 + 4), 128-column accumulator, odd out
+    (1000, 64, 128, 9, "normal"),         # full 128 outputs
+    (3000, 200, 40, 0, "normal"),         # degree 0: one K block per input block
+    (3000, 36, 96, 1, "normal"),          # degree 1
+    (50000, 64, 64, 6, "normal"),         # more tiles than SMs: persistent loop, both accumulator buffers
+    (20000, 784, 64, 4, "sparse"),        # configuration 2's first layer shape at a large batch: 25 (13) input blocks
+    (70000, 64, 64, 32, "uniform3"),      # configuration 5's layer
+    (4096, 8, 8, 63, "normal"),           # highest tested degree: 64 K blocks from one input block
+]
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist", NARROW_SHAPES)
+def test_narrow_forward_with_basis_in_tensor_memory(mode, B, n_in, n_out, deg, dist):
+    x, coeffs, _ = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    y = run_fwd(x, coeffs, mode)
+    err = o.rel_l2(y, oracle_y(x, coeffs, mode))
+    assert err <= TC_TOL, err
+    if deg > 0:
+        assert err > 1e-6
+    # a block of rows that starts on a 256-row boundary gives the same bits as inside the full batch
+    if B >= 1024:
+        blk = run_fwd(x[512:1024].contiguous(), coeffs, mode)
+        assert torch.equal(y[512:1024], blk)
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+def test_narrow_forward_propagates_nan_rows(mode):
+    """A NaN input poisons exactly its own row (the tf32 rounding increment must not turn it into a number)."""
+    x, coeffs, _ = make_case(600, 64, 64, 5, seed=3)
+    x[17, 5] = float("nan")
+    x[300, 63] = float("nan")
+    xd = x.cuda()
+    y = ops.forward(xd, ops.pack_coeffs(coeffs.cuda(), mode), 64, 64, 5, mode).cpu()
+    bad = torch.isnan(y).any(dim=1)
+    assert bad[17] and bad[300] and int(bad.sum()) == 2
+    ok = ~bad
+    assert o.rel_l2(y[ok], oracle_y(x[ok], coeffs, mode)) <= TC_TOL
+
+
 @pytest.mark.parametrize("mode", ["bf16", "tf32"])
 def test_tc_bitwise_repeatable_and_row_block_invariant(mode):
     x, coeffs, _ = make_case(3000, 128, 256, 4, seed=77)
