@@ -18,10 +18,11 @@
 //   warp X           TMA loads of the x tiles (two slots per row sub-tile)
 //   4 epilogue warps tcgen05.ld of the accumulator -> y
 //
-// A K block is 32 TMEM columns (one degree of 32 tf32 or 64 bf16 inputs = four MMAs); a stage is KP K blocks, the
-// ring has two stages.  In tf32 mode a CTA works on two row sub-tiles of 128 rows at once (two sets of eight
-// producer warps, two accumulators): every W stage then feeds 256 rows, which halves the coefficient bytes the SM
-// pulls from L2 per row (the whole packed matrix is re-read for every row tile).
+// A K block is 32 TMEM columns (one degree of 32 tf32 or 64 bf16 inputs = four MMAs); a stage is KP K blocks of A in
+// TMEM plus the matching W panels in shared memory, handed over with one full and one empty barrier; the ring takes
+// whatever TMEM columns the accumulators leave.  A CTA may work on two row sub-tiles of 128 rows at once (two sets of
+// eight producer warps, two accumulators): every W stage then feeds 256 rows, which halves the coefficient bytes the
+// SM pulls from L2 per row (the whole packed matrix is re-read for every row tile).
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a role code in *status, drains and frees its TMEM.
 #include "tc_common.cuh"
@@ -34,12 +35,15 @@ using namespace tc;
 enum { TS_PRODUCER = 21, TS_TMA_W = 22, TS_MMA_A = 23, TS_MMA_B = 24, TS_MMA_ACC = 25, TS_EPILOGUE = 26, TS_X_LOAD = 27,
        TS_X_WAIT = 28 };
 
-template <int MODE, int BN>
+// NSUBM: row sub-tiles (of 128 rows) a CTA works on at once; KP: K blocks per stage; NACC: accumulator buffers.
+// The A ring takes the tensor-memory columns the accumulators leave: NSTG = (512 - NACC*NSUBM*BN) / (NSUBM*KP*32).
+#define TOTAL_CHECK(v) ((v) <= 232448)
+template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 struct TsCfg {
     static constexpr bool BF16 = MODE == CHEBYKAN_MODE_BF16;
-    static constexpr int NSUBM = BF16 ? 1 : 2;          // row sub-tiles (of 128 rows) a CTA works on at once
-    static constexpr int KP = BF16 ? 4 : 2;             // K blocks per stage
-    static constexpr int NSTG = 2;                      // A stages (TMEM)
+    static constexpr int NSUBM = NSUBM_;
+    static constexpr int KP = KP_;
+    static constexpr int NACC = NACC_;
     static constexpr int IB = BF16 ? 64 : 32;           // inputs per K block
     static constexpr int EPT = IB / 2;                  // inputs per producer thread (two threads share a row's block)
     static constexpr int XBOXES = IB / 32;              // x boxes of 32 fp32 per input block
@@ -47,23 +51,24 @@ struct TsCfg {
     static constexpr int EPI_WARP0 = NPW, MMA_WARP = NPW + 4, W_WARP = NPW + 5, X_WARP = NPW + 6;
     static constexpr int NUM_THREADS = (NPW + 8) * 32;  // + 4 epilogue, MMA, W, X, one idle (whole warpgroups)
     // register split (setmaxnreg): 65536 = producers + others
-    static constexpr int PRODUCER_REGS = BF16 ? 168 : 96;
-    static constexpr int OTHER_REGS = BF16 ? 88 : 48;
-    static constexpr int A_COLS = NSUBM * NSTG * KP * 32;
-    static constexpr int NACC = (2 * NSUBM * BN + A_COLS <= 512) ? 2 : 1;
+    static constexpr int PRODUCER_REGS = NSUBM == 1 ? 168 : 96;
+    static constexpr int OTHER_REGS = NSUBM == 1 ? 88 : 48;
     static constexpr int D_COLS = NACC * NSUBM * BN;
+    static constexpr int NSTG = (512 - D_COLS) / (NSUBM * KP * 32);      // A stages (TMEM)
+    static constexpr int A_COLS = NSUBM * NSTG * KP * 32;
     static constexpr int B_PANEL_BYTES = BN * 128;
     static constexpr int B_STAGE_BYTES = KP * B_PANEL_BYTES;
-    static constexpr int NSB = (131072 / B_STAGE_BYTES) > 6 ? 6 : (131072 / B_STAGE_BYTES);
+    static constexpr int NSB = NSTG;                    // one ring: stage s holds the W panels and the A columns of the same K blocks
     static constexpr int X_SLOT_BYTES = XBOXES * 128 * 128;       // 128 rows x 128 bytes per box
     static constexpr int NXS = 2;                                 // x slots per sub-tile
     static constexpr int B_OFFSET = 0;
     static constexpr int X_OFFSET = NSB * B_STAGE_BYTES;
     static constexpr int BAR_OFFSET = X_OFFSET + NSUBM * NXS * X_SLOT_BYTES;
-    // fullA[NSTG] emptyA[NSTG] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] x_full[NSUBM*NXS] x_empty[NSUBM*NXS] drain
-    static constexpr int NUM_BARS = 2 * NSTG + 2 * NSB + 4 + 2 * NSUBM * NXS + 1;
+    // full[NSTG] empty[NSTG] acc_full[2] acc_empty[2] x_full[NSUBM*NXS] x_empty[NSUBM*NXS] drain
+    static constexpr int NUM_BARS = 2 * NSTG + 4 + 2 * NSUBM * NXS + 1;
+    static_assert(TOTAL_CHECK(BAR_OFFSET + NUM_BARS * 8 + 16 + 1024), "shared memory");
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
-    static_assert(D_COLS + A_COLS <= 512, "tensor memory holds 512 columns");
+    static_assert(NSTG >= 2 && D_COLS + A_COLS <= 512, "tensor memory holds 512 columns");
 };
 
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -79,6 +84,12 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
+}
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 template <int MODE>
@@ -96,11 +107,11 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
     }
 }
 
-template <int MODE, int BN>
-__global__ void __launch_bounds__(TsCfg<MODE, BN>::NUM_THREADS, 1)
+template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
+__global__ void __launch_bounds__(TsCfg<MODE, BN, NSUBM_, KP_, NACC_>::NUM_THREADS, 1)
 fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int64_t num_tiles, int32_t* status) {
-    using C = TsCfg<MODE, BN>;
+    using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     constexpr int NSUBM = C::NSUBM, KP = C::KP, NSTG = C::NSTG, NSB = C::NSB, NACC = C::NACC, NXS = C::NXS;
     constexpr int IB = C::IB, EPT = C::EPT;
     constexpr uint32_t FMT = C::BF16 ? 1u : 2u;
@@ -111,15 +122,15 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
     const uint32_t bars = smem_base + C::BAR_OFFSET;
-    auto fullA = [&](int s) { return bars + 8u * s; };
-    auto emptyA = [&](int s) { return bars + 8u * (NSTG + s); };
-    auto fullB = [&](int s) { return bars + 8u * (2 * NSTG + s); };
-    auto emptyB = [&](int s) { return bars + 8u * (2 * NSTG + NSB + s); };
-    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NSTG + 2 * NSB + a); };
-    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NSTG + 2 * NSB + 2 + a); };
-    auto x_full = [&](int sub, int slot) { return bars + 8u * (2 * NSTG + 2 * NSB + 4 + sub * NXS + slot); };
-    auto x_empty = [&](int sub, int slot) { return bars + 8u * (2 * NSTG + 2 * NSB + 4 + NSUBM * NXS + sub * NXS + slot); };
-    const uint32_t drain_bar = bars + 8u * (2 * NSTG + 2 * NSB + 4 + 2 * NSUBM * NXS);
+    // full(s): all producer warps have stored the stage's A columns and the stage's W panels have landed;
+    // empty(s): the MMAs that read the stage have retired
+    auto full = [&](int s) { return bars + 8u * s; };
+    auto empty = [&](int s) { return bars + 8u * (NSTG + s); };
+    auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NSTG + a); };
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NSTG + 2 + a); };
+    auto x_full = [&](int sub, int slot) { return bars + 8u * (2 * NSTG + 4 + sub * NXS + slot); };
+    auto x_empty = [&](int sub, int slot) { return bars + 8u * (2 * NSTG + 4 + NSUBM * NXS + sub * NXS + slot); };
+    const uint32_t drain_bar = bars + 8u * (2 * NSTG + 4 + 2 * NSUBM * NXS);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + C::BAR_OFFSET + C::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + C::BAR_OFFSET + C::NUM_BARS * 8 + 4);
 
@@ -128,8 +139,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const int nkb = n_iblk * dp1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < NSTG; ++s) { mbar_init(fullA(s), C::NPW); mbar_init(emptyA(s), 1); }
-        for (int s = 0; s < NSB; ++s) { mbar_init(fullB(s), 1); mbar_init(emptyB(s), 1); }
+        for (int s = 0; s < NSTG; ++s) { mbar_init(full(s), C::NPW + 1); mbar_init(empty(s), 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), 4); }
         for (int sub = 0; sub < NSUBM; ++sub)
             for (int slot = 0; slot < NXS; ++slot) { mbar_init(x_full(sub, slot), 1); mbar_init(x_empty(sub, slot), 8); }
@@ -178,7 +188,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 for (int c = 0; c < 16; ++c) w[c] = tf32_rna(v[c % EPT], inc);
             }
             if (kpos == 0) {
-                const bool ok = mbar_wait(emptyA(s), ph ^ 1u, abort_flag, status, TS_PRODUCER);
+                const bool ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_PRODUCER);
                 if (!__all_sync(0xffffffffu, ok)) return false;
                 tc_fence_after();
             }
@@ -190,7 +200,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(fullA(s));
+            if (lane == 0) mbar_arrive(full(s));
             if (++s == NSTG) { s = 0; ph ^= 1u; }
             return true;
         };
@@ -255,12 +265,12 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
                 for (int kb = 0; kb < nkb && alive; kb += KP) {
                     const int np = (nkb - kb < KP) ? nkb - kb : KP;
-                    if (!mbar_wait(emptyB(s), ph ^ 1u, abort_flag, status, TS_TMA_W)) { alive = false; break; }
+                    if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_TMA_W)) { alive = false; break; }
                     const uint32_t dst = smem_base + C::B_OFFSET + s * C::B_STAGE_BYTES;
-                    mbar_arrive_expect_tx(fullB(s), (uint32_t)(np * C::B_PANEL_BYTES));
+                    mbar_arrive_expect_tx(full(s), (uint32_t)(np * C::B_PANEL_BYTES));
                     for (int p = 0; p < np; ++p)
-                        tma_load_2d(dst + p * C::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, 0, fullB(s));
-                    if (++s == NSB) { s = 0; ph ^= 1u; }
+                        tma_load_2d(dst + p * C::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, 0, full(s));
+                    if (++s == NSTG) { s = 0; ph ^= 1u; }
                 }
             }
             if (!alive) {
@@ -293,47 +303,63 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         }
     } else if (warp == C::MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
-        if (lane == 0) {
+        // The whole warp runs this loop in lock step and only the MMA / commit instructions themselves are executed by
+        // one elected lane.  The operands of tcgen05.mma live in uniform registers: inside a divergent region (a loop
+        // under `if (lane == 0)`) the compiler has to move every address from a vector register first, which costs
+        // more than the 32 cycles an N = 64 MMA occupies the tensor pipe.  Operand addresses are per-stage bases plus
+        // compile-time offsets (the descriptor's high word never changes; its low word is a 32-bit add), the accumulate
+        // predicate is a constant except for a tile's very first MMA, and a stage takes one wait and one commit.
+        {
+            const bool elected = elect_one_sync();
             int sa = 0; uint32_t pha = 0;
-            int sb = 0; uint32_t phb = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
+            const uint64_t desc0 = make_smem_desc(smem_base + C::B_OFFSET);
+            const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
+            auto issue = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool acc_const_one, uint32_t acc_dyn) {
+                uint64_t b_desc;
+                asm volatile("mov.b64 %0, {%1, %2};" : "=l"(b_desc) : "r"(b_lo), "r"(desc_hi));
+                if (elected) {
+                    if (acc_const_one) umma_ts<MODE>(d_tmem, a_tmem, b_desc, IDESC, 1u);
+                    else umma_ts<MODE>(d_tmem, a_tmem, b_desc, IDESC, acc_dyn);
+                }
+            };
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, TS_MMA_ACC)) { alive = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, TS_MMA_ACC))) { alive = false; break; }
                 tc_fence_after();
+                const uint32_t d0 = tmem_base + D_COL0 + (uint32_t)(acc * NSUBM * BN);
                 for (int kb = 0; kb < nkb && alive; kb += KP) {
                     const int np = (nkb - kb < KP) ? nkb - kb : KP;
-                    if (!mbar_wait(fullA(sa), pha, abort_flag, status, TS_MMA_A)) { alive = false; break; }
-                    if (!mbar_wait(fullB(sb), phb, abort_flag, status, TS_MMA_B)) { alive = false; break; }
+                    const uint32_t a0 = tmem_base + A_COL0 + (uint32_t)(sa * KP * 32);
+                    const uint32_t b0 = desc_lo0 + (uint32_t)((sa * C::B_STAGE_BYTES) >> 4);
+                    if (!__all_sync(0xffffffffu, mbar_wait(full(sa), pha, abort_flag, status, TS_MMA_A))) { alive = false; break; }
                     tc_fence_after();
-                    const uint32_t b_addr = smem_base + C::B_OFFSET + sb * C::B_STAGE_BYTES;
 #pragma unroll
                     for (int p = 0; p < KP; ++p) {
-                        if (p >= np) break;
-                        const uint64_t b_desc = make_smem_desc(b_addr + p * C::B_PANEL_BYTES);
+                        if (p < np) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {          // 4 x 8 columns of A, 4 x 32 bytes of each W row
+                            for (int k = 0; k < 4; ++k) {          // 4 x 8 columns of A, 4 x 32 bytes of each W row
 #pragma unroll
-                            for (int sub = 0; sub < NSUBM; ++sub) {
-                                const uint32_t d_tmem = tmem_base + D_COL0 + (uint32_t)((acc * NSUBM + sub) * BN);
-                                const uint32_t a_tmem = tmem_base + A_COL0 + (uint32_t)(((sub * NSTG + sa) * KP + p) * 32 + k * 8);
-                                umma_ts<MODE>(d_tmem, a_tmem, b_desc + 2 * k, IDESC, (uint32_t)((kb | p | k) != 0));
+                                for (int sub = 0; sub < NSUBM; ++sub)
+                                    issue(d0 + (uint32_t)(sub * BN), a0 + (uint32_t)(sub * NSTG * KP * 32 + p * 32 + k * 8),
+                                          b0 + (uint32_t)((p * C::B_PANEL_BYTES) >> 4) + 2u * k, (p | k) != 0, (uint32_t)(kb != 0));
                             }
                         }
                     }
-                    umma_commit(emptyA(sa));
-                    umma_commit(emptyB(sb));
+                    if (elected) umma_commit(empty(sa));
+                    __syncwarp();
                     if (++sa == NSTG) { sa = 0; pha ^= 1u; }
-                    if (++sb == NSB) { sb = 0; phb ^= 1u; }
                 }
-                if (alive) umma_commit(acc_full_bar(acc));
+                if (alive && elected) umma_commit(acc_full_bar(acc));
+                __syncwarp();
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
             }
-            if (!alive) {
+            if (!alive && elected) {
                 umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
+            __syncwarp();
         }
     } else if (warp >= C::EPI_WARP0 && warp < C::EPI_WARP0 + 4) {
         // ------------------------------ epilogue ------------------------------
@@ -388,16 +414,16 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
 }
 
-template <int MODE, int BN>
+template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 int launch_ts(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, float* y, int64_t B, int in, int out, int dp1,
               int32_t* status, cudaStream_t s) {
-    using C = TsCfg<MODE, BN>;
+    using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     static bool attr_set[64] = {false};
     static int sms[64] = {0};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return CHEBYKAN_EINVAL;
-    auto kernel = fwd_ts_kernel<MODE, BN>;
+    auto kernel = fwd_ts_kernel<MODE, BN, NSUBM_, KP_, NACC_>;
     if (!attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::TOTAL));
         if (rc) return rc;
@@ -452,12 +478,15 @@ int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t i
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
     }
     const int dp1 = (int)deg + 1;
+#ifdef TS_PROBE_VARIANTS
+    TS_PROBE_VARIANTS
+#endif
     if (mode == CHEBYKAN_MODE_BF16) {
-        if (bn == 64) return launch_ts<CHEBYKAN_MODE_BF16, 64>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
-        return launch_ts<CHEBYKAN_MODE_BF16, 128>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+        if (bn == 64) return launch_ts<CHEBYKAN_MODE_BF16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+        return launch_ts<CHEBYKAN_MODE_BF16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
     }
-    if (bn == 64) return launch_ts<CHEBYKAN_MODE_TF32, 64>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
-    return launch_ts<CHEBYKAN_MODE_TF32, 128>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+    if (bn == 64) return launch_ts<CHEBYKAN_MODE_TF32, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+    return launch_ts<CHEBYKAN_MODE_TF32, 128, 1, 4, 1>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
 }
 
 }  // namespace chebykan
