@@ -332,43 +332,66 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
         }
     } else if (warp == DC_MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
-        if (lane == 0 && rank == 0) {
+        // The warp runs the loop in lock step; one elected lane executes the MMAs and commits (see elect_one_sync).
+        // Operand descriptors are per-stage low words plus compile-time offsets.
+        if (rank == 0) {
+            const bool elected = elect_one_sync();
             bool alive = true;
+            const uint64_t a_desc0 = make_smem_desc(smem_base);
+            const uint64_t b_desc0 = make_smem_desc_mn(smem_base + L::A_STAGE);
+            const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
             // slots of the pair: the odd CTA's tile may hold fewer (or no) inputs, its MMAs run all the same
+            const int mt_used = (ti * dp1 + 127) / 128;       // M tiles past the CTA's last slot stay unused
+            int nsub_used = 1;                                // 256-wide halves that hold real outputs
+            for (int sub = 1; sub < L::NSUB; ++sub)
+                if (n0 + sub * L::BNI < out) nsub_used = sub + 1;
+            int s = 0; uint32_t ph = 0;
             for (int kb = 0; kb < nkb; ++kb) {
-                const int s = kb % NS;
-                const uint32_t ph = (uint32_t)((kb / NS) & 1);
-                if (!mbar_wait(full(s), ph, abort_flag, status, DST_MMA_A)) { alive = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(full(s), ph, abort_flag, status, DST_MMA_A))) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t a_addr = smem_base + s * L::STAGE;
+                const uint32_t a_lo = (uint32_t)a_desc0 + (uint32_t)((s * L::STAGE) >> 4);
+                const uint32_t b_lo = (uint32_t)b_desc0 + (uint32_t)((s * L::STAGE) >> 4);
+                const uint32_t first = (uint32_t)(kb != 0);
 #pragma unroll
                 for (int mt = 0; mt < L::MT; ++mt) {
-                    if (mt * 128 >= ti * dp1) break;          // M tiles past the CTA's last slot stay unused
-                    const uint64_t a_desc = make_smem_desc(a_addr + mt * DC_A_TILE);
+                    if (mt < mt_used) {
 #pragma unroll
-                    for (int sub = 0; sub < L::NSUB; ++sub) {
-                        if (sub > 0 && n0 + sub * L::BNI >= out) break;   // no real outputs in this half
-                        // column blocks of 32 outputs are 4096 B apart
-                        const uint64_t b_desc = make_smem_desc_mn(a_addr + L::A_STAGE + sub * (L::BNI / 32 / CG) * 4096);
+                        for (int sub = 0; sub < L::NSUB; ++sub) {
+                            if (sub < nsub_used) {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) { // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
-                            if (CG == 2)
-                                umma2<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN + sub * L::BNI, a_desc + 2 * k,
-                                                          b_desc + 64 * k, IDESC, (uint32_t)((kb | k) != 0));
-                            else
-                                umma<CHEBYKAN_MODE_TF32>(tmem_base + mt * BN + sub * L::BNI, a_desc + 2 * k,
-                                                         b_desc + 64 * k, IDESC, (uint32_t)((kb | k) != 0));
+                                for (int k = 0; k < 4; ++k) { // 8 batch rows per MMA: +32 B in A's rows, +1024 B in B
+                                    // A: M tiles are DC_A_TILE apart; B: column blocks of 32 outputs are 4096 B apart
+                                    const uint64_t ad = desc_from_words(a_lo + (uint32_t)((mt * DC_A_TILE) >> 4) + 2u * k, a_hi);
+                                    const uint64_t bd = desc_from_words(
+                                        b_lo + (uint32_t)((sub * (L::BNI / 32 / CG) * 4096) >> 4) + 64u * k, b_hi);
+                                    const uint32_t d_tmem = tmem_base + (uint32_t)(mt * BN + sub * L::BNI);
+                                    if (elected) {
+                                        if (CG == 2) {
+                                            if (k != 0) umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
+                                            else umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, first);
+                                        } else {
+                                            if (k != 0) umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
+                                            else umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, first);
+                                        }
+                                    }
+                                }
+                            }
                         }
                     }
                 }
-                if (CG == 2) umma2_commit_both(empty(s)); else umma_commit(empty(s));
+                if (elected) { if (CG == 2) umma2_commit_both(empty(s)); else umma_commit(empty(s)); }
+                __syncwarp();
+                if (++s == NS) { s = 0; ph ^= 1u; }
             }
-            if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar); else umma_commit(acc_full_bar); }
-            else {
-                if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
-                const uint64_t t0 = globaltimer_ns();
-                while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
+            if (elected) {
+                if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar); else umma_commit(acc_full_bar); }
+                else {
+                    if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
+                    const uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
+                }
             }
+            __syncwarp();
         }
     }
 

@@ -190,38 +190,52 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             }
         }
     } else if (warp == DX_MMA_WARP) {
-        if (lane == 0 && rank == 0) {
+        // The warp runs the loop in lock step; one elected lane executes the MMAs and commits (see elect_one_sync).
+        if (rank == 0) {
+            const bool elected = elect_one_sync();
             int s = 0; uint32_t ph = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
+            const uint64_t a_desc0 = make_smem_desc(smem_base);
+            const uint64_t b_desc0 = make_smem_desc(smem_base + DX_A_STAGE);
+            const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
-                if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, XST_MMA_ACC)) { alive = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, XST_MMA_ACC))) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * DX_BN);
                 for (int kb = 0; kb < nkb; ++kb) {
-                    if (!mbar_wait(full_bar(s), ph, abort_flag, status, XST_MMA_FULL)) { alive = false; break; }
+                    if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abort_flag, status, XST_MMA_FULL))) { alive = false; break; }
                     tc_fence_after();
-                    const uint32_t a_addr = smem_base + s * DX_STAGE;
-                    const uint64_t a_desc = make_smem_desc(a_addr);
-                    const uint64_t b_desc = make_smem_desc(a_addr + DX_A_STAGE);
+                    const uint32_t a_lo = (uint32_t)a_desc0 + (uint32_t)((s * DX_STAGE) >> 4);
+                    const uint32_t b_lo = (uint32_t)b_desc0 + (uint32_t)((s * DX_STAGE) >> 4);
+                    const uint32_t later = (uint32_t)(kb != 0);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        if (CG == 2) umma2<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                               (uint32_t)((kb | k) != 0));
-                        else umma<CHEBYKAN_MODE_TF32>(d_tmem, a_desc + 2 * k, b_desc + 2 * k, IDESC,
-                                                      (uint32_t)((kb | k) != 0));
+                        const uint64_t ad = desc_from_words(a_lo + 2u * k, a_hi), bd = desc_from_words(b_lo + 2u * k, b_hi);
+                        if (elected) {
+                            if (CG == 2) {
+                                if (k != 0) umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
+                                else umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, later);
+                            } else {
+                                if (k != 0) umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
+                                else umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, later);
+                            }
+                        }
                     }
-                    if (CG == 2) umma2_commit_both(empty_bar(s)); else umma_commit(empty_bar(s));
+                    if (elected) { if (CG == 2) umma2_commit_both(empty_bar(s)); else umma_commit(empty_bar(s)); }
+                    __syncwarp();
                     if (++s == NS) { s = 0; ph ^= 1u; }
                 }
-                if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
+                if (alive && elected) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
+                __syncwarp();
                 if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
             }
-            if (!alive) {
+            if (!alive && elected) {
                 if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
+            __syncwarp();
         }
     } else {
         // ------------------------------ epilogue ------------------------------

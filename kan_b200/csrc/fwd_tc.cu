@@ -38,22 +38,9 @@
 // full/empty mbarriers.  With NSUB*BN <= 256 two accumulator buffers
 // alternate, so the epilogue overlaps the next tile's main loop.
 //
-// Split contraction ("stream-K", the SK template flag, CTA-pair kernel only).  A launch whose tile count is not a
-// multiple of the number of CTA pairs leaves part of the last wave idle (65536 rows sharded over 8 GPUs: 64 tiles for
-// 74 pairs).  With SK the work is cut in units of one input block of one tile, every pair takes an equal, contiguous
-// run of units, and a tile whose input blocks are spread over two or three pairs is summed through y itself: the
-// pair holding the tile's last input blocks stores its partial sums and raises a flag, each pair before it waits for
-// that flag, adds its own accumulator to what y holds, and raises its own flag, until the pair holding the first
-// input blocks has written the final values.  The order of the additions is fixed by the partition, so results are
-// repeatable; they differ in the last bits from an unsplit launch.  Flags live in a small array inside the library,
-// are cleared by the CTA that consumes them, and every wait on them is bounded like the mbarrier waits.
-//
 // Phi never reaches device memory.  Every mbarrier wait is bounded: when one
 // gives up the kernel raises an abort flag, records a code in *status, drains
 // what it has in flight, frees its TMEM and returns.
-#include <stdlib.h>
-#include <atomic>
-#include <mutex>
 #include "tc_common.cuh"
 
 namespace chebykan {
@@ -75,39 +62,7 @@ constexpr int A_PANEL_BYTES = BM * 128;     // one K block of A: 128 rows x 128 
 
 // status codes recorded by a wait that gave up
 enum { ST_PRODUCER = 1, ST_TMA = 2, ST_MMA_A = 3, ST_MMA_B = 4, ST_MMA_ACC = 5, ST_EPILOGUE = 6, ST_X_LOAD = 7,
-       ST_X_WAIT = 8, ST_SPLIT_FLAG = 9, ST_SPLIT_SYNC = 10 };
-
-// Split-contraction flags: SK_SLOTS launches may be in flight on one device at a time, each with one flag per CTA.
-constexpr int SK_SLOTS = 64;
-constexpr int SK_MAX_CTAS = 160;
-constexpr int SK_MAX_SEGMENTS = 4;        // a tile is spread over at most this many CTA pairs
-__device__ uint32_t g_sk_flags[SK_SLOTS * SK_MAX_CTAS];
-
-// The run of work a CTA (pair) walks through: whole tiles strided over the grid, or - SK - a contiguous range of
-// (tile, input block) units.  Every role iterates the same sequence.
-template <bool SK>
-struct SegIter {
-    int64_t a, a_end, stride;
-    int n_iblk;
-    __device__ SegIter(int64_t unit, int64_t nunits, int64_t num_tiles, int64_t sk_units, int n_iblk_) : n_iblk(n_iblk_) {
-        if (SK) { a = unit * sk_units / nunits; a_end = (unit + 1) * sk_units / nunits; stride = 0; }
-        else    { a = unit; a_end = num_tiles; stride = nunits; }
-    }
-    // next segment: input blocks [ib0, ib1) of `tile`
-    __device__ bool next(int64_t& tile, int& ib0, int& ib1) {
-        if (a >= a_end) return false;
-        if (SK) {
-            tile = a / n_iblk;
-            ib0 = (int)(a - tile * n_iblk);
-            const int64_t rem = a_end - a;
-            ib1 = (rem < n_iblk - ib0) ? ib0 + (int)rem : n_iblk;
-            a += ib1 - ib0;
-        } else {
-            tile = a; ib0 = 0; ib1 = n_iblk; a += stride;
-        }
-        return true;
-    }
-};
+       ST_X_WAIT = 8 };
 
 // PP = 2: every K block is staged twice, as a tf32 head and a tf32 tail (the fp32-grade FP32X3 mode)
 template <int BN, int NSUB, int CG = 1, int PP = 1>
@@ -132,18 +87,18 @@ struct Smem {
     static constexpr int GB_OFFSET = X_OFFSET + X_BYTES;               // LayerNorm gamma | beta of the input block
     static constexpr int GB_BYTES = 512;                              // 2 x 64 fp32
     static constexpr int BAR_OFFSET = GB_OFFSET + GB_BYTES;
-    // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain x_full x_empty epi_sync
-    static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 8;
+    // barriers: fullA[NSA] emptyA[NSA] fullB[NSB] emptyB[NSB] acc_full[2] acc_empty[2] drain x_full x_empty
+    static constexpr int NUM_BARS = 2 * NSA + 2 * NSB + 7;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;  // +1024 alignment slack
     static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
-template <int MODE, int BN, int NSUB, bool LN, int CG, bool SK = false>
+template <int MODE, int BN, int NSUB, bool LN, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
-              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad, int64_t sk_units, uint32_t* sk_flags) {
+              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad) {
     constexpr bool X3 = MODE == CHEBYKAN_MODE_FP32X3;
     constexpr int PP = X3 ? 2 : 1;
     using L = Smem<BN, NSUB, CG, PP>;
@@ -169,11 +124,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const uint32_t drain_bar = bars + 8u * (2 * NSA + 2 * NSB + 4);
     const uint32_t x_full_bar = bars + 8u * (2 * NSA + 2 * NSB + 5);
     const uint32_t x_empty_bar = bars + 8u * (2 * NSA + 2 * NSB + 6);
-    const uint32_t epi_sync_bar = bars + 8u * (2 * NSA + 2 * NSB + 7);
     constexpr uint32_t X_TILE_BYTES = BM * IB * 4;
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 4);
-    volatile int* sk_ok = reinterpret_cast<volatile int*>(smem_gen + L::BAR_OFFSET + L::NUM_BARS * 8 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // CTA pair: the even CTA (rank 0) issues every MMA; each CTA owns 128 of the pair's 256 rows
@@ -195,7 +148,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         mbar_init(drain_bar, 1);
         mbar_init(x_full_bar, 1);
         mbar_init(x_empty_bar, NUM_PRODUCER_WARPS);
-        mbar_init(epi_sync_bar, 4);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -289,11 +241,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             return true;
         };
 
-        SegIter<SK> it(unit, nunits, num_tiles, sk_units, n_iblk);
-        int64_t tile; int ib0, ib1;
-        while (alive && it.next(tile, ib0, ib1)) {
+        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
             const int64_t m0 = (tile / n_tiles) * (BM * CG) + rank * BM;
-            kb_left = (ib1 - ib0) * dp1;
+            kb_left = nkb;
             // fused LayerNorm of the input rows: per-row mean and 1/std from the previous layer's sums
             float ln_mean[4], ln_rstd[4];
             if (LN && ln.stats_in != nullptr) {
@@ -309,7 +259,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     ln_mean[j] = -mean * ln_rstd[j];       // (x - mean) * rstd as one fma
                 }
             }
-            for (int ib = ib0; ib < ib1 && alive; ++ib) {
+            for (int ib = 0; ib < n_iblk && alive; ++ib) {
                 const int i_base = ib * IB + c * CH;
                 float ln_g[CH], ln_b[CH];
                 if (LN && ln.stats_in != nullptr && !use_x_tma) {
@@ -417,13 +367,10 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool alive = true;
-            SegIter<SK> it(unit, nunits, num_tiles, sk_units, n_iblk);
-            int64_t tile; int ib0, ib1;
-            while (alive && it.next(tile, ib0, ib1)) {
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 const int n0 = (int)(tile % n_tiles) * BNT;
-                const int kb_hi = ib1 * dp1;
-                for (int kb = ib0 * dp1; kb < kb_hi && alive; kb += KP) {
-                    const int np = (kb_hi - kb < KP) ? kb_hi - kb : KP;     // K blocks in this stage
+                for (int kb = 0; kb < nkb && alive; kb += KP) {
+                    const int np = (nkb - kb < KP) ? nkb - kb : KP;     // K blocks in this stage
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub) {
                         if (!mbar_wait(emptyB(s), ph ^ 1u, abort_flag, status, ST_TMA)) { alive = false; break; }
@@ -456,11 +403,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         if (lane == 0 && use_x_tma) {
             uint32_t xph = 0;
             bool alive = true;
-            SegIter<SK> it(unit, nunits, num_tiles, sk_units, n_iblk);
-            int64_t tile; int ib0, ib1;
-            while (alive && it.next(tile, ib0, ib1)) {
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 const int m0 = (int)((tile / n_tiles) * (BM * CG) + rank * BM);
-                for (int ib = ib0; ib < ib1; ++ib) {
+                for (int ib = 0; ib < n_iblk; ++ib) {
                     if (!mbar_wait(x_empty_bar, xph ^ 1u, abort_flag, status, ST_X_LOAD)) { alive = false; break; }
                     if (LN && ln.stats_in != nullptr) {
                         // gamma | beta of this block of inputs ride on the same barrier (plain bulk copies)
@@ -483,66 +428,81 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------ MMA issue ------------------------------
-        if (lane == 0 && rank == 0) {
+        // The warp runs the loop in lock step; one elected lane executes the MMAs and commits (see elect_one_sync).
+        // Operand descriptors are per-stage low words plus compile-time offsets.
+        if (rank == 0) {
+            const bool elected = elect_one_sync();
             int sa = 0; uint32_t pha = 0;
             int sb = 0; uint32_t phb = 0;
             int acc = 0; uint32_t acc_ph = 0;
             bool alive = true;
-            SegIter<SK> it(unit, nunits, num_tiles, sk_units, n_iblk);
-            int64_t tile; int ib0, ib1;
-            while (alive && it.next(tile, ib0, ib1)) {
-              const int kb_hi = ib1 * dp1;
-              for (int kb0 = ib0 * dp1; kb0 < kb_hi && alive; kb0 += kb_chunk) {     // one accumulator per chunk of K blocks
-                const int kb_end = (kb_hi - kb0 < kb_chunk) ? kb_hi : kb0 + kb_chunk;
-                if (!mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC)) { alive = false; break; }
+            const uint64_t a_desc0 = make_smem_desc(smem_base + L::A_OFFSET);
+            const uint64_t b_desc0 = make_smem_desc(smem_base + L::B_OFFSET);
+            const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+            for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+              for (int kb0 = 0; kb0 < nkb && alive; kb0 += kb_chunk) {     // one accumulator per chunk of K blocks
+                const int kb_end = (nkb - kb0 < kb_chunk) ? nkb : kb0 + kb_chunk;
+                if (!__all_sync(0xffffffffu, mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, ST_MMA_ACC))) { alive = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BNT);
                 for (int kb = kb0; kb < kb_end && alive; kb += KP) {
                     const int np = (kb_end - kb < KP) ? kb_end - kb : KP;     // K blocks in this stage
-                    if (!mbar_wait(fullA(sa), pha, abort_flag, status, ST_MMA_A)) { alive = false; break; }
-                    const uint32_t a_addr = smem_base + L::A_OFFSET + sa * A_STAGE_BYTES;
+                    if (!__all_sync(0xffffffffu, mbar_wait(fullA(sa), pha, abort_flag, status, ST_MMA_A))) { alive = false; break; }
+                    const uint32_t a_lo = (uint32_t)a_desc0 + (uint32_t)((sa * A_STAGE_BYTES) >> 4);
+                    const uint32_t later = (uint32_t)(kb != kb0);       // 0 only for the first stage of an accumulator
 #pragma unroll
                     for (int sub = 0; sub < NSUB; ++sub) {
-                        if (!mbar_wait(fullB(sb), phb, abort_flag, status, ST_MMA_B)) { alive = false; break; }
+                        if (!__all_sync(0xffffffffu, mbar_wait(fullB(sb), phb, abort_flag, status, ST_MMA_B))) { alive = false; break; }
                         tc_fence_after();
-                        const uint32_t b_addr = smem_base + L::B_OFFSET + sb * L::B_STAGE_BYTES;
+                        const uint32_t b_lo = (uint32_t)b_desc0 + (uint32_t)((sb * L::B_STAGE_BYTES) >> 4);
 #pragma unroll
                         for (int p = 0; p < KP; ++p) {
-                            if (p >= np) break;
-                            const uint64_t a_desc = make_smem_desc(a_addr + p * (PP * A_PANEL_BYTES));
-                            const uint64_t b_desc = make_smem_desc(b_addr + p * (PP * L::B_PANEL_BYTES));
-                            auto mma = [&](uint64_t ad, uint64_t bd, uint32_t accumulate) {
-                                if (CG == 2) umma2<MODE>(d_tmem + sub * BN, ad, bd, IDESC, accumulate);
-                                else umma<MODE>(d_tmem + sub * BN, ad, bd, IDESC, accumulate);
-                            };
+                            if (p < np) {
+                                auto mma = [&](uint32_t a_off, uint32_t b_off, bool acc_is_one) {
+                                    const uint64_t ad = desc_from_words(a_lo + a_off, a_hi), bd = desc_from_words(b_lo + b_off, b_hi);
+                                    if (elected) {
+                                        if (CG == 2) {
+                                            if (acc_is_one) umma2<MODE>(d_tmem + sub * BN, ad, bd, IDESC, 1u);
+                                            else umma2<MODE>(d_tmem + sub * BN, ad, bd, IDESC, later);
+                                        } else {
+                                            if (acc_is_one) umma<MODE>(d_tmem + sub * BN, ad, bd, IDESC, 1u);
+                                            else umma<MODE>(d_tmem + sub * BN, ad, bd, IDESC, later);
+                                        }
+                                    }
+                                };
+                                constexpr uint32_t A_P = (uint32_t)((PP * A_PANEL_BYTES) >> 4), B_P = (uint32_t)((PP * L::B_PANEL_BYTES) >> 4);
 #pragma unroll
-                            for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
-                                mma(a_desc + 2 * k, b_desc + 2 * k, (uint32_t)(((kb - kb0) | p | k) != 0));
-                                if (X3) {
-                                    // head x tail and tail x head (tail x tail is below fp32 rounding); descriptors
-                                    // address 16-byte units
-                                    const uint64_t a_lo = a_desc + (A_PANEL_BYTES >> 4), b_lo = b_desc + (L::B_PANEL_BYTES >> 4);
-                                    mma(a_desc + 2 * k, b_lo + 2 * k, 1u);
-                                    mma(a_lo + 2 * k, b_desc + 2 * k, 1u);
+                                for (int k = 0; k < 4; ++k) {  // 4 x 32 bytes of K per 128-byte row
+                                    mma(p * A_P + 2u * k, p * B_P + 2u * k, (p | k) != 0);
+                                    if (X3) {
+                                        // head x tail and tail x head (tail x tail is below fp32 rounding); descriptors
+                                        // address 16-byte units
+                                        mma(p * A_P + 2u * k, p * B_P + (uint32_t)(L::B_PANEL_BYTES >> 4) + 2u * k, true);
+                                        mma(p * A_P + (uint32_t)(A_PANEL_BYTES >> 4) + 2u * k, p * B_P + 2u * k, true);
+                                    }
                                 }
                             }
                         }
-                        if (CG == 2) umma2_commit_both(emptyB(sb)); else umma_commit(emptyB(sb));
+                        if (elected) { if (CG == 2) umma2_commit_both(emptyB(sb)); else umma_commit(emptyB(sb)); }
+                        __syncwarp();
                         if (++sb == NSB) { sb = 0; phb ^= 1u; }
                     }
-                    if (CG == 2) umma2_commit_both(emptyA(sa)); else umma_commit(emptyA(sa));
+                    if (elected) { if (CG == 2) umma2_commit_both(emptyA(sa)); else umma_commit(emptyA(sa)); }
+                    __syncwarp();
                     if (++sa == NSA) { sa = 0; pha ^= 1u; }
                 }
-                if (alive) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
+                if (alive && elected) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
+                __syncwarp();
                 if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
               }
             }
-            if (!alive) {
+            if (!alive && elected) {
                 // wait (bounded) until the MMAs already issued have retired
                 if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
                 const uint64_t t0 = globaltimer_ns();
                 while (!mbar_try_wait(drain_bar, 0) && globaltimer_ns() - t0 < 10000000ull) { }
             }
+            __syncwarp();
         }
     } else if (warp < X_WARP) {
         // ------------------------------ epilogue ------------------------------
@@ -555,15 +515,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         float ln_s1 = 0.f, ln_s2 = 0.f;    // this row's sum and sum of squares over the tile (fused LayerNorm)
         auto store32 = [&](uint32_t (&r)[32], int64_t row, int col0, bool add) {
             if (row >= B) return;
-            if ((X3 || SK) && add) {
-                // y already holds part of the sum: the earlier chunks of the K range (FP32X3) or the partial sums of
-                // the CTA pairs that own the tile's later input blocks (split contraction); read past L1, which may
-                // hold nothing newer than this SM's own accesses
+            if (X3 && add) {
+                // later chunk of the K range: y already holds the earlier chunks' sum
                 const float* src = y + row * out + col0;
                 if (vec4 && col0 + 32 <= out) {
                     float4 p[8];
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) p[g] = __ldcg(reinterpret_cast<const float4*>(src) + g);
+                    for (int g = 0; g < 8; ++g) p[g] = *reinterpret_cast<const float4*>(src + 4 * g);
 #pragma unroll
                     for (int g = 0; g < 8; ++g) {
                         r[4 * g] = __float_as_uint(__uint_as_float(r[4 * g]) + p[g].x);
@@ -574,7 +532,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 } else {
 #pragma unroll
                     for (int e = 0; e < 32; ++e)
-                        if (col0 + e < out) r[e] = __float_as_uint(__uint_as_float(r[e]) + __ldcg(src + e));
+                        if (col0 + e < out) r[e] = __float_as_uint(__uint_as_float(r[e]) + src[e]);
                 }
             }
             if (LN && ln.stats_out != nullptr) {
@@ -613,47 +571,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(acc_empty_bar(a), 0));
             else mbar_arrive(acc_empty_bar(a));
         };
-        // the four epilogue warps meet on an mbarrier (bounded like every other wait)
-        uint32_t epi_ph = 0;
-        auto epi_sync = [&]() -> bool {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(epi_sync_bar);
-            const bool ok = mbar_wait(epi_sync_bar, epi_ph, abort_flag, status, ST_SPLIT_SYNC);
-            epi_ph ^= 1u;
-            return __all_sync(0xffffffffu, ok);
-        };
-        SegIter<SK> it(unit, nunits, num_tiles, sk_units, n_iblk);
-        int64_t tile; int ib0, ib1;
-        while (alive && it.next(tile, ib0, ib1)) {
-          const int kb_lo = ib0 * dp1, kb_hi = ib1 * dp1;
-          for (int kb0 = kb_lo; kb0 < kb_hi && alive; kb0 += kb_chunk) {
-            bool add = kb0 > kb_lo;
+        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
+          for (int kb0 = 0; kb0 < nkb && alive; kb0 += kb_chunk) {
+            const bool add = kb0 > 0;
             const int64_t row = (tile / n_tiles) * (BM * CG) + rank * BM + q * 32 + lane;
             const int n0 = (int)(tile % n_tiles) * BNT;
             // tcgen05.ld is warp-collective: leave the loop only as a whole warp
             const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, ST_EPILOGUE);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
-            if (SK && ib1 < n_iblk) {
-                // The tile's later input blocks belong to the next CTA pair, which worked on them first: once the flag
-                // of its CTA of the same rank is up, y holds their partial sums and this accumulator is added onto them.
-                if (warp == MMA_WARP + 1 && lane == 0) {
-                    volatile uint32_t* f = sk_flags + blockIdx.x + CG;
-                    const uint64_t t0 = globaltimer_ns();
-                    bool up = false;
-                    for (uint32_t spin = 1;; ++spin) {
-                        uint32_t v;
-                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
-                        if (v != 0u) { up = true; break; }
-                        if ((spin & 63u) == 0 && (*abort_flag || globaltimer_ns() - t0 > WAIT_LIMIT_NS)) break;
-                    }
-                    if (up) *f = 0u;                       // consumed: the array is clean again for the next launch
-                    else { *abort_flag = 1; atomicCAS(status, 0, ST_SPLIT_FLAG); }
-                    *sk_ok = up ? 1 : 0;
-                }
-                if (!epi_sync() || !*sk_ok) { alive = false; break; }
-                add = true;
-            }
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BNT);
             // columns that hold real outputs (a ragged last tile ends early), in chunks of 32
             int ncols = out - n0;
@@ -682,16 +608,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 }
                 ln_s1 = 0.f; ln_s2 = 0.f;
             }
-            if (SK && ib0 > 0) {
-                // partial sums of the tile's later input blocks are in y: publish them to the pair that holds the
-                // earlier ones (stores of all four warps first, then one release store of the flag)
-                __threadfence();
-                if (!epi_sync()) { alive = false; break; }
-                if (warp == MMA_WARP + 1 && lane == 0) {
-                    const uint32_t one = 1u;
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sk_flags + blockIdx.x), "r"(one) : "memory");
-                }
-            }
             if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
           }
         }
@@ -710,36 +626,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
 }
 
-// device address of the split-contraction flag array, looked up once per device (with that device current)
-static int sk_flags_base(uint32_t** out) {
-    static uint32_t* base[64] = {nullptr};
-    static std::mutex mu;
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return check_cuda(e);
-    if (dev < 0 || dev >= 64) return CHEBYKAN_EDEVICE;
-    std::lock_guard<std::mutex> lock(mu);
-    if (base[dev] == nullptr) {
-        void* ptr = nullptr;
-        e = cudaGetSymbolAddress(&ptr, g_sk_flags);
-        if (e != cudaSuccess) return check_cuda(e);
-        base[dev] = reinterpret_cast<uint32_t*>(ptr);
-    }
-    *out = base[dev];
-    return CHEBYKAN_OK;
-}
-
-// CHEBYKAN_SPLIT_K=0 in the environment keeps every tile on one CTA pair (results then do not depend on how many
-// rows share a launch); read once
-static bool split_contraction_enabled() {
-    static const bool v = [] {
-        const char* e = getenv("CHEBYKAN_SPLIT_K");
-        return !(e != nullptr && e[0] == '0');
-    }();
-    return v;
-}
-
-template <int MODE, int BN, int NSUB, bool LN, int CG, bool SK = false>
+template <int MODE, int BN, int NSUB, bool LN, int CG>
 int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
     using L = Smem<BN, NSUB, CG, (MODE == CHEBYKAN_MODE_FP32X3) ? 2 : 1>;
@@ -748,7 +635,7 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return CHEBYKAN_EINVAL;
-    auto kernel = fwd_tc_kernel<MODE, BN, NSUB, LN, CG, SK>;
+    auto kernel = fwd_tc_kernel<MODE, BN, NSUB, LN, CG>;
     if (!attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -772,31 +659,7 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     }
     const int n_tiles = (int)ceil_div(out, BN * NSUB);      // n_pad is out rounded up to a divisor of the tile
     const int64_t num_tiles = ceil_div(B, BM * CG) * n_tiles;
-    constexpr int IBK = (MODE == CHEBYKAN_MODE_BF16) ? 64 : 32;
-    const int64_t n_iblk = ceil_div(in, IBK);
-    if constexpr (!SK && CG == 2 && !LN && MODE != CHEBYKAN_MODE_FP32X3 && BN == 256 && NSUB == 2) {
-        // tiles that do not fill whole waves of the CTA pairs: split the contraction so that every pair gets the
-        // same number of (tile, input block) units
-        if (split_contraction_enabled() && n_iblk >= 2 && num_tiles % max_units[dev] != 0 &&
-            2 * max_units[dev] <= SK_MAX_CTAS)
-            return launch_one_ln<MODE, BN, NSUB, LN, CG, true>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad,
-                                                               status, s, ln);
-    }
-    int64_t units64 = num_tiles < max_units[dev] ? num_tiles : max_units[dev];
-    int64_t sk_units = 0;
-    uint32_t* sk_flags = nullptr;
-    if constexpr (SK) {
-        sk_units = num_tiles * n_iblk;
-        units64 = max_units[dev];
-        if (units64 > num_tiles * SK_MAX_SEGMENTS) units64 = num_tiles * SK_MAX_SEGMENTS;   // short chains of partial sums
-        if (units64 > sk_units) units64 = sk_units;                                         // no pair without work
-        uint32_t* base = nullptr;
-        int rc = sk_flags_base(&base);
-        if (rc) return rc;
-        static std::atomic<uint32_t> launches{0};
-        sk_flags = base + (launches.fetch_add(1) % SK_SLOTS) * SK_MAX_CTAS;
-    }
-    const unsigned units = (unsigned)units64;
+    const unsigned units = (unsigned)(num_tiles < max_units[dev] ? num_tiles : max_units[dev]);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(units * CG); cfg.blockDim = dim3(NUM_THREADS); cfg.dynamicSmemBytes = L::TOTAL; cfg.stream = s;
     cudaLaunchAttribute attrs[1];
@@ -804,7 +667,7 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_tiles,
-                                         num_tiles, status, ln, n_pad, sk_units, sk_flags));
+                                         num_tiles, status, ln, n_pad));
 }
 
 // the LayerNorm-fused variant is a separate instantiation, so the plain kernel carries none of its registers

@@ -85,12 +85,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
           "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr) : "memory");
 }
-// true in exactly one lane of a converged warp
-__device__ __forceinline__ bool elect_one_sync() {
-    uint32_t pred;
-    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
-    return pred != 0;
-}
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 template <int MODE>
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
@@ -317,8 +311,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             const uint64_t desc0 = make_smem_desc(smem_base + C::B_OFFSET);
             const uint32_t desc_hi = (uint32_t)(desc0 >> 32), desc_lo0 = (uint32_t)desc0;
             auto issue = [&](uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, bool acc_const_one, uint32_t acc_dyn) {
-                uint64_t b_desc;
-                asm volatile("mov.b64 %0, {%1, %2};" : "=l"(b_desc) : "r"(b_lo), "r"(desc_hi));
+                const uint64_t b_desc = desc_from_words(b_lo, desc_hi);
                 if (elected) {
                     if (acc_const_one) umma_ts<MODE>(d_tmem, a_tmem, b_desc, IDESC, 1u);
                     else umma_ts<MODE>(d_tmem, a_tmem, b_desc, IDESC, acc_dyn);

@@ -74,6 +74,22 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
     d |= (uint64_t)2 << 61;                   // SWIZZLE_128B
     return d;
 }
+// true in exactly one lane of a converged warp.  The MMA-issuing warps run their loops in lock step and let only
+// this lane execute tcgen05.mma / tcgen05.commit: the instructions take their operands from uniform registers, and
+// inside a divergent region (a loop under `if (lane == 0)`) the compiler has to move every operand there from a
+// vector register, which costs more than a small MMA occupies the tensor pipe.
+__device__ __forceinline__ bool elect_one_sync() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+// descriptor from its two words: the high word of a kernel's operand descriptors never changes, the low word
+// (start address >> 4 in bits 0-13) moves with the stage, so stepping through a ring is a 32-bit add
+__device__ __forceinline__ uint64_t desc_from_words(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm volatile("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
 template <int MODE>
 __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                      uint32_t accumulate) {

@@ -513,3 +513,4 @@ def test_cta_pair_kernels_replay_from_a_cuda_graph():
     torch.cuda.synchronize()
     ops.check_status()
     assert torch.equal(y_g, y_e) and torch.equal(dc_g, dc_e) and torch.equal(dx_g, dx_e)
+
