@@ -535,6 +535,7 @@ bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
 }
 
 int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
+    if (!x3 && dcoeff_f16_supported(B, in, out, deg)) return dcoeff_f16_workspace_bytes(B, in, out, deg);
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int64_t partials = p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
     return x3 ? round_up(B * out * 4, 256) + partials : partials;     // x3: the tails of dY come first
@@ -545,6 +546,8 @@ int launch_dy_tail(const float* dy, float* lo, int64_t n, cudaStream_t s);
 
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
                      int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3) {
+    if (!x3 && dcoeff_f16_supported(B, in, out, deg))
+        return launch_dcoeff_f16(x, dy, dc, ws, ws_bytes, B, in, out, deg, accumulate, status, s);
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int dp1 = (int)deg + 1;
     const int64_t n = in * out * dp1;

@@ -118,6 +118,11 @@ inline bool x3_dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t de
     return out <= 2048 && x3_backward_on_tensor_cores(B, in, out, deg);
 }
 bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
+// narrow layers (<= 128 outputs): fp16 operands (11 significant bits, like tf32) with a scaled, transposed copy of dY
+bool dcoeff_f16_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
+int64_t dcoeff_f16_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg);
+int launch_dcoeff_f16(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B, int64_t in,
+                      int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s);
 int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0);
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
                      int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3 = 0);

@@ -216,6 +216,44 @@ def test_tc_dcoeff_vs_oracle(mode, B, n_in, n_out, deg, dist):
     assert err > 1e-6            # tf32 operands leave a visible rounding: this is the tensor-core path
 
 
+# Narrow layers (at most 128 outputs, inputs a multiple of 4) contract in tcgen05 kind::f16 with fp16 operands: the
+# basis values as they are, dY scaled by a power of two and transposed by a pre-pass.  fp16 has tf32's 11 significant
+# bits, so the error is the tf32 kernel's.
+DC_F16_SHAPES = [
+    # B, in, out, deg, dist, dY scale
+    (70000, 64, 64, 32, "uniform3", 1.0),      # configuration 5 layer, batch split over CTAs, ragged last K block
+    (3000, 64, 128, 8, "normal", 1.0),         # 128-column accumulators
+    (3000, 100, 96, 5, "normal", 1.0),         # several input tiles, ragged outputs
+    (777, 28, 4, 3, "normal", 1.0),            # 28 inputs in one tile (the x tile's 32 columns almost full)
+    (63, 8, 8, 63, "normal", 1.0),             # less than one K block; highest tested degree (two inputs per M tile)
+    (4096, 64, 64, 32, "uniform3", 3e7),       # large gradients: scaled down into fp16's range
+    (4096, 64, 64, 32, "uniform3", 1e-12),     # tiny gradients: scaled up (fp16 alone would flush them to zero)
+]
+
+
+@pytest.mark.parametrize("B,n_in,n_out,deg,dist,dy_scale", DC_F16_SHAPES)
+def test_narrow_dcoeff_fp16_operands(B, n_in, n_out, deg, dist, dy_scale):
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, dist, seed=B + n_in + deg)
+    dy = dy * dy_scale
+    _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
+    dC, dCw = guarded((n_in, n_out, deg + 1))
+    xd, dyd = x.cuda(), dy.cuda()
+    ops.bwd_dcoeff(xd, dyd, n_in, n_out, deg, "tf32", out=dC)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dC, dCw)
+    err = o.rel_l2(dC.cpu(), dC_ref)
+    assert 1e-6 < err <= TC_TOL, err
+    again = ops.bwd_dcoeff(xd, dyd, n_in, n_out, deg, "tf32")
+    assert torch.equal(again, dC)                       # fixed summation order: repeatable bit for bit
+    acc = dC.clone()
+    ops.bwd_dcoeff(xd, dyd, n_in, n_out, deg, "tf32", out=acc, accumulate=True)
+    assert o.rel_l2(acc.cpu(), 2 * dC_ref) <= TC_TOL
+    # an all-zero gradient gives an all-zero result (no scale can be derived from it)
+    z = ops.bwd_dcoeff(xd, torch.zeros_like(dyd), n_in, n_out, deg, "tf32")
+    assert float(z.abs().max()) == 0.0
+
+
 def test_tc_dcoeff_accumulate_and_repeatable():
     x, coeffs, dy = make_case(6000, 24, 64, 8, seed=31)
     _, dC_ref, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
