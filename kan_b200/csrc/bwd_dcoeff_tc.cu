@@ -534,8 +534,19 @@ bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     return B > 0 && (out % 4) == 0 && dp1 <= 128;
 }
 
+// FP32X3 keeps one partial result per DC_X3_ROWS batch rows.  So that the workspace does not grow with the batch
+// (43 partial copies of a 37.7 MB gradient on a 65536 x 1024 -> 1024 degree-8 layer), the batch is worked off in
+// groups of slices whose partial results fit about 512 MB; each group's reduction adds into dC.
+static int64_t x3_group_rows(int64_t in, int64_t out, int64_t deg) {
+    const int64_t n_bytes = in * out * (deg + 1) * 4;
+    int64_t slices = ((int64_t)512 << 20) / n_bytes;
+    if (slices < 2) slices = 2;
+    return slices * DC_X3_ROWS;
+}
+
 int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
     if (!x3 && dcoeff_f16_supported(B, in, out, deg)) return dcoeff_f16_workspace_bytes(B, in, out, deg);
+    if (x3 && B > x3_group_rows(in, out, deg)) B = x3_group_rows(in, out, deg);
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int64_t partials = p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
     return x3 ? round_up(B * out * 4, 256) + partials : partials;     // x3: the tails of dY come first
@@ -548,6 +559,17 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
                      int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3) {
     if (!x3 && dcoeff_f16_supported(B, in, out, deg))
         return launch_dcoeff_f16(x, dy, dc, ws, ws_bytes, B, in, out, deg, accumulate, status, s);
+    if (x3 && B > x3_group_rows(in, out, deg)) {
+        // group after group of batch slices through the same workspace (stream order keeps them apart)
+        const int64_t rows = x3_group_rows(in, out, deg);
+        for (int64_t b0 = 0; b0 < B; b0 += rows) {
+            const int64_t bg = (B - b0 < rows) ? B - b0 : rows;
+            const int rc = launch_dcoeff_tc(x + b0 * in, dy + b0 * out, dc, ws, ws_bytes, bg, in, out, deg,
+                                            (b0 > 0) ? 1 : accumulate, status, s, x3);
+            if (rc) return rc;
+        }
+        return CHEBYKAN_OK;
+    }
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int dp1 = (int)deg + 1;
     const int64_t n = in * out * dp1;

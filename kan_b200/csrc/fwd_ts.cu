@@ -164,12 +164,11 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         float tt[EPT], ta[EPT], tb[EPT];
         uint32_t inc = TF32_HALF_ULP;
         int s = 0; uint32_t ph = 0;
-        int kpos = 0, kb_left = 0;
         int xs = 0; uint32_t xph = 0;
         bool alive = true;
 
-        // store one K block's values of this thread (16 columns), hand the stage over after its last K block
-        auto emit = [&](const float (&v)[EPT]) -> bool {
+        // one K block's values of this thread -> 16 columns of the stage, straight-line code
+        auto emit = [&](uint32_t taddr, const float (&v)[EPT]) {
             uint32_t w[16];
             if (C::BF16) {
 #pragma unroll
@@ -181,26 +180,15 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 #pragma unroll
                 for (int c = 0; c < 16; ++c) w[c] = tf32_rna(v[c % EPT], inc);
             }
-            if (kpos == 0) {
-                const bool ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_PRODUCER);
-                if (!__all_sync(0xffffffffu, ok)) return false;
-                tc_fence_after();
-            }
-            const uint32_t col = A_COL0 + (uint32_t)(((sub * NSTG + s) * KP + kpos) * 32 + h * 16);
-            tmem_st16(lane_addr + col, w);
-            --kb_left;
-            if (kpos + 1 < KP && kb_left > 0) { ++kpos; return true; }
-            kpos = 0;
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full(s));
-            if (++s == NSTG) { s = 0; ph ^= 1u; }
-            return true;
+            tmem_st16(taddr, w);
         };
 
+        // A stage never spans two input blocks: the K blocks of an input block are cut into stages of KP degrees (the
+        // last one shorter), so that inside a stage the degree parity, the column offsets and the trip count are
+        // compile-time and the recurrence runs as straight-line code.  KP is even: a stage starts on an even degree
+        // with ta = T_{d0-2}, tb = T_{d0-1}.
+        static_assert(KP % 2 == 0, "stages start on even degrees");
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-            kb_left = nkb;
             for (int ib = 0; ib < n_iblk && alive; ++ib) {
                 {
                     const bool ok = mbar_wait(x_full(sub, xs), xph, abort_flag, status, TS_X_WAIT);
@@ -223,30 +211,53 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     for (int e = 0; e < 4; ++e) {
                         const float t = tanh_fast(vv[e]);
                         finite = finite && (t == t);
-                        tt[4 * c + e] = 2.f * t; ta[4 * c + e] = 1.f; tb[4 * c + e] = t;   // T_0 = 1, T_{-1} = T_1 = t
+                        tt[4 * c + e] = 2.f * t; ta[4 * c + e] = 1.f; tb[4 * c + e] = t;   // T_0 = 1, T_1 = t
                     }
                 }
                 inc = finite ? TF32_HALF_ULP : 0u;
-                // degree 0, then degrees alternate between tb and ta; the x slot goes back after the first store whose
-                // data derives from it has been issued (an mbarrier arrive does not wait for outstanding ld.shared)
-                if (!emit(ta)) { alive = false; break; }
-                bool x_held = true;
-                auto release_x = [&]() {
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(x_empty(sub, xs));
-                    x_held = false;
-                };
-                if (dp1 == 1) release_x();
-                for (int d = 1; d < dp1; d += 2) {
-#pragma unroll
-                    for (int e = 0; e < EPT; ++e) tb[e] = fmaf(tt[e], ta[e], -tb[e]);
-                    if (!emit(tb)) { alive = false; break; }
-                    if (x_held) release_x();
-                    if (d + 1 < dp1) {
+                for (int d0 = 0; d0 < dp1 && alive; d0 += KP) {
+                    const int np = (dp1 - d0 < KP) ? dp1 - d0 : KP;
+                    {
+                        const bool ok = mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_PRODUCER);
+                        if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
+                        tc_fence_after();
+                    }
+                    const uint32_t st0 = lane_addr + A_COL0 + (uint32_t)((sub * NSTG + s) * KP * 32 + h * 16);
+                    if (d0 == 0) {
+                        emit(st0, ta);                                     // degree 0
+                        // the x slot goes back after a store whose data derives from it has been issued (an mbarrier
+                        // arrive does not wait for this thread's outstanding ld.shared, the store does)
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(x_empty(sub, xs));
+                        if (1 < np) emit(st0 + 32, tb);                    // degree 1
+                    } else {
 #pragma unroll
                         for (int e = 0; e < EPT; ++e) ta[e] = fmaf(tt[e], tb[e], -ta[e]);
-                        if (!emit(ta)) { alive = false; break; }
+                        emit(st0, ta);
+                        if (1 < np) {
+#pragma unroll
+                            for (int e = 0; e < EPT; ++e) tb[e] = fmaf(tt[e], ta[e], -tb[e]);
+                            emit(st0 + 32, tb);
+                        }
                     }
+#pragma unroll
+                    for (int p = 2; p < KP; p += 2) {
+                        if (p < np) {
+#pragma unroll
+                            for (int e = 0; e < EPT; ++e) ta[e] = fmaf(tt[e], tb[e], -ta[e]);
+                            emit(st0 + (uint32_t)(p * 32), ta);
+                        }
+                        if (p + 1 < np) {
+#pragma unroll
+                            for (int e = 0; e < EPT; ++e) tb[e] = fmaf(tt[e], ta[e], -tb[e]);
+                            emit(st0 + (uint32_t)((p + 1) * 32), tb);
+                        }
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(full(s));
+                    if (++s == NSTG) { s = 0; ph ^= 1u; }
                 }
                 if (++xs == NXS) { xs = 0; xph ^= 1u; }
             }
@@ -257,14 +268,17 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             int s = 0; uint32_t ph = 0;
             bool alive = true;
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
-                for (int kb = 0; kb < nkb && alive; kb += KP) {
-                    const int np = (nkb - kb < KP) ? nkb - kb : KP;
-                    if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_TMA_W)) { alive = false; break; }
-                    const uint32_t dst = smem_base + C::B_OFFSET + s * C::B_STAGE_BYTES;
-                    mbar_arrive_expect_tx(full(s), (uint32_t)(np * C::B_PANEL_BYTES));
-                    for (int p = 0; p < np; ++p)
-                        tma_load_2d(dst + p * C::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, 0, full(s));
-                    if (++s == NSTG) { s = 0; ph ^= 1u; }
+                for (int ib = 0; ib < n_iblk && alive; ++ib) {
+                    for (int d0 = 0; d0 < dp1 && alive; d0 += KP) {      // the producers' stages: KP degrees of one input block
+                        const int np = (dp1 - d0 < KP) ? dp1 - d0 : KP;
+                        const int kb = ib * dp1 + d0;
+                        if (!mbar_wait(empty(s), ph ^ 1u, abort_flag, status, TS_TMA_W)) { alive = false; break; }
+                        const uint32_t dst = smem_base + C::B_OFFSET + s * C::B_STAGE_BYTES;
+                        mbar_arrive_expect_tx(full(s), (uint32_t)(np * C::B_PANEL_BYTES));
+                        for (int p = 0; p < np; ++p)
+                            tma_load_2d(dst + p * C::B_PANEL_BYTES, &tmap_w, (kb + p) * IB, 0, full(s));
+                        if (++s == NSTG) { s = 0; ph ^= 1u; }
+                    }
                 }
             }
             if (!alive) {
@@ -320,9 +334,10 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
                 if (!__all_sync(0xffffffffu, mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, TS_MMA_ACC))) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t d0 = tmem_base + D_COL0 + (uint32_t)(acc * NSUBM * BN);
-                for (int kb = 0; kb < nkb && alive; kb += KP) {
-                    const int np = (nkb - kb < KP) ? nkb - kb : KP;
+                const uint32_t dacc = tmem_base + D_COL0 + (uint32_t)(acc * NSUBM * BN);
+                for (int ib = 0; ib < n_iblk && alive; ++ib) {
+                  for (int d0 = 0; d0 < dp1 && alive; d0 += KP) {        // the producers' stages
+                    const int np = (dp1 - d0 < KP) ? dp1 - d0 : KP;
                     const uint32_t a0 = tmem_base + A_COL0 + (uint32_t)(sa * KP * 32);
                     const uint32_t b0 = desc_lo0 + (uint32_t)((sa * C::B_STAGE_BYTES) >> 4);
                     if (!__all_sync(0xffffffffu, mbar_wait(full(sa), pha, abort_flag, status, TS_MMA_A))) { alive = false; break; }
@@ -334,14 +349,15 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                             for (int k = 0; k < 4; ++k) {          // 4 x 8 columns of A, 4 x 32 bytes of each W row
 #pragma unroll
                                 for (int sub = 0; sub < NSUBM; ++sub)
-                                    issue(d0 + (uint32_t)(sub * BN), a0 + (uint32_t)(sub * NSTG * KP * 32 + p * 32 + k * 8),
-                                          b0 + (uint32_t)((p * C::B_PANEL_BYTES) >> 4) + 2u * k, (p | k) != 0, (uint32_t)(kb != 0));
+                                    issue(dacc + (uint32_t)(sub * BN), a0 + (uint32_t)(sub * NSTG * KP * 32 + p * 32 + k * 8),
+                                          b0 + (uint32_t)((p * C::B_PANEL_BYTES) >> 4) + 2u * k, (p | k) != 0, (uint32_t)((ib | d0) != 0));
                             }
                         }
                     }
                     if (elected) umma_commit(empty(sa));
                     __syncwarp();
                     if (++sa == NSTG) { sa = 0; pha ^= 1u; }
+                  }
                 }
                 if (alive && elected) umma_commit(acc_full_bar(acc));
                 __syncwarp();

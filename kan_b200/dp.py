@@ -10,6 +10,7 @@ NVLink on GPUs; gloo in the CPU tests of this host logic).
 """
 from __future__ import annotations
 
+import os
 from typing import Iterable, List, Tuple
 
 import torch
@@ -70,6 +71,9 @@ class FlatGradBuffer:
         self.attach()
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(group) == 1:
             return None
+        if self.flat.is_cuda and os.environ.get("KAN_B200_NVTX", "0") == "1":
+            with torch.cuda.nvtx.range("chebykan.allreduce_dC"):
+                return dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
         return dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=async_op)
 
 

@@ -5,12 +5,32 @@ sm_100a kernels of libchebykan_b200.so.  Nothing here computes on the CPU.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
 from ._lib import MODES, OP_BWD_DCOEFF, OP_BWD_DX
 
 _status = {}  # device index -> int32[1] tensor the tensor-core kernels report into
+
+# KAN_B200_NVTX=1: every library call of this module runs inside an NVTX range named after the operation, so that a
+# timeline shows pack / forward / dC / dx / optimizer / loss next to torch's own ranges (off by default: no overhead)
+_NVTX = os.environ.get("KAN_B200_NVTX", "0") == "1"
+
+
+class _Range:
+    def __init__(self, name):
+        self.name = name
+
+    def __enter__(self):
+        if _NVTX:
+            torch.cuda.nvtx.range_push(self.name)
+
+    def __exit__(self, *exc):
+        if _NVTX:
+            torch.cuda.nvtx.range_pop()
+        return False
 
 
 def _mode(mode) -> int:
@@ -75,7 +95,7 @@ def pack_coeffs(coeffs: torch.Tensor, mode, out: torch.Tensor | None = None) -> 
         out = torch.empty(nbytes, dtype=torch.uint8, device=coeffs.device)
     elif out.numel() * out.element_size() < nbytes or out.device != coeffs.device:
         raise RuntimeError("packed buffer too small or on another device")
-    with torch.cuda.device(coeffs.device):
+    with _Range("chebykan.pack"), torch.cuda.device(coeffs.device):
         rc = _lib.load().chebykan_pack_coeffs(coeffs.data_ptr(), out.data_ptr(), n_in, n_out, dp1 - 1, m,
                                               _stream(coeffs))
     _lib.check(rc, "chebykan_pack_coeffs")
@@ -94,7 +114,7 @@ def forward(x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, de
         out = torch.empty(B, out_dim, dtype=torch.float32, device=x.device)
     else:
         _require(out, "out")
-    with torch.cuda.device(x.device):
+    with _Range("chebykan.forward"), torch.cuda.device(x.device):
         rc = _lib.load().chebykan_fwd(x.data_ptr(), packed.data_ptr(), out.data_ptr(), B, in_dim, out_dim,
                                       degree, m, status_tensor(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "chebykan_fwd")
@@ -128,7 +148,7 @@ def forward_ln(x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int,
         if stats_out.shape != (B, 2):
             raise RuntimeError("stats_out must be [B, 2]")
         so = stats_out.data_ptr()
-    with torch.cuda.device(x.device):
+    with _Range("chebykan.forward_ln"), torch.cuda.device(x.device):
         rc = _lib.load().chebykan_fwd_ln(x.data_ptr(), packed.data_ptr(), out.data_ptr(), B, in_dim, out_dim, degree,
                                          _mode(mode), st_in, g, b, float(eps), so,
                                          status_tensor(x.device).data_ptr(), _stream(x))
@@ -154,7 +174,7 @@ def bwd_dcoeff(x: torch.Tensor, dy: torch.Tensor, in_dim: int, out_dim: int, deg
     ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DCOEFF, B, in_dim, out_dim, degree, m)
     _lib.check(ws_bytes, "chebykan_workspace_bytes")
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _Range("chebykan.dcoeff"), torch.cuda.device(x.device):
         rc = lib.chebykan_bwd_dcoeff(x.data_ptr(), dy.data_ptr(), out.data_ptr(), ws.data_ptr(), ws_bytes, B,
                                      in_dim, out_dim, degree, m, int(accumulate),
                                      status_tensor(x.device).data_ptr(), _stream(x))
@@ -181,7 +201,7 @@ def bwd_dx(x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor, mode,
     ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DX, B, n_in, n_out, dp1 - 1, m)
     _lib.check(ws_bytes, "chebykan_workspace_bytes")
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
-    with torch.cuda.device(x.device):
+    with _Range("chebykan.dx"), torch.cuda.device(x.device):
         rc = lib.chebykan_bwd_dx(x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(), out.data_ptr(), ws.data_ptr(),
                                  ws_bytes, B, n_in, n_out, dp1 - 1, m,
                                  status_tensor(x.device).data_ptr(), _stream(x))
@@ -245,7 +265,7 @@ def mse_loss_grad(y: torch.Tensor, target: torch.Tensor, n_mean: int | None = No
         ws = _mse_ws[idx] = torch.empty(lib.chebykan_mse_workspace_bytes(), dtype=torch.uint8, device=y.device)
     dy = torch.empty_like(y)
     loss = torch.empty((), dtype=torch.float32, device=y.device)
-    with torch.cuda.device(y.device):
+    with _Range("chebykan.mse_loss"), torch.cuda.device(y.device):
         rc = lib.chebykan_mse_loss_grad(y.data_ptr(), target.data_ptr(), dy.data_ptr(), loss.data_ptr(), ws.data_ptr(),
                                         ws.numel(), n, int(n_mean or n), float(grad_scale), _stream(y))
     _lib.check(rc, "chebykan_mse_loss_grad")
@@ -269,7 +289,7 @@ def sgd_step(param: torch.Tensor, grad: torch.Tensor, lr: float, grad_scale: flo
     _require(grad, "grad")
     if grad.numel() != param.numel():
         raise RuntimeError("grad and param sizes differ")
-    with torch.cuda.device(param.device):
+    with _Range("chebykan.sgd"), torch.cuda.device(param.device):
         rc = _lib.load().chebykan_sgd_step(param.data_ptr(), grad.data_ptr(), param.numel(), lr, grad_scale,
                                            _stream(param))
     _lib.check(rc, "chebykan_sgd_step")
@@ -282,7 +302,7 @@ def adam_step(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tensor, ex
         _require(t, n)
         if t.numel() != param.numel():
             raise RuntimeError(f"{n} and param sizes differ")
-    with torch.cuda.device(param.device):
+    with _Range("chebykan.adam"), torch.cuda.device(param.device):
         rc = _lib.load().chebykan_adam_step(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(),
                                             exp_avg_sq.data_ptr(), param.numel(), lr, beta1, beta2, eps, step,
                                             grad_scale, _stream(param))
@@ -299,7 +319,7 @@ def adam_step_graph(param: torch.Tensor, grad: torch.Tensor, exp_avg: torch.Tens
             raise RuntimeError(f"{n} and param sizes differ")
     if step_dev.dtype != torch.int64 or not step_dev.is_cuda or step_dev.numel() != 1:
         raise RuntimeError("step_dev must be a CUDA int64 tensor with one element")
-    with torch.cuda.device(param.device):
+    with _Range("chebykan.adam"), torch.cuda.device(param.device):
         rc = _lib.load().chebykan_adam_step_graph(param.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(),
                                                   exp_avg_sq.data_ptr(), param.numel(), lr, beta1, beta2, eps,
                                                   step_dev.data_ptr(), grad_scale, _stream(param))
@@ -360,7 +380,7 @@ def forward_host_packed(x_host: torch.Tensor, packed: torch.Tensor, n_in: int, n
         scratch = torch.empty(need, dtype=torch.uint8, device=packed.device)
     if out is None:
         out = torch.empty(B, n_out, dtype=torch.float32, pin_memory=True)
-    with torch.cuda.device(packed.device):
+    with _Range("chebykan.forward_host"), torch.cuda.device(packed.device):
         rc = lib.chebykan_fwd_host_packed(x2.data_ptr(), packed.data_ptr(), out.data_ptr(), scratch.data_ptr(),
                                           scratch.numel(), B, n_in, n_out, degree, _mode(mode), rows,
                                           torch.cuda.current_stream(packed.device).cuda_stream)
