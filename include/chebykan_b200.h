@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 4
+#define CHEBYKAN_ABI_VERSION 5
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -194,6 +194,60 @@ int chebykan_jacobian(const float* x, const float* coeffs, float* jac,
 int chebykan_normalize_input(const float* x, float* t, int64_t n, void* stream);
 int chebykan_basis_functions(const float* t, float* phi, int64_t n, int64_t deg,
                              void* stream);
+
+/*
+ * The reference's other polynomial layers have the Chebyshev layer's structure - normalise the
+ * input, evaluate a three-term recurrence, contract with coefficients[in][out][deg+1] through
+ * einsum('bid,iod->bo') - and run on the same fp32 kernels with the recurrence swapped:
+ *   CHEBYKAN_FAMILY_JACOBI       P_d^(alpha,beta)(tanh x), alpha, beta > -1
+ *                                (JacobiKANLayer / JacobiBasis, kan/layers/jacobikan.py:20-68,
+ *                                 kan/basis/jacobi.py:84-188);
+ *   CHEBYKAN_FAMILY_HERMITE      physicist's H_d(u),  H_{d+1} = 2u H_d - 2d H_{d-1}
+ *   CHEBYKAN_FAMILY_HERMITE_PROB probabilist's He_d(u), He_{d+1} = u He_d - d He_{d-1}
+ *                                (HermiteKANLayer / HermiteBasis, kan/layers/hermitekan.py:22-83,
+ *                                 kan/basis/hermite.py:85-233), u = 3 tanh x, or - for a finite
+ *                                 domain [lo, hi] with domain normalisation on - the affine map
+ *                                 u = 6/(hi-lo) * (x - lo) - 3;
+ *   CHEBYKAN_FAMILY_CHEBYSHEV    T_d(tanh x) through the same table-driven kernels (a cross-check of
+ *                                them against the Chebyshev entry points above).
+ * A family is described on the HOST by a chebykan_family; the library turns it into the recurrence
+ * table the kernels take as a launch parameter, so there is nothing to upload or keep alive.
+ * `packed` is the FP32 layout of chebykan_pack_coeffs (the packing does not depend on the family) and
+ * the workspace of chebykan_family_bwd_dcoeff is chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DCOEFF, ...,
+ * CHEBYKAN_MODE_FP32).  All three layer functions compute in fp32 on the FFMA pipe with a correctly
+ * rounded tanh; the reference has no hand-written backward, the two bwd functions return what autograd
+ * derives from the forward.  chebykan_family_normalize / chebykan_family_basis are the basis object's
+ * normalize_input / basis_functions on flat arrays of n elements (phi has n*(deg+1) elements), and
+ * chebykan_family_table copies the recurrence P_d = (a[d] u + b[d]) P_{d-1} - c[d] P_{d-2}
+ * (d = 1..deg, P_0 = 1, P_{-1} = 0; deg+1 floats per HOST array, entry 0 unused) for inspection.
+ */
+#define CHEBYKAN_FAMILY_CHEBYSHEV    0
+#define CHEBYKAN_FAMILY_JACOBI       1
+#define CHEBYKAN_FAMILY_HERMITE      2
+#define CHEBYKAN_FAMILY_HERMITE_PROB 3
+
+typedef struct chebykan_family {
+    int32_t kind;        /* CHEBYKAN_FAMILY_*                                                   */
+    float   alpha, beta; /* Jacobi parameters; ignored by the other kinds                       */
+    int32_t affine;      /* 0: u = scale * tanh(x);  1: u = scale * (x - shift) + offset        */
+    float   scale;       /* 0 selects the kind's default (3 for the Hermite kinds, 1 otherwise) */
+    float   shift, offset;
+} chebykan_family;
+
+int chebykan_family_table(const chebykan_family* family, int64_t deg, float* a_host, float* b_host,
+                          float* c_host);
+int chebykan_family_fwd(const chebykan_family* family, const float* x, const void* packed, float* y,
+                        int64_t B, int64_t in, int64_t out, int64_t deg, void* stream);
+int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, const float* dy,
+                               float* dcoeffs, void* workspace, int64_t workspace_bytes, int64_t B,
+                               int64_t in, int64_t out, int64_t deg, int accumulate, void* stream);
+int chebykan_family_bwd_dx(const chebykan_family* family, const float* x, const float* dy,
+                           const float* coeffs, float* dx, int64_t B, int64_t in, int64_t out,
+                           int64_t deg, void* stream);
+int chebykan_family_normalize(const chebykan_family* family, const float* x, float* u, int64_t n,
+                              void* stream);
+int chebykan_family_basis(const chebykan_family* family, const float* u, float* phi, int64_t n,
+                          int64_t deg, void* stream);
 
 /*
  * Mean-squared-error loss and its gradient in one pass: *loss = sum (y - target)^2 / n_mean and

@@ -16,6 +16,16 @@ LIB_PATH = os.path.join(_HERE, "libchebykan_b200.so")
 MODE_FP32, MODE_TF32, MODE_BF16, MODE_FP32X3 = 0, 1, 2, 3
 MODES = {"fp32": MODE_FP32, "tf32": MODE_TF32, "bf16": MODE_BF16, "fp32x3": MODE_FP32X3}
 OP_FWD, OP_BWD_DCOEFF, OP_BWD_DX = 0, 1, 2
+FAMILY_CHEBYSHEV, FAMILY_JACOBI, FAMILY_HERMITE, FAMILY_HERMITE_PROB = 0, 1, 2, 3
+
+
+class Family(ctypes.Structure):
+    """chebykan_family of the C header: a polynomial family described on the host."""
+    _fields_ = [("kind", c_int32), ("alpha", c_float), ("beta", c_float), ("affine", c_int32),
+                ("scale", c_float), ("shift", c_float), ("offset", c_float)]
+
+
+_FAM = ctypes.POINTER(Family)
 
 # name -> (restype, argtypes); every symbol declared in include/chebykan_b200.h
 SIGNATURES = {
@@ -38,6 +48,14 @@ SIGNATURES = {
     "chebykan_jacobian": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
     "chebykan_normalize_input": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "chebykan_basis_functions": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "chebykan_family_table": (c_int, [_FAM, c_int64, c_void_p, c_void_p, c_void_p]),
+    "chebykan_family_fwd": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "chebykan_family_bwd_dcoeff": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                           c_int64, c_int64, c_int, c_void_p]),
+    "chebykan_family_bwd_dx": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
+                                       c_int64, c_void_p]),
+    "chebykan_family_normalize": (c_int, [_FAM, c_void_p, c_void_p, c_int64, c_void_p]),
+    "chebykan_family_basis": (c_int, [_FAM, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "chebykan_mse_workspace_bytes": (c_int64, []),
     "chebykan_mse_loss_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                        c_float, c_void_p]),
@@ -73,7 +91,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 4:
+    if lib.chebykan_abi_version() != 5:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -26,12 +26,12 @@ static inline int tile_inputs(int64_t in, int dp1) {
 // the batch, 8 rows per stage.  Partial sums of the batch slices go to the
 // workspace and are added up by dcoeff_reduce_kernel in a fixed order.
 // ---------------------------------------------------------------------------
-template <int G_N>
+template <int G_N, class REC>
 __global__ void __launch_bounds__(256)
 dcoeff_ffma_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                    float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI,
                    int i_tiles, int n_tiles, int64_t rows_per_split, int64_t split_stride,
-                   int add_to_dst) {
+                   int add_to_dst, const __grid_constant__ REC rec) {
     constexpr int BN = 64 * G_N;
     constexpr int LDA = BWD_KK + 4;
     constexpr int MAXP = 4;  // (row, input) pairs per thread per stage: 8*TI <= 1024
@@ -99,20 +99,20 @@ dcoeff_ffma_kernel(const float* __restrict__ x, const float* __restrict__ dy,
             dreg[v] = r;
         }
     };
-    // rows beyond b_end carry x = 0 -> T_d(0) != 0, but their dY row is zero
+    // rows beyond b_end carry x = 0 -> a non-zero basis value, but their dY row is zero
     auto generate = [&](int buf) {
 #pragma unroll
         for (int j = 0; j < MAXP; ++j) {
             const int p = tid + j * 256;
             if (p < npairs) {
                 const int bb = p / ti, ii = p % ti;
-                const float t = tanh_exact(xreg[j]);
-                const float t2 = 2.f * t;
+                const float u = rec.normalize(xreg[j]);
+                const float c = rec.carry(u);
                 float* dstA = &As[buf][bb][ii * dp1];
-                float tm1 = 1.f, tm2 = t;
+                float tm1 = 1.f, tm2 = rec.before_first(u);
                 dstA[0] = 1.f;
                 for (int d = 1; d < dp1; ++d) {
-                    const float v = fmaf(t2, tm1, -tm2);
+                    const float v = rec.next(d, c, tm1, tm2);
                     dstA[d] = v; tm2 = tm1; tm1 = v;
                 }
             }
@@ -224,9 +224,10 @@ int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, 
     return p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
 }
 
-int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
-                       int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
-                       cudaStream_t s) {
+template <class REC>
+static int launch_dcoeff_ffma_rec(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
+                                  int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
+                                  cudaStream_t s, const REC& rec) {
     const DcoeffPlan p = dcoeff_plan(B, in, out, deg);
     const int dp1 = (int)deg + 1;
     const int64_t n = in * out * dp1;
@@ -236,15 +237,25 @@ int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int
     const unsigned grid = (unsigned)((int64_t)p.i_tiles * p.n_tiles * p.splits);
     const int add = direct && accumulate;
     if (p.g_n == 2)
-        dcoeff_ffma_kernel<2><<<grid, 256, 0, s>>>(x, dy, dst, B, (int)in, (int)out, dp1, p.TI,
-                                                  p.i_tiles, p.n_tiles, p.rows_per_split, n, add);
+        dcoeff_ffma_kernel<2, REC><<<grid, 256, 0, s>>>(x, dy, dst, B, (int)in, (int)out, dp1, p.TI,
+                                                       p.i_tiles, p.n_tiles, p.rows_per_split, n, add, rec);
     else
-        dcoeff_ffma_kernel<1><<<grid, 256, 0, s>>>(x, dy, dst, B, (int)in, (int)out, dp1, p.TI,
-                                                  p.i_tiles, p.n_tiles, p.rows_per_split, n, add);
+        dcoeff_ffma_kernel<1, REC><<<grid, 256, 0, s>>>(x, dy, dst, B, (int)in, (int)out, dp1, p.TI,
+                                                       p.i_tiles, p.n_tiles, p.rows_per_split, n, add, rec);
     int rc = check_cuda(cudaGetLastError());
     if (rc) return rc;
     if (!direct) rc = launch_dcoeff_reduce(reinterpret_cast<const float*>(ws), dc, n, p.splits, accumulate, s);
     return rc;
+}
+
+int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
+                       int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
+                       cudaStream_t s, const RecurrenceTable* rec) {
+    if (rec == nullptr)
+        return launch_dcoeff_ffma_rec(x, dy, dc, ws, ws_bytes, B, in, out, deg, accumulate, s, ChebyshevRec());
+    TableRec t;
+    t.t = *rec;
+    return launch_dcoeff_ffma_rec(x, dy, dc, ws, ws_bytes, B, in, out, deg, accumulate, s, t);
 }
 
 // ---------------------------------------------------------------------------
@@ -292,10 +303,11 @@ static int static_scratch_address(void** out) {
 // all outputs (8 per stage), then each (row, input) pair folds its deg+1 values
 // of G with d*U_{d-1}(t) and the tanh derivative.
 // ---------------------------------------------------------------------------
+template <class REC>
 __global__ void __launch_bounds__(256)
 dx_ffma_kernel(const float* __restrict__ x, const float* __restrict__ dy,
                const float* __restrict__ coeffs, float* __restrict__ dx, int64_t B, int in,
-               int out, int dp1, int TI, int i_tiles) {
+               int out, int dp1, int TI, int i_tiles, const __grid_constant__ REC rec) {
     constexpr int BM = 64;
     constexpr int LDA = BM + 4;
     constexpr int LDG = BWD_KK + 1;
@@ -386,27 +398,48 @@ dx_ffma_kernel(const float* __restrict__ x, const float* __restrict__ dy,
         const int bb = p / ti, ii = p % ti;
         const int64_t row = m0 + bb;
         if (row >= B) continue;
-        const float t = tanh_exact(x[row * in + i0 + ii]);
-        const float t2 = 2.f * t;
         const float* g = &Gs[bb][ii * dp1];
-        float um1 = 1.f, um2 = 0.f, sum = 0.f;  // U_0 = 1, U_{-1} = 0
-        for (int d = 1; d < dp1; ++d) {
-            sum = fmaf((float)d * um1, g[d], sum);   // T_d' = d U_{d-1}
-            const float u = fmaf(t2, um1, -um2);
-            um2 = um1; um1 = u;
+        if constexpr (REC::kChebyshev) {
+            const float t = tanh_exact(x[row * in + i0 + ii]);
+            const float t2 = 2.f * t;
+            float um1 = 1.f, um2 = 0.f, sum = 0.f;  // U_0 = 1, U_{-1} = 0
+            for (int d = 1; d < dp1; ++d) {
+                sum = fmaf((float)d * um1, g[d], sum);   // T_d' = d U_{d-1}
+                const float u = fmaf(t2, um1, -um2);
+                um2 = um1; um1 = u;
+            }
+            dx[row * in + i0 + ii] = fmaf(-t, t, 1.f) * sum;
+        } else {
+            // P_d and dP_d/du side by side from the recurrence and its derivative
+            const float u = rec.normalize(x[row * in + i0 + ii]);
+            float pm1 = 1.f, pm2 = 0.f, dpm1 = 0.f, dpm2 = 0.f, sum = 0.f;
+            for (int d = 1; d < dp1; ++d) {
+                const float dp = rec.dnext(d, u, pm1, dpm1, dpm2);
+                const float p = rec.next(d, u, pm1, pm2);
+                sum = fmaf(dp, g[d], sum);
+                pm2 = pm1; pm1 = p; dpm2 = dpm1; dpm1 = dp;
+            }
+            dx[row * in + i0 + ii] = rec.dnormalize(u) * sum;
         }
-        dx[row * in + i0 + ii] = fmaf(-t, t, 1.f) * sum;
     }
 }
 
 int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
-                   int64_t in, int64_t out, int64_t deg, cudaStream_t s) {
+                   int64_t in, int64_t out, int64_t deg, cudaStream_t s, const RecurrenceTable* rec) {
     const int dp1 = (int)deg + 1;
     const int TI = tile_inputs(in, dp1);
     const int i_tiles = (int)ceil_div(in, TI);
     const int64_t grid = ceil_div(B, 64) * i_tiles;
     if (grid > 0x7fffffffLL) return CHEBYKAN_EUNSUPPORTED;
-    dx_ffma_kernel<<<(unsigned)grid, 256, 0, s>>>(x, dy, coeffs, dx, B, (int)in, (int)out, dp1, TI, i_tiles);
+    if (rec == nullptr) {
+        dx_ffma_kernel<ChebyshevRec><<<(unsigned)grid, 256, 0, s>>>(x, dy, coeffs, dx, B, (int)in, (int)out, dp1, TI,
+                                                                    i_tiles, ChebyshevRec());
+    } else {
+        TableRec t;
+        t.t = *rec;
+        dx_ffma_kernel<TableRec><<<(unsigned)grid, 256, 0, s>>>(x, dy, coeffs, dx, B, (int)in, (int)out, dp1, TI,
+                                                                i_tiles, t);
+    }
     return check_cuda(cudaGetLastError());
 }
 

@@ -66,6 +66,51 @@ __device__ __forceinline__ float tanh_fast(float x) {
     return fmaf(-2.0f, r, 1.0f);
 }
 
+// ---- polynomial families ------------------------------------------------------
+// Every layer of the reference that is "normalise, three-term recurrence, einsum('bid,iod->bo')" fits
+//   u = scale * tanh(x)            (or the affine map u = scale * (x - shift) + offset)
+//   P_0 = 1,  P_d = (A[d] u + B[d]) P_{d-1} - C[d] P_{d-2}   for d >= 1, with P_{-1} = 0
+// (kan/basis/jacobi.py:136-188, kan/basis/hermite.py:163-233).  The fp32 kernels take the recurrence as a
+// policy: ChebyshevRec is the compile-time special case (A = 2, C = 1, P_1 = u), TableRec reads the
+// coefficients from a table passed by value as a __grid_constant__ kernel parameter.
+struct RecurrenceTable {
+    float scale, shift, offset;
+    int32_t affine;               // 0: u = scale * tanh(x);  1: u = scale * (x - shift) + offset
+    float A[128], B[128], C[128]; // entry 0 unused; entry 1 holds P_1 = A[1] u + B[1], C[1] = 0
+};
+
+struct ChebyshevRec {
+    static constexpr bool kChebyshev = true;
+    __device__ __forceinline__ float normalize(float x) const { return tanh_exact(x); }
+    // value carried per point between degrees (2u), and the stand-in for P_{-1} that makes degree 1 come out as u
+    __device__ __forceinline__ float carry(float u) const { return 2.f * u; }
+    __device__ __forceinline__ float before_first(float u) const { return u; }
+    __device__ __forceinline__ float next(int, float c, float pm1, float pm2) const { return fmaf(c, pm1, -pm2); }
+};
+
+struct TableRec {
+    static constexpr bool kChebyshev = false;
+    RecurrenceTable t;
+    __device__ __forceinline__ float normalize(float x) const {
+        return t.affine ? fmaf(t.scale, x - t.shift, t.offset) : t.scale * tanh_exact(x);
+    }
+    // du/dx at a point whose normalised value is u
+    __device__ __forceinline__ float dnormalize(float u) const {
+        if (t.affine) return t.scale;
+        const float th = u / t.scale;
+        return t.scale * fmaf(-th, th, 1.f);
+    }
+    __device__ __forceinline__ float carry(float u) const { return u; }
+    __device__ __forceinline__ float before_first(float) const { return 0.f; }
+    __device__ __forceinline__ float next(int d, float u, float pm1, float pm2) const {
+        return fmaf(fmaf(t.A[d], u, t.B[d]), pm1, -(t.C[d] * pm2));
+    }
+    // derivative with respect to u of the same recurrence
+    __device__ __forceinline__ float dnext(int d, float u, float pm1, float dpm1, float dpm2) const {
+        return fmaf(t.A[d], pm1, fmaf(fmaf(t.A[d], u, t.B[d]), dpm1, -(t.C[d] * dpm2)));
+    }
+};
+
 // thread-local record of the last CUDA error seen by an entry point
 void set_last_cuda_error(int e);
 inline int check_cuda(cudaError_t e) {
@@ -95,8 +140,9 @@ struct LnFusion {
 // ---- launchers implemented in the .cu files ------------------------------------
 int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, int mode,
                 cudaStream_t s);
+// fp32 launchers: `rec` == nullptr is the Chebyshev layer, otherwise the family described by the table
 int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
-                    int64_t deg, cudaStream_t s);
+                    int64_t deg, cudaStream_t s, const RecurrenceTable* rec = nullptr);
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
                   int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion());
 // narrow layers (<= 128 outputs): the basis tile lives in tensor memory (fwd_ts.cu)
@@ -106,7 +152,7 @@ int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t i
 int64_t dcoeff_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
 int launch_dcoeff_ffma(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes,
                        int64_t B, int64_t in, int64_t out, int64_t deg, int accumulate,
-                       cudaStream_t s);
+                       cudaStream_t s, const RecurrenceTable* rec = nullptr);
 int launch_dcoeff_reduce(const float* ws, float* dc, int64_t n, int splits, int accumulate, cudaStream_t s);
 // FP32X3 backward: the tf32 tensor-core kernels run three times on head/tail operands.  Worth it only for
 // large products (three launches and two operand splits against one FFMA launch), and the dx kernel keeps a whole
@@ -127,7 +173,7 @@ int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t de
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
                      int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3 = 0);
 int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
-                   int64_t in, int64_t out, int64_t deg, cudaStream_t s);
+                   int64_t in, int64_t out, int64_t deg, cudaStream_t s, const RecurrenceTable* rec = nullptr);
 bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
 int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3);
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,

@@ -38,10 +38,10 @@ __device__ __forceinline__ float ld_peer_smem(const float* local, uint32_t rank)
     return v;
 }
 
-template <int G_M, int G_N, bool KSPLIT = false>
+template <int G_M, int G_N, bool KSPLIT, class REC>
 __global__ void __launch_bounds__(256, 2)
 fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float* __restrict__ y,
-                int64_t B, int in, int out, int dp1, int n_pad, int n_tiles) {
+                int64_t B, int in, int out, int dp1, int n_pad, int n_tiles, const __grid_constant__ REC rec) {
     constexpr int BM = 64 * G_M, BN = 64 * G_N;
     constexpr int LDA = BM + 4;         // +4 keeps the producer's stores bank-conflict free
     constexpr int EPT = BM / 32;        // (row, input) pairs per thread per stage
@@ -88,15 +88,15 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
         if (d == 0) {
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
-                const float t = tanh_exact(xpre[j]);
-                tt[j] = 2.f * t; tm1[j] = 1.f; tm2[j] = t;   // T_0 = 1, T_{-1} = T_1 = t
+                const float u = rec.normalize(xpre[j]);
+                tt[j] = rec.carry(u); tm1[j] = 1.f; tm2[j] = rec.before_first(u);   // Chebyshev: T_0 = 1, T_{-1} = T_1 = t
                 phi[j] = 1.f;
             }
             load_x(s / dp1 + 1);
         } else {
 #pragma unroll
             for (int j = 0; j < EPT; ++j) {
-                phi[j] = fmaf(tt[j], tm1[j], -tm2[j]);
+                phi[j] = rec.next(d, tt[j], tm1[j], tm2[j]);
                 tm2[j] = tm1[j]; tm1[j] = phi[j];
             }
         }
@@ -200,8 +200,9 @@ fwd_ffma_kernel(const float* __restrict__ x, const float* __restrict__ wf, float
         }
 }
 
-int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
-                    int64_t deg, cudaStream_t s) {
+template <class REC>
+static int launch_fwd_ffma_rec(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
+                               int64_t deg, cudaStream_t s, const REC& rec) {
     const PackedDims p = packed_dims(in, out, deg, CHEBYKAN_MODE_FP32);
     const int dp1 = (int)deg + 1;
     const bool wide = (p.n_pad % 128) == 0;
@@ -210,12 +211,12 @@ int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_
     if (tiles128 >= 2 * 148) {
         if (wide) {
             const int nt = (int)(p.n_pad / 128);
-            fwd_ffma_kernel<2, 2><<<(unsigned)(ceil_div(B, 128) * nt), 256, 0, s>>>(
-                x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt);
+            fwd_ffma_kernel<2, 2, false, REC><<<(unsigned)(ceil_div(B, 128) * nt), 256, 0, s>>>(
+                x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt, rec);
         } else {
             const int nt = (int)(p.n_pad / 64);
-            fwd_ffma_kernel<2, 1><<<(unsigned)(ceil_div(B, 128) * nt), 256, 0, s>>>(
-                x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt);
+            fwd_ffma_kernel<2, 1, false, REC><<<(unsigned)(ceil_div(B, 128) * nt), 256, 0, s>>>(
+                x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt, rec);
         }
     } else {
         const int nt = (int)(p.n_pad / 64);
@@ -231,13 +232,21 @@ int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_
             attrs[0].id = cudaLaunchAttributeClusterDimension;
             attrs[0].val.clusterDim.x = (unsigned)ks; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
             cfg.attrs = attrs; cfg.numAttrs = 1;
-            return check_cuda(cudaLaunchKernelEx(&cfg, fwd_ffma_kernel<1, 1, true>, x, wf, y, B, (int)in, (int)out, dp1,
-                                                 (int)p.n_pad, nt));
+            return check_cuda(cudaLaunchKernelEx(&cfg, fwd_ffma_kernel<1, 1, true, REC>, x, wf, y, B, (int)in, (int)out, dp1,
+                                                 (int)p.n_pad, nt, rec));
         }
-        fwd_ffma_kernel<1, 1><<<(unsigned)tiles, 256, 0, s>>>(
-            x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt);
+        fwd_ffma_kernel<1, 1, false, REC><<<(unsigned)tiles, 256, 0, s>>>(
+            x, wf, y, B, (int)in, (int)out, dp1, (int)p.n_pad, nt, rec);
     }
     return check_cuda(cudaGetLastError());
+}
+
+int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
+                    int64_t deg, cudaStream_t s, const RecurrenceTable* rec) {
+    if (rec == nullptr) return launch_fwd_ffma_rec(x, wf, y, B, in, out, deg, s, ChebyshevRec());
+    TableRec t;
+    t.t = *rec;
+    return launch_fwd_ffma_rec(x, wf, y, B, in, out, deg, s, t);
 }
 
 }  // namespace chebykan

@@ -5,6 +5,7 @@ sm_100a kernels of libchebykan_b200.so.  Nothing here computes on the CPU.
 """
 from __future__ import annotations
 
+import ctypes
 import os
 
 import torch
@@ -242,6 +243,120 @@ def basis_functions(t: torch.Tensor, degree: int) -> torch.Tensor:
     with torch.cuda.device(t.device):
         rc = _lib.load().chebykan_basis_functions(t.data_ptr(), phi.data_ptr(), t.numel(), degree, _stream(t))
     _lib.check(rc, "chebykan_basis_functions")
+    return phi
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Jacobi / Hermite layers: the fp32 kernels with the family's recurrence as a launch parameter
+# ---------------------------------------------------------------------------------------------------------------
+def make_family(kind: str, alpha: float = 0.0, beta: float = 0.0, scale: float = 0.0, affine: bool = False,
+                shift: float = 0.0, offset: float = 0.0) -> "_lib.Family":
+    """Host-side description of a polynomial family: kind in {'chebyshev', 'jacobi', 'hermite', 'hermite_prob'};
+    u = scale * tanh(x) (scale 0 = the kind's default) or, with affine, u = scale * (x - shift) + offset."""
+    kinds = {"chebyshev": _lib.FAMILY_CHEBYSHEV, "jacobi": _lib.FAMILY_JACOBI, "hermite": _lib.FAMILY_HERMITE,
+             "hermite_prob": _lib.FAMILY_HERMITE_PROB}
+    if kind not in kinds:
+        raise ValueError(f"family must be one of {sorted(kinds)}, got {kind!r}")
+    return _lib.Family(kinds[kind], float(alpha), float(beta), int(bool(affine)), float(scale), float(shift),
+                       float(offset))
+
+
+def family_table(family, degree: int):
+    """(a, b, c) of P_d = (a[d] u + b[d]) P_{d-1} - c[d] P_{d-2} as the kernels use them: three CPU float32
+    tensors of degree+1 entries (entry 0 unused).  Host only: needs no GPU."""
+    bufs = [(ctypes.c_float * (degree + 1))() for _ in range(3)]
+    rc = _lib.load().chebykan_family_table(ctypes.byref(family), degree, *[ctypes.addressof(b) for b in bufs])
+    _lib.check(rc, "chebykan_family_table")
+    return tuple(torch.tensor(list(b), dtype=torch.float32) for b in bufs)
+
+
+def family_forward(family, x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, degree: int,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[B,out] = sum_i sum_d C[i,o,d] P_d(u(x[b,i])) from the FP32 packed coefficients."""
+    _require(x, "x")
+    if x.dim() != 2 or x.shape[1] != in_dim:
+        raise RuntimeError(f"x must have shape [B, {in_dim}]")
+    need = packed_bytes(in_dim, out_dim, degree, "fp32")
+    if packed.numel() * packed.element_size() < need:
+        raise RuntimeError("packed coefficient buffer is too small for this shape")
+    B = x.shape[0]
+    if out is None:
+        out = torch.empty(B, out_dim, dtype=torch.float32, device=x.device)
+    else:
+        _require(out, "out")
+        if out.shape != (B, out_dim):
+            raise RuntimeError(f"out must have shape [{B}, {out_dim}]")
+    with _Range("chebykan.family_forward"), torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_family_fwd(ctypes.byref(family), x.data_ptr(), packed.data_ptr(), out.data_ptr(), B,
+                                             in_dim, out_dim, degree, _stream(x))
+    _lib.check(rc, "chebykan_family_fwd")
+    return out
+
+
+def family_bwd_dcoeff(family, x: torch.Tensor, dy: torch.Tensor, in_dim: int, out_dim: int, degree: int,
+                      out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """dC[in,out,deg+1] = sum_b P_d(u(x[b,i])) dY[b,o]."""
+    _require(x, "x")
+    _require(dy, "dy")
+    B = x.shape[0]
+    if x.shape != (B, in_dim) or dy.shape != (B, out_dim):
+        raise RuntimeError("x must be [B, in] and dy [B, out]")
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty(in_dim, out_dim, degree + 1, dtype=torch.float32, device=x.device)
+        accumulate = False
+    else:
+        _require(out, "out")
+    ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DCOEFF, B, in_dim, out_dim, degree, _lib.MODE_FP32)
+    _lib.check(ws_bytes, "chebykan_workspace_bytes")
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
+    with _Range("chebykan.family_dcoeff"), torch.cuda.device(x.device):
+        rc = lib.chebykan_family_bwd_dcoeff(ctypes.byref(family), x.data_ptr(), dy.data_ptr(), out.data_ptr(),
+                                            ws.data_ptr(), ws_bytes, B, in_dim, out_dim, degree, int(accumulate),
+                                            _stream(x))
+    _lib.check(rc, "chebykan_family_bwd_dcoeff")
+    return out
+
+
+def family_bwd_dx(family, x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
+    """dx[B,in] = du/dx * sum_d P_d'(u) sum_o dY[b,o] C[i,o,d]."""
+    _require(x, "x")
+    _require(dy, "dy")
+    _require(coeffs, "coeffs")
+    n_in, n_out, dp1 = coeffs.shape
+    B = x.shape[0]
+    if x.shape != (B, n_in) or dy.shape != (B, n_out):
+        raise RuntimeError("x must be [B, in] and dy [B, out]")
+    if out is None:
+        out = torch.empty_like(x)
+    else:
+        _require(out, "out")
+    with _Range("chebykan.family_dx"), torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_family_bwd_dx(ctypes.byref(family), x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(),
+                                                out.data_ptr(), B, n_in, n_out, dp1 - 1, _stream(x))
+    _lib.check(rc, "chebykan_family_bwd_dx")
+    return out
+
+
+def family_normalize(family, x: torch.Tensor) -> torch.Tensor:
+    """u(x): the family's input normalisation, element-wise."""
+    _require(x, "x")
+    u = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        rc = _lib.load().chebykan_family_normalize(ctypes.byref(family), x.data_ptr(), u.data_ptr(), x.numel(), _stream(x))
+    _lib.check(rc, "chebykan_family_normalize")
+    return u
+
+
+def family_basis(family, u: torch.Tensor, degree: int) -> torch.Tensor:
+    """Phi[..., d] = P_d(u) for d = 0..degree at already normalised points u."""
+    _require(u, "u")
+    phi = torch.empty(*u.shape, degree + 1, dtype=torch.float32, device=u.device)
+    with torch.cuda.device(u.device):
+        rc = _lib.load().chebykan_family_basis(ctypes.byref(family), u.data_ptr(), phi.data_ptr(), u.numel(), degree,
+                                               _stream(u))
+    _lib.check(rc, "chebykan_family_basis")
     return phi
 
 

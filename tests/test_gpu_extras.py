@@ -111,3 +111,73 @@ def test_cfg5_training_trajectory_vs_oracle_model(mode, tol):
         assert o.rel_l2(a.detach(), p0) > 1e-2                 # the steps did change the coefficients
         assert o.rel_l2(b.detach().cpu(), a.detach()) <= 2.5 * tol
         assert o.rel_l2(b.detach().cpu() - p0, a.detach() - p0) <= 25 * tol      # the update itself, not just the end point
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Full BASELINE sizes, through properties that need no CPU oracle run of that size: rows are independent, so a
+# sample of rows of the full-size result can be checked against the oracle; the coefficient gradient is additive
+# over row blocks and linear in dY.
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("mode,tol", [("bf16", TC_TOL), ("tf32", TC_TOL)])
+def test_full_size_cfg4_stack_row_sample(mode, tol):
+    """Configuration 4 at full size (32768 rows through 4 x (2048 -> 2048, degree 4) with LayerNorms): 48 sampled rows of
+    the GPU result against the oracle model, for the plain and the LayerNorm-fused stack."""
+    cfg = workloads.CONFIGS["cfg4"]
+    ref = workloads.build_model(cfg, OracleLayer)
+    ours = workloads.build_model(cfg, kan_b200.ChebyKANLayer, math_mode=mode)
+    if mode == "bf16":            # coefficients stored in bf16: the oracle evaluates with the same rounded values
+        with torch.no_grad():
+            for m in ref:
+                if hasattr(m, "cheby_coeffs"):
+                    m.cheby_coeffs.copy_(m.cheby_coeffs.bfloat16().float())
+    ours = ours.cuda()
+    x, _ = workloads.make_inputs(cfg)
+    xd = x.cuda()
+    rows = torch.cat([torch.tensor([0, 1, 127, 128, 255, 256, 16383, 16384, 32767]), torch.arange(20000, 20039)])
+    with torch.no_grad():
+        y = ours(xd)
+        y_fused = kan_b200.fuse_layernorm(ours)(xd)
+        y_ref = ref(x[rows])
+    ops.check_status()
+    assert y.shape == (cfg.batch, 2048)
+    # four layers compound the per-layer rounding: allow twice the single-kernel tolerance
+    assert o.rel_l2(y[rows.cuda()].cpu(), y_ref) <= 2 * tol
+    assert o.rel_l2(y_fused[rows.cuda()].cpu(), y_ref) <= 2 * tol
+
+
+@pytest.mark.parametrize("mode", ["tf32", "bf16"])
+def test_full_size_cfg5_layer_properties(mode):
+    """Configuration 5's layer at full size (1048576 x 64 -> 64, degree 32, x ~ U(-3,3)): forward and dx on sampled rows
+    against the oracle; dC additive over the two halves of the batch, linear in dY, and equal to the oracle on a
+    32768-row block."""
+    B, n_in, n_out, deg = 1048576, 64, 64, 32
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.rand(B, n_in, device="cuda", generator=g) * 6 - 3
+    dy = torch.randn(B, n_out, device="cuda", generator=g)
+    coeffs = torch.randn(n_in, n_out, deg + 1, device="cuda", generator=g) / (n_in * (deg + 1))
+    packed = ops.pack_coeffs(coeffs, mode)
+    y = ops.forward(x, packed, n_in, n_out, deg, mode)
+    dx = ops.bwd_dx(x, dy, coeffs, mode)
+    dC = ops.bwd_dcoeff(x, dy, n_in, n_out, deg, mode)
+    torch.cuda.synchronize()
+    ops.check_status()
+    rows = torch.cat([torch.tensor([0, 1, 127, 128, 255, 256, 524287, 524288, B - 1]), torch.arange(700000, 700055)]).cuda()
+    c_cpu = coeffs.cpu()
+    c_fwd = c_cpu.bfloat16().float() if mode == "bf16" else c_cpu
+    y_ref = o.forward(x[rows].cpu(), c_fwd)
+    _, _, dx_ref = o.forward_backward(x[rows].cpu(), c_cpu, dy[rows].cpu())
+    assert o.rel_l2(y[rows].cpu(), y_ref) <= TC_TOL
+    assert o.rel_l2(dx[rows].cpu(), dx_ref) <= TC_TOL
+    # additivity over row blocks (each half is its own launch with its own batch split and dY scale)
+    h = B // 2
+    dC_a = ops.bwd_dcoeff(x[:h].contiguous(), dy[:h].contiguous(), n_in, n_out, deg, mode)
+    dC_b = ops.bwd_dcoeff(x[h:].contiguous(), dy[h:].contiguous(), n_in, n_out, deg, mode)
+    assert o.rel_l2(dC_a + dC_b, dC) <= 1e-4
+    # linearity in dY (powers of two are exact through the fp16 scaling; a general factor rounds differently)
+    dC_4 = ops.bwd_dcoeff(x, dy * 4.0, n_in, n_out, deg, mode)
+    assert torch.equal(dC_4, 4.0 * dC)
+    # a 32768-row block against the oracle
+    blk = slice(300000, 300000 + 32768)
+    _, dC_ref, _ = o.forward_backward(x[blk].cpu(), c_cpu, dy[blk].cpu(), need_dx=False)
+    dC_blk = ops.bwd_dcoeff(x[blk].contiguous(), dy[blk].contiguous(), n_in, n_out, deg, mode)
+    assert o.rel_l2(dC_blk.cpu(), dC_ref) <= TC_TOL
