@@ -453,6 +453,36 @@ def layer_record(ctx, mode, op, B_rank, B_total, shape, ms, peaks, tf32_peak, ex
     return rec
 
 
+def sub_family(ctx: Ctx, kind: str, B: int, n_in: int, n_out: int, deg: int, peaks, **family_kw):
+    """Forward (fp32 FFMA kernel and bf16 tensor-core kernel), dC and dx (fp32) of a Jacobi / Hermite layer, all with a
+    table-driven recurrence, on B resident rows of this rank; ms per launch and the rate of each against its pipe."""
+    from kan_b200 import ops
+    fam = ops.make_family(kind, **family_kw)
+    g = torch.Generator().manual_seed(77 + ctx.rank)
+    x = torch.randn(B, n_in, generator=g).to(ctx.dev)
+    dy = torch.randn(B, n_out, generator=g).to(ctx.dev)
+    coeffs = (torch.randn(n_in, n_out, deg + 1, generator=g) / (n_in * (deg + 1))).to(ctx.dev)
+    packed = ops.pack_coeffs(coeffs, "fp32")
+    y, dc, dx = torch.empty(B, n_out, device=ctx.dev), torch.empty_like(coeffs), torch.empty_like(x)
+    packed_bf16 = ops.pack_coeffs(coeffs, "bf16")
+    steps = {"fwd": lambda: ops.family_forward(fam, x, packed, n_in, n_out, deg, "fp32", out=y),
+             "fwd_bf16": lambda: ops.family_forward(fam, x, packed_bf16, n_in, n_out, deg, "bf16", out=y),
+             "dcoeff": lambda: ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, out=dc),
+             "dx": lambda: ops.family_bwd_dx(fam, x, dy, coeffs, out=dx)}
+    flops = 2.0 * B * n_in * (deg + 1) * n_out
+    rec = {"family": dict(family_kw, kind=kind), "rows_per_gpu": B, "shape": [n_in, n_out, deg], "dtype": "fp32"}
+    for op, fn in steps.items():
+        ms, _ = ctx.time_steps(fn, 3, 3, False, flush_l2=B * 4 * (n_in + n_out) < 2 * L2_BYTES)
+        peak, note = tensor_peak("bf16" if op == "fwd_bf16" else "fp32", "fwd", peaks, None)
+        rec[op] = {"ms_per_step": ms, "value": B * ctx.world / (ms * 1e-3), "unit": UNIT,
+                   "roofline": {"bound": "tensor" if op == "fwd_bf16" else "ffma", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                                "frac": flops / (ms * 1e-3) / 1e12 / peak, "peak_note": note}}
+    ops.check_status()
+    del x, dy, coeffs, packed, packed_bf16, y, dc, dx
+    free_gpu()
+    return rec
+
+
 def sub_sustained(ctx: Ctx, state, B: int, peaks: dict, seconds: float = 2.0):
     """Back-to-back launches for `seconds`: the clock settles under the power limit.  Quoted against the sustained
     cuBLAS figure, with time x median SM clock beside it."""
@@ -684,6 +714,8 @@ def run_ours(args):
         if ctx.world == 1:
             sub["cfg5_train_tf32_torch_loss"] = sub_train_cfg5(ctx, "tf32", ks, kw, peaks, tf32_peak, torch_loss=True)
             sub["cfg5_train_fp32x3"] = sub_train_cfg5(ctx, "fp32x3", 3, kw, peaks, tf32_peak)
+            sub["cfg3_shape_jacobi_fp32"] = sub_family(ctx, "jacobi", 16384, n_in, n_out, deg, peaks, alpha=0.5, beta=-0.3)
+            sub["cfg3_shape_hermite_fp32"] = sub_family(ctx, "hermite", 16384, n_in, n_out, deg, peaks)
             for name in ("cfg1", "cfg2"):
                 sub[name + "_train_eager"] = sub_small_train(ctx, name, False, 50, 5)
                 sub[name + "_train_graph"] = sub_small_train(ctx, name, True, 200, 5)

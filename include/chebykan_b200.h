@@ -212,11 +212,14 @@ int chebykan_basis_functions(const float* t, float* phi, int64_t n, int64_t deg,
  *                                them against the Chebyshev entry points above).
  * A family is described on the HOST by a chebykan_family; the library turns it into the recurrence
  * table the kernels take as a launch parameter, so there is nothing to upload or keep alive.
- * `packed` is the FP32 layout of chebykan_pack_coeffs (the packing does not depend on the family) and
+ * `packed` is chebykan_pack_coeffs' layout for `mode` (the packing does not depend on the family) and
  * the workspace of chebykan_family_bwd_dcoeff is chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DCOEFF, ...,
- * CHEBYKAN_MODE_FP32).  All three layer functions compute in fp32 on the FFMA pipe with a correctly
- * rounded tanh; the reference has no hand-written backward, the two bwd functions return what autograd
- * derives from the forward.  chebykan_family_normalize / chebykan_family_basis are the basis object's
+ * CHEBYKAN_MODE_FP32).  chebykan_family_fwd runs in CHEBYKAN_MODE_FP32 (FFMA pipe, correctly rounded
+ * tanh; status may be NULL), CHEBYKAN_MODE_TF32 or CHEBYKAN_MODE_BF16 (the tcgen05 kernel of
+ * chebykan_fwd with the family's recurrence in its producer warps; status as for chebykan_fwd);
+ * CHEBYKAN_MODE_FP32X3 returns CHEBYKAN_EUNSUPPORTED.  The two bwd functions always compute in fp32 on
+ * the FFMA pipe; the reference has no hand-written backward, they return what autograd derives from
+ * the forward.  chebykan_family_normalize / chebykan_family_basis are the basis object's
  * normalize_input / basis_functions on flat arrays of n elements (phi has n*(deg+1) elements), and
  * chebykan_family_table copies the recurrence P_d = (a[d] u + b[d]) P_{d-1} - c[d] P_{d-2}
  * (d = 1..deg, P_0 = 1, P_{-1} = 0; deg+1 floats per HOST array, entry 0 unused) for inspection.
@@ -237,7 +240,8 @@ typedef struct chebykan_family {
 int chebykan_family_table(const chebykan_family* family, int64_t deg, float* a_host, float* b_host,
                           float* c_host);
 int chebykan_family_fwd(const chebykan_family* family, const float* x, const void* packed, float* y,
-                        int64_t B, int64_t in, int64_t out, int64_t deg, void* stream);
+                        int64_t B, int64_t in, int64_t out, int64_t deg, int mode, int32_t* status,
+                        void* stream);
 int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, const float* dy,
                                float* dcoeffs, void* workspace, int64_t workspace_bytes, int64_t B,
                                int64_t in, int64_t out, int64_t deg, int accumulate, void* stream);

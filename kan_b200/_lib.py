@@ -49,7 +49,8 @@ SIGNATURES = {
     "chebykan_normalize_input": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "chebykan_basis_functions": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "chebykan_family_table": (c_int, [_FAM, c_int64, c_void_p, c_void_p, c_void_p]),
-    "chebykan_family_fwd": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "chebykan_family_fwd": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
+                                    c_void_p, c_void_p]),
     "chebykan_family_bwd_dcoeff": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
                                            c_int64, c_int64, c_int, c_void_p]),
     "chebykan_family_bwd_dx": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,

@@ -143,8 +143,10 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
 // fp32 launchers: `rec` == nullptr is the Chebyshev layer, otherwise the family described by the table
 int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
                     int64_t deg, cudaStream_t s, const RecurrenceTable* rec = nullptr);
+// `rec` != nullptr: another polynomial family (bf16 / tf32 modes, no LayerNorm fusion)
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
-                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion());
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion(),
+                  const RecurrenceTable* rec = nullptr);
 // narrow layers (<= 128 outputs): the basis tile lives in tensor memory (fwd_ts.cu)
 bool fwd_ts_supported(int64_t B, int64_t in, int64_t out, int64_t deg, int mode);
 int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out, int64_t deg, int mode,

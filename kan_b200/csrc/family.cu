@@ -1,7 +1,8 @@
-// Polynomial families other than Chebyshev on the fp32 kernels: Jacobi and Hermite layers of the reference
+// Polynomial families other than Chebyshev: Jacobi and Hermite layers of the reference
 // (kan/layers/jacobikan.py:20-68, kan/layers/hermitekan.py:22-83) share the Chebyshev layer's structure, so the
-// forward, dC and dx kernels take the family's three-term recurrence as a table and are otherwise unchanged.
-// This file builds the table on the host from the family's description and holds the entry points.
+// fp32 forward, dC and dx kernels and the tcgen05 forward take the family's three-term recurrence as a table and are
+// otherwise unchanged.  This file builds the table on the host from the family's description and holds the entry
+// points.
 #include <math.h>
 #include "common.cuh"
 
@@ -100,16 +101,22 @@ int chebykan_family_table(const chebykan_family* family, int64_t deg, float* a_h
 }
 
 int chebykan_family_fwd(const chebykan_family* family, const float* x, const void* packed, float* y, int64_t B,
-                        int64_t in, int64_t out, int64_t deg, void* stream) {
+                        int64_t in, int64_t out, int64_t deg, int mode, int32_t* status, void* stream) {
     RecurrenceTable t;
     if (!family_shape_ok(B, in, out, deg) || !packed) return CHEBYKAN_EINVAL;
+    if (mode != CHEBYKAN_MODE_FP32 && mode != CHEBYKAN_MODE_TF32 && mode != CHEBYKAN_MODE_BF16)
+        return mode == CHEBYKAN_MODE_FP32X3 ? CHEBYKAN_EUNSUPPORTED : CHEBYKAN_EINVAL;
     int rc = build_table(family, deg, &t);
     if (rc) return rc;
     if (B == 0) return CHEBYKAN_OK;
     if (!x || !y) return CHEBYKAN_EINVAL;
     if (!aligned16(x) || !aligned16(y) || !aligned16(packed)) return CHEBYKAN_EALIGN;
     if ((rc = check_device())) return rc;
-    return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg, (cudaStream_t)stream, &t);
+    if (mode == CHEBYKAN_MODE_FP32)
+        return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg, (cudaStream_t)stream, &t);
+    // bf16 / tf32: the tcgen05 kernel of the Chebyshev layer with the table-driven recurrence in its producer warps
+    if (!status) return CHEBYKAN_EINVAL;
+    return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream, LnFusion(), &t);
 }
 
 int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, const float* dy, float* dcoeffs,

@@ -93,12 +93,22 @@ struct Smem {
     static constexpr uint32_t TMEM_COLS = NACC * NSUB * BN;
 };
 
-template <int MODE, int BN, int NSUB, bool LN, int CG>
+// Kernel variants: 0 = the plain Chebyshev layer, 1 = with LayerNorm fused on either side, 2 = another polynomial
+// family, whose recurrence table arrives as one more by-value parameter (the other variants pass an empty struct).
+constexpr int VAR_PLAIN = 0, VAR_LN = 1, VAR_FAMILY = 2;
+struct NoTable {};
+template <int VAR> struct VariantTable { using type = NoTable; };
+template <> struct VariantTable<VAR_FAMILY> { using type = RecurrenceTable; };
+
+template <int MODE, int BN, int NSUB, int VAR, int CG>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
-              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad) {
+              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad,
+              const __grid_constant__ typename VariantTable<VAR>::type rec) {
+    constexpr bool LN = VAR == VAR_LN;
+    constexpr bool FAM = VAR == VAR_FAMILY;
     constexpr bool X3 = MODE == CHEBYKAN_MODE_FP32X3;
     constexpr int PP = X3 ? 2 : 1;
     using L = Smem<BN, NSUB, CG, PP>;
@@ -327,9 +337,15 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     bool finite = true;
 #pragma unroll
                     for (int e = 0; e < CH; ++e) {
-                        const float t = X3 ? tanhf(v[e]) : tanh_fast(v[e]);
+                        float t = X3 ? tanhf(v[e]) : tanh_fast(v[e]);
+                        if constexpr (FAM) {
+                            // the family's normalised input u, P_0 = 1 and P_{-1} = 0
+                            t = rec.affine ? fmaf(rec.scale, v[e] - rec.shift, rec.offset) : rec.scale * t;
+                            tt[j][e] = t; ta[j][e] = 1.f; tb[j][e] = 0.f;
+                        } else {
+                            tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
+                        }
                         finite = finite && (t == t);
-                        tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
                     }
                     inc[j] = finite ? TF32_HALF_ULP : 0u;
                 }
@@ -346,17 +362,35 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                 if (!emit(ta)) { alive = false; break; }
                 if (x_held && dp1 == 1) release_x();      // degree 0 only: the tile's values are never used
                 for (int d = 1; d < dp1; d += 2) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-#pragma unroll
-                        for (int e = 0; e < CH; ++e) tb[j][e] = fmaf(tt[j][e], ta[j][e], -tb[j][e]);
-                    if (!emit(tb)) { alive = false; break; }
-                    if (x_held) release_x();
-                    if (d + 1 < dp1) {
+                    if constexpr (FAM) {
+                        const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];   // P_d = (A u + B) P_{d-1} - C P_{d-2}
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
 #pragma unroll
-                            for (int e = 0; e < CH; ++e) ta[j][e] = fmaf(tt[j][e], tb[j][e], -ta[j][e]);
+                            for (int e = 0; e < CH; ++e)
+                                tb[j][e] = fmaf(fmaf(ra, tt[j][e], rb), ta[j][e], -(rc * tb[j][e]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+#pragma unroll
+                            for (int e = 0; e < CH; ++e) tb[j][e] = fmaf(tt[j][e], ta[j][e], -tb[j][e]);
+                    }
+                    if (!emit(tb)) { alive = false; break; }
+                    if (x_held) release_x();
+                    if (d + 1 < dp1) {
+                        if constexpr (FAM) {
+                            const float ra = rec.A[d + 1], rb = rec.B[d + 1], rc = rec.C[d + 1];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int e = 0; e < CH; ++e)
+                                    ta[j][e] = fmaf(fmaf(ra, tt[j][e], rb), tb[j][e], -(rc * ta[j][e]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                                for (int e = 0; e < CH; ++e) ta[j][e] = fmaf(tt[j][e], tb[j][e], -ta[j][e]);
+                        }
                         if (!emit(ta)) { alive = false; break; }
                     }
                 }
@@ -626,16 +660,17 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     }
 }
 
-template <int MODE, int BN, int NSUB, bool LN, int CG>
+template <int MODE, int BN, int NSUB, int VAR, int CG>
 int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
-               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
+               const typename VariantTable<VAR>::type& rec) {
     using L = Smem<BN, NSUB, CG, (MODE == CHEBYKAN_MODE_FP32X3) ? 2 : 1>;
     static bool attr_set[64] = {false};
     static int max_units[64] = {0};       // CTAs (or CTA pairs) that can be resident at once
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) return CHEBYKAN_EINVAL;
-    auto kernel = fwd_tc_kernel<MODE, BN, NSUB, LN, CG>;
+    auto kernel = fwd_tc_kernel<MODE, BN, NSUB, VAR, CG>;
     if (!attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -667,34 +702,41 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_tiles,
-                                         num_tiles, status, ln, n_pad));
+                                         num_tiles, status, ln, n_pad, rec));
 }
 
-// the LayerNorm-fused variant is a separate instantiation, so the plain kernel carries none of its registers
+// the LayerNorm-fused and the family variants are separate instantiations, so the plain kernel carries none of
+// their registers
 template <int MODE, int BN, int NSUB, int CG = 1>
 int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
-               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
-    if constexpr (MODE != CHEBYKAN_MODE_FP32X3) {   // no LayerNorm fusion in the FP32X3 mode (the entry point refuses it)
+               int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
+               const RecurrenceTable* rec) {
+    if constexpr (MODE != CHEBYKAN_MODE_FP32X3) {   // neither LayerNorm fusion nor families in the FP32X3 mode (the entry points refuse)
+        if (rec != nullptr)
+            return launch_one_ln<MODE, BN, NSUB, VAR_FAMILY, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, *rec);
         if (ln.stats_in != nullptr || ln.stats_out != nullptr)
-            return launch_one_ln<MODE, BN, NSUB, true, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+            return launch_one_ln<MODE, BN, NSUB, VAR_LN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, NoTable());
     }
-    return launch_one_ln<MODE, BN, NSUB, false, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln);
+    return launch_one_ln<MODE, BN, NSUB, VAR_PLAIN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, NoTable());
 }
 
 template <int MODE>
 int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, int cg, const float* x, float* y,
-                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln) {
-    if (bn == 64) return launch_one<MODE, 64, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
-    if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
-    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
-    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
-    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln);
+                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
+                const RecurrenceTable* rec) {
+    if (bn == 64) return launch_one<MODE, 64, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
+    if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
+    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
+    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
+    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
 }
 
 }  // namespace
 
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
-                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln) {
+                  int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln, const RecurrenceTable* rec) {
+    if (rec != nullptr && (mode == CHEBYKAN_MODE_FP32X3 || ln.stats_in != nullptr || ln.stats_out != nullptr))
+        return CHEBYKAN_EUNSUPPORTED;
     const PackedDims p = packed_dims(in, out, deg, mode);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
@@ -732,12 +774,12 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
     const int dp1 = (int)deg + 1;
     if (mode == CHEBYKAN_MODE_FP32X3)
         return launch_mode<CHEBYKAN_MODE_FP32X3>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                                 (int)p.n_pad, status, s, ln);
+                                                 (int)p.n_pad, status, s, ln, rec);
     if (mode == CHEBYKAN_MODE_BF16)
         return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                               (int)p.n_pad, status, s, ln);
+                                               (int)p.n_pad, status, s, ln, rec);
     return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                           (int)p.n_pad, status, s, ln);
+                                           (int)p.n_pad, status, s, ln, rec);
 }
 
 }  // namespace chebykan

@@ -271,12 +271,13 @@ def family_table(family, degree: int):
 
 
 def family_forward(family, x: torch.Tensor, packed: torch.Tensor, in_dim: int, out_dim: int, degree: int,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
-    """y[B,out] = sum_i sum_d C[i,o,d] P_d(u(x[b,i])) from the FP32 packed coefficients."""
+                   mode="fp32", out: torch.Tensor | None = None) -> torch.Tensor:
+    """y[B,out] = sum_i sum_d C[i,o,d] P_d(u(x[b,i])) from coefficients packed for `mode` ('fp32', 'tf32' or 'bf16')."""
     _require(x, "x")
     if x.dim() != 2 or x.shape[1] != in_dim:
         raise RuntimeError(f"x must have shape [B, {in_dim}]")
-    need = packed_bytes(in_dim, out_dim, degree, "fp32")
+    m = _mode(mode)
+    need = packed_bytes(in_dim, out_dim, degree, m)
     if packed.numel() * packed.element_size() < need:
         raise RuntimeError("packed coefficient buffer is too small for this shape")
     B = x.shape[0]
@@ -288,7 +289,7 @@ def family_forward(family, x: torch.Tensor, packed: torch.Tensor, in_dim: int, o
             raise RuntimeError(f"out must have shape [{B}, {out_dim}]")
     with _Range("chebykan.family_forward"), torch.cuda.device(x.device):
         rc = _lib.load().chebykan_family_fwd(ctypes.byref(family), x.data_ptr(), packed.data_ptr(), out.data_ptr(), B,
-                                             in_dim, out_dim, degree, _stream(x))
+                                             in_dim, out_dim, degree, m, status_tensor(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "chebykan_family_fwd")
     return out
 

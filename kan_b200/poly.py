@@ -1,12 +1,14 @@
-"""Drop-in JacobiKANLayer and HermiteKANLayer on the fp32 sm_100a kernels.
+"""Drop-in JacobiKANLayer and HermiteKANLayer on the sm_100a kernels.
 
 The reference's Jacobi and Hermite layers (kan/layers/jacobikan.py:10-113, kan/layers/hermitekan.py:10-121)
 have the Chebyshev layer's structure - normalise the input, evaluate a three-term recurrence, contract with
 ``coefficients[in, out, deg+1]`` through ``einsum('bid,iod->bo')`` - so they run on the same fused kernels
 with the recurrence coefficients swapped (the library's ``chebykan_family_*`` entry points).  Constructors,
 parameter names (``jacobi_coeffs`` / ``hermite_coeffs``), RNG consumption, ``state_dict``, ``forward``'s flatten
-rule, ``get_coefficients``, ``get_analytical_form`` and ``extra_repr`` mirror the reference.  fp32 only: forward,
-dC and dx run on the FFMA pipe with a correctly rounded tanh; there is no CPU path.
+rule, ``get_coefficients``, ``get_analytical_form`` and ``extra_repr`` mirror the reference.  ``math_mode='fp32'``
+(default) runs forward, dC and dx on the FFMA pipe with a correctly rounded tanh (rel-L2 <= 1e-5 to the reference);
+``'tf32'`` / ``'bf16'`` run the forward on the tcgen05 tensor cores (rel-L2 <= 2e-3) and keep the backward in fp32.
+There is no CPU path.
 """
 from __future__ import annotations
 
@@ -107,11 +109,11 @@ def family_of(basis):
 # ---------------------------------------------------------------------------------------------------------------
 class _FamilyKANFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, coeffs, family, cache):
+    def forward(ctx, x, coeffs, family, cache, mode):
         n_in, n_out, dp1 = coeffs.shape
-        packed = cache.get(coeffs, "fp32") if cache is not None else ops.pack_coeffs(coeffs.detach(), "fp32")
+        packed = cache.get(coeffs, mode) if cache is not None else ops.pack_coeffs(coeffs.detach(), mode)
         x = _aligned(x)
-        y = ops.family_forward(family, x, packed, n_in, n_out, dp1 - 1)
+        y = ops.family_forward(family, x, packed, n_in, n_out, dp1 - 1, mode)
         ctx.save_for_backward(x, coeffs)
         ctx.family = family
         return y
@@ -126,10 +128,10 @@ class _FamilyKANFunction(torch.autograd.Function):
             dc = ops.family_bwd_dcoeff(ctx.family, x, dy, n_in, n_out, dp1 - 1)
         if ctx.needs_input_grad[0]:
             dx = ops.family_bwd_dx(ctx.family, x, dy, _aligned(coeffs.detach()))
-        return dx, dc, None, None
+        return dx, dc, None, None, None
 
 
-def family_apply(x: torch.Tensor, coeffs: torch.Tensor, family, cache=None) -> torch.Tensor:
+def family_apply(x: torch.Tensor, coeffs: torch.Tensor, family, cache=None, mode: str = "fp32") -> torch.Tensor:
     """y = sum_i sum_d coeffs[i,o,d] P_d(u(x[b,i])) with autograd, x already [B, in]."""
     if not x.is_cuda or not coeffs.is_cuda:
         raise RuntimeError("kan_b200 layers run on CUDA (sm_100a) only: move the layer and its input to the GPU; "
@@ -138,26 +140,37 @@ def family_apply(x: torch.Tensor, coeffs: torch.Tensor, family, cache=None) -> t
         raise RuntimeError(f"input is on {x.device} but the layer's coefficients are on {coeffs.device}")
     if x.dtype != torch.float32:
         raise RuntimeError(f"expected scalar type Float but found {str(x.dtype).replace('torch.', '').capitalize()}")
-    return _FamilyKANFunction.apply(x, coeffs, family, cache)
+    return _FamilyKANFunction.apply(x, coeffs, family, cache, mode)
 
 
 # ---------------------------------------------------------------------------------------------------------------
 # the layers
 # ---------------------------------------------------------------------------------------------------------------
+FAMILY_MODES = ("fp32", "tf32", "bf16")
+
+
+def _check_mode(math_mode: str) -> None:
+    if math_mode not in FAMILY_MODES:
+        raise ValueError(f"math_mode must be one of {list(FAMILY_MODES)} for this layer, got {math_mode!r}")
+
+
 def make_jacobikan_layer_class(base_cls, basis_cls, name: str = "JacobiKANLayer"):
     """JacobiKANLayer on a given (KANLayer base, JacobiBasis) pair: the stand-ins, or the reference's own classes."""
 
     class _Layer(base_cls):
-        """KAN layer on Jacobi polynomials, computed by sm_100a CUDA kernels (fp32).
-        Args as in the reference (kan/layers/jacobikan.py:20-33): input_dim, output_dim, degree, alpha, beta, init_scale."""
+        """KAN layer on Jacobi polynomials, computed by sm_100a CUDA kernels.
+        Args as in the reference (kan/layers/jacobikan.py:20-33): input_dim, output_dim, degree, alpha, beta, init_scale;
+        keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor-core forward, fp32 backward)."""
 
         def __init__(self, input_dim: int, output_dim: int, degree: int, alpha: float = 0.0, beta: float = 0.0,
-                     init_scale: float = None):
+                     init_scale: float = None, *, math_mode: str = "fp32"):
+            _check_mode(math_mode)
             if alpha <= -1 or beta <= -1:
                 raise ValueError(f"Parameters must satisfy α, β > -1, got α={alpha}, β={beta}")
             basis_function = basis_cls(degree=degree, alpha=alpha, beta=beta)
             super().__init__(input_dim=input_dim, output_dim=output_dim, basis_function=basis_function)
             self.degree = degree
+            self.math_mode = math_mode
             self.alpha = alpha
             self.beta = beta
             # identical RNG consumption to kan/layers/jacobikan.py:58-63
@@ -169,7 +182,7 @@ def make_jacobikan_layer_class(base_cls, basis_cls, name: str = "JacobiKANLayer"
 
         def forward(self, x: torch.Tensor) -> torch.Tensor:
             x = x.view(-1, self.input_dim)
-            return family_apply(x, self.jacobi_coeffs, self._family, self._packed)
+            return family_apply(x, self.jacobi_coeffs, self._family, self._packed, self.math_mode)
 
         def get_analytical_form(self) -> Dict[str, Any]:
             return {
@@ -203,17 +216,20 @@ def make_hermitekan_layer_class(base_cls, basis_cls, name: str = "HermiteKANLaye
     """HermiteKANLayer on a given (KANLayer base, HermiteBasis) pair."""
 
     class _Layer(base_cls):
-        """KAN layer on Hermite polynomials, computed by sm_100a CUDA kernels (fp32).
+        """KAN layer on Hermite polynomials, computed by sm_100a CUDA kernels.
         Args as in the reference (kan/layers/hermitekan.py:22-40): input_dim, output_dim, degree, scaling, domain,
-        normalize_domain, init_scale."""
+        normalize_domain, init_scale; keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor-core forward,
+        fp32 backward)."""
 
         def __init__(self, input_dim: int, output_dim: int, degree: int, scaling: str = 'physicist',
                      domain: Optional[Tuple[float, float]] = None, normalize_domain: bool = True,
-                     init_scale: float = None):
+                     init_scale: float = None, *, math_mode: str = "fp32"):
+            _check_mode(math_mode)
             basis_function = basis_cls(degree=degree, scaling=scaling, domain=domain,
                                        normalize_domain=normalize_domain)
             super().__init__(input_dim=input_dim, output_dim=output_dim, basis_function=basis_function)
             self.degree = degree
+            self.math_mode = math_mode
             self.scaling = scaling
             self.domain = domain
             self.normalize_domain = normalize_domain
@@ -226,7 +242,7 @@ def make_hermitekan_layer_class(base_cls, basis_cls, name: str = "HermiteKANLaye
 
         def forward(self, x: torch.Tensor) -> torch.Tensor:
             x = x.view(-1, self.input_dim)
-            return family_apply(x, self.hermite_coeffs, self._family, self._packed)
+            return family_apply(x, self.hermite_coeffs, self._family, self._packed, self.math_mode)
 
         def get_analytical_form(self) -> Dict[str, Any]:
             return {

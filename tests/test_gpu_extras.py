@@ -140,9 +140,12 @@ def test_full_size_cfg4_stack_row_sample(mode, tol):
         y_ref = ref(x[rows])
     ops.check_status()
     assert y.shape == (cfg.batch, 2048)
-    # four layers compound the per-layer rounding: allow twice the single-kernel tolerance
-    assert o.rel_l2(y[rows.cuda()].cpu(), y_ref) <= 2 * tol
-    assert o.rel_l2(y_fused[rows.cuda()].cpu(), y_ref) <= 2 * tol
+    # rounding accumulates over the four layers (each LayerNorm rescales the previous layer's error with its signal):
+    # the same bound as the reduced-size stack tests, 1.5 x the single-kernel tolerance per layer
+    err, err_fused = o.rel_l2(y[rows.cuda()].cpu(), y_ref), o.rel_l2(y_fused[rows.cuda()].cpu(), y_ref)
+    print(f"cfg4 full size, {mode}: rel-L2 {err:.3e} (plain), {err_fused:.3e} (LayerNorm fused)")
+    assert err <= 1.5 * tol * 4
+    assert err_fused <= 1.1 * err + 1e-4
 
 
 @pytest.mark.parametrize("mode", ["tf32", "bf16"])

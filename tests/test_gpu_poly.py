@@ -10,7 +10,7 @@ from kan_b200 import ops
 from oracle import chebykan_oracle as o
 from oracle import polykan_oracle as po
 from conftest import load_golden_poly
-from _util import FP32_TOL, guarded, assert_guards_intact
+from _util import FP32_TOL, TC_TOL, guarded, assert_guards_intact
 
 pytestmark = pytest.mark.gpu
 
@@ -35,7 +35,7 @@ def run_all(fam: dict, x, coeffs, dy):
     y, y_whole = guarded((x.shape[0], n_out))
     dC, dC_whole = guarded(tuple(coeffs.shape))
     dx, dx_whole = guarded(tuple(x.shape))
-    ops.family_forward(lf, xd, ops.pack_coeffs(cd, "fp32"), n_in, n_out, dp1 - 1, out=y)
+    ops.family_forward(lf, xd, ops.pack_coeffs(cd, "fp32"), n_in, n_out, dp1 - 1, "fp32", out=y)
     ops.family_bwd_dcoeff(lf, xd, dyd, n_in, n_out, dp1 - 1, out=dC)
     ops.family_bwd_dx(lf, xd, dyd, cd, out=dx)
     torch.cuda.synchronize()
@@ -93,6 +93,54 @@ def test_kernels_match_oracle(fam, shape):
         assert o.rel_l2(dx, dx_ref) <= FP32_TOL
     else:
         assert not bool(dx.any())
+
+
+# (rows, in, out, degree): CTA pairs on 2 x 256-output tiles, a single 256-wide tile, 128- and 64-wide tiles, an input
+# count that rules out the TMA path for x, ragged everything, one row
+TC_SHAPES = [(1000, 96, 520, 5), (300, 64, 256, 4), (257, 40, 100, 8), (4096, 64, 64, 12), (333, 33, 17, 5),
+             (1, 8, 600, 3), (128, 256, 1024, 0), (64, 70, 390, 1)]
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+@pytest.mark.parametrize("fam", FAMILIES, ids=lambda f: "-".join(str(v) for v in f.values()))
+@pytest.mark.parametrize("shape", TC_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_tensor_core_forward_matches_oracle(mode, fam, shape):
+    B, n_in, n_out, deg = shape
+    g = torch.Generator().manual_seed(B + n_in + deg + 1)
+    x = torch.randn(B, n_in, generator=g)
+    if fam.get("domain"):
+        x = x.clamp(-4, 4)
+    coeffs = torch.randn(n_in, n_out, deg + 1, generator=g) / (n_in * (deg + 1))
+    y, whole = guarded((B, n_out))
+    ops.family_forward(lib_family(fam), x.cuda(), ops.pack_coeffs(coeffs.cuda(), mode), n_in, n_out, deg, mode, out=y)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(y, whole)
+    # bf16 mode stores the coefficients in bf16: the oracle evaluates with the same rounded values
+    y_ref = po.forward(fam, x, coeffs.bfloat16().float() if mode == "bf16" else coeffs)
+    assert o.rel_l2(y.cpu(), y_ref) <= TC_TOL
+
+
+@pytest.mark.parametrize("mode", ["bf16", "tf32"])
+def test_tensor_core_layers_keep_an_fp32_backward(mode):
+    torch.manual_seed(4)
+    layer = kan_b200.JacobiKANLayer(48, 300, 6, alpha=0.5, beta=-0.3, math_mode=mode).cuda()
+    coeffs = layer.jacobi_coeffs.detach().cpu()
+    x = torch.randn(700, 48)
+    dy = torch.randn(700, 300)
+    xd = x.cuda().requires_grad_(True)
+    y = layer(xd)
+    y.backward(dy.cuda())
+    ops.check_status()
+    fam = {"kind": "jacobi", "alpha": 0.5, "beta": -0.3}
+    y_ref, dC_ref, dx_ref = po.forward_backward(fam, x, coeffs, dy)
+    assert o.rel_l2(y.detach().cpu(), po.forward(fam, x, coeffs.bfloat16().float() if mode == "bf16" else coeffs)) <= TC_TOL
+    assert o.rel_l2(layer.jacobi_coeffs.grad.cpu(), dC_ref) <= FP32_TOL
+    assert o.rel_l2(xd.grad.cpu(), dx_ref) <= FP32_TOL
+    with pytest.raises(ValueError, match="math_mode"):
+        kan_b200.HermiteKANLayer(3, 2, 4, math_mode="fp32x3")
+    with pytest.raises(RuntimeError, match="not supported"):
+        ops.family_forward(ops.make_family("hermite"), x.cuda(), ops.pack_coeffs(coeffs.cuda(), "fp32x3"), 48, 300, 6, "fp32x3")
 
 
 def test_chebyshev_through_the_table_equals_the_chebyshev_kernels():
