@@ -1,6 +1,7 @@
 """Data-parallel checks over NCCL on every GPU of the box (skipped on a single-GPU box): sharded inference
 reproduces the single-GPU rows bit for bit, the all-reduced coefficient gradient matches the full-batch
-gradient, and one sharded training step leaves identical coefficients on every rank."""
+gradient, one sharded training step leaves identical coefficients on every rank, and a layer sharded over its
+output columns gives the unsharded layer's y, dC and dx."""
 import os
 
 import pytest
@@ -77,6 +78,28 @@ def _worker(rank, world, port, results):
         torch.nn.functional.mse_loss(o.forward(xt, cr), tt).backward()
         expect = start - 0.5 * cr.grad
         ok = ok and o.rel_l2(mine.cpu() - start, expect - start) <= 2e-3
+        # --- the output dimension as a second sharding axis: every rank holds a block of output columns of one layer
+        # (Chebyshev fp32 and a Jacobi layer), sees all rows, and dx is summed over the ranks
+        from oracle import polykan_oracle as po
+        n_out = 8 * world + 3                           # shards differ by one column
+        go = torch.Generator().manual_seed(11)
+        xo, dyo = torch.randn(333, 40, generator=go), torch.randn(333, n_out, generator=go)
+        full = torch.randn(40, n_out, 6, generator=go) / 240
+        cases = ((lambda n: kan_b200.ChebyKANLayer(40, n, 5), lambda x, c: o.forward(x, c)),
+                 (lambda n: kan_b200.JacobiKANLayer(40, n, 5, alpha=0.5, beta=0.25),
+                  lambda x, c: po.jacobi_forward(x, c, 0.5, 0.25)))
+        for make, ref_fwd in cases:
+            tp = dp.OutputParallel(lambda n: make(n).cuda(), n_out, full_coefficients=full.cuda(), gather_output=True)
+            xg = xo.cuda().requires_grad_(True)
+            yo = tp(xg)
+            yo.backward(dyo.cuda())
+            xr, cr = xo.clone().requires_grad_(True), full.clone().requires_grad_(True)
+            y_ref = ref_fwd(xr, cr)
+            y_ref.backward(dyo)
+            ok = ok and o.rel_l2(yo.detach().cpu(), y_ref.detach()) <= 1e-5
+            ok = ok and o.rel_l2(xg.grad.cpu(), xr.grad) <= 1e-5
+            ok = ok and o.rel_l2(tp.shard.get_coefficients().grad.cpu(), cr.grad[:, tp.begin:tp.end]) <= 1e-5
+            ok = ok and torch.equal(tp.full_coefficients().cpu(), full)
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()

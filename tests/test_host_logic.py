@@ -169,6 +169,67 @@ def test_flat_grad_allreduce_gloo_world2():
         assert dict(results) == {0: True, 1: True}
 
 
+def _tp_worker(rank, world, port, results):
+    """Output-sharded layer on `world` CPU ranks (the oracle layer stands in for the CUDA layer: the sharding logic
+    does not depend on which layer class computes): y, dC and dx equal the unsharded layer's."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from _util import OracleLayer
+
+        class Layer(OracleLayer):
+            def get_coefficients(self):
+                return self.cheby_coeffs
+
+        torch.manual_seed(3)
+        full = o.init_coeffs(6, 7, 3)                      # 7 outputs over 2 ranks: shards of 4 and 3 columns
+        g = torch.Generator().manual_seed(4)
+        x = torch.randn(20, 6, generator=g)
+        dy = torch.randn(20, 7, generator=g)
+        y_ref, dC_ref, dx_ref = o.forward_backward(x, full, dy)
+        ok = True
+        for gather in (False, True):
+            tp = dp.OutputParallel(lambda n: Layer(6, n, 3), 7, full_coefficients=full, gather_output=gather)
+            xr = x.clone().requires_grad_(True)
+            y = tp(xr)
+            b, e = dp.shard_outputs(7, rank, world)
+            if gather:
+                ok = ok and y.shape == (20, 7) and torch.equal(y.detach(), y_ref)
+                y.backward(dy)
+            else:
+                ok = ok and y.shape == (20, e - b) and torch.equal(y.detach(), y_ref[:, b:e])
+                y.backward(dy[:, b:e])
+            ok = ok and o.rel_l2(tp.shard.cheby_coeffs.grad, dC_ref[:, b:e]) < 1e-6
+            ok = ok and o.rel_l2(xr.grad, dx_ref) < 1e-6         # summed over the ranks' column blocks
+            ok = ok and torch.equal(tp.full_coefficients(), full)
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_output_parallel_gloo_world2():
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        results = mgr.dict()
+        port = 31500 + os.getpid() % 2000
+        procs = [ctx.Process(target=_tp_worker, args=(r, 2, port, results)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=180)
+            assert p.exitcode == 0
+        assert dict(results) == {0: True, 1: True}
+
+
+def test_output_parallel_single_process_is_the_plain_layer():
+    assert dp.shard_outputs(7, 0, 2) == (0, 4) and dp.shard_outputs(7, 1, 2) == (4, 7)
+    tp = dp.OutputParallel(lambda n: kan_b200.ChebyKANLayer(5, n, 2), 9)
+    assert (tp.world, tp.begin, tp.end) == (1, 0, 9) and tp.shard.cheby_coeffs.shape == (5, 9, 3)
+    with pytest.raises(ValueError):
+        dp.OutputParallel(lambda n: kan_b200.ChebyKANLayer(5, max(n, 1), 2), 0)
+
+
 def test_ref_loader_search_order(tmp_path, monkeypatch):
     """$KAN_REF first, then baseline/_ref/ under the repository, then the container's read-only mount."""
     fake = tmp_path / "ref"
