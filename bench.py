@@ -404,8 +404,9 @@ def measure_host_link(ctx: Ctx, bytes_in: int, bytes_out: int, reps: int = 5):
 
 
 def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg: int, steps: int, warmup: int,
-                sample_clocks: bool = False, seed_offset: int = 0):
-    """One kernel of one layer on `B` resident rows per rank; returns (ms per step, clocks, state for e2e)."""
+                sample_clocks: bool = False, seed_offset: int = 0, family: str = ""):
+    """One kernel of one layer on `B` resident rows per rank; returns (ms per step, clocks, state for e2e).
+    `family` ('jacobi', 'hermite', 'hermite_prob'): the same kernel with that family's recurrence table."""
     import kan_b200
     from kan_b200 import ops
     torch.manual_seed(1003)
@@ -416,11 +417,15 @@ def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg
     x_host = torch.randn(B, n_in, generator=g)
     x = x_host.to(ctx.dev)
     packed = ops.pack_coeffs(layer.cheby_coeffs.detach(), mode)
+    fam = ops.make_family(family, alpha=0.5, beta=-0.3) if family else None     # (alpha, beta) matter to Jacobi only
     if op == "fwd":
         y = torch.empty(B, n_out, dtype=torch.float32, device=ctx.dev)
 
         def step():
-            ops.forward(x, packed, n_in, n_out, deg, mode, out=y)
+            if fam is not None:
+                ops.family_forward(fam, x, packed, n_in, n_out, deg, mode, out=y)
+            else:
+                ops.forward(x, packed, n_in, n_out, deg, mode, out=y)
     else:
         dy = torch.randn(B, n_out, device=ctx.dev)
         cdev = layer.cheby_coeffs.detach()
@@ -428,12 +433,18 @@ def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg
             dc = torch.empty(n_in, n_out, deg + 1, device=ctx.dev)
 
             def step():
-                ops.bwd_dcoeff(x, dy, n_in, n_out, deg, mode, out=dc)
+                if fam is not None:
+                    ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, out=dc)      # always the fp32 kernel
+                else:
+                    ops.bwd_dcoeff(x, dy, n_in, n_out, deg, mode, out=dc)
         else:
             dx = torch.empty(B, n_in, device=ctx.dev)
 
             def step():
-                ops.bwd_dx(x, dy, cdev, mode, out=dx)
+                if fam is not None:
+                    ops.family_bwd_dx(fam, x, dy, cdev, out=dx)                       # always the fp32 kernel
+                else:
+                    ops.bwd_dx(x, dy, cdev, mode, out=dx)
     flush = B * 4 * (n_in + n_out) < 2 * L2_BYTES
     ms, clocks = ctx.time_steps(step, steps, warmup, sample_clocks, flush_l2=flush)
     return ms, clocks, dict(layer=layer, x_host=x_host, step=step, flushed=flush)
@@ -648,7 +659,9 @@ def run_ours(args):
     Bg = args.batch or CFG3["global_batch"]
     if args.shape:
         Bg, n_in, n_out, deg = [int(v) for v in args.shape.split(",")]
-    single = bool(args.shape or args.batch or args.op != "fwd")      # a profiling run: one measurement only
+    single = bool(args.shape or args.batch or args.op != "fwd" or args.family)      # a profiling run: one measurement only
+    if args.family and args.mode == "fp32x3":
+        raise SystemExit("--family runs in fp32, tf32 or bf16")
     mode = args.mode
     b, e = dp.shard_rows(Bg, ctx.rank, ctx.world)
     B = e - b
@@ -658,13 +671,13 @@ def run_ours(args):
 
     # ---- headline: strong-scaled forward, inputs resident
     ms_step, clocks, state = bench_layer(ctx, mode, args.op, B, n_in, n_out, deg, args.steps, args.warmup,
-                                         sample_clocks=True, seed_offset=ctx.rank)
+                                         sample_clocks=True, seed_offset=ctx.rank, family=args.family)
     value = Bg / (ms_step * 1e-3)
     flushed = state["flushed"]
 
     # ---- end to end through the layer's public host-buffer call: H2D of x, forward, D2H of y, pipelined
     e2e = None
-    if args.op == "fwd" and not args.no_e2e:
+    if args.op == "fwd" and not args.no_e2e and not args.family:
         layer, x_host = state["layer"], state["x_host"].pin_memory()
         y_host = torch.empty(B, n_out, dtype=torch.float32).pin_memory()
         e2e_steps = max(3, min(args.steps, 10))
@@ -724,10 +737,10 @@ def run_ours(args):
         flops = 2.0 * B * n_in * (deg + 1) * n_out            # per GPU
         achieved = flops / (ms_step * 1e-3) / 1e12
         peak, peak_note = tensor_peak(mode, args.op, peaks, tf32_peak)
-        traffic = measured_traffic(f"{args.op}_{mode}_cfg3", B) if not args.shape else None
+        traffic = measured_traffic(f"{args.op}_{mode}_cfg3", B) if not (args.shape or args.family) else None
         cfg = headline_config(ctx.world)
         if single:
-            cfg = dict(cfg, workload=f"layer {args.op}, {Bg} rows x {n_in} -> {n_out}, degree {deg} (profiling run)",
+            cfg = dict(cfg, workload=f"{args.family or 'chebyshev'} layer {args.op}, {Bg} rows x {n_in} -> {n_out}, degree {deg} (profiling run)",
                        global_batch=Bg, input_dim=n_in, output_dim=n_out, degree=deg)
         line = {
             "metric": METRIC if args.op == "fwd" else f"chebykan_layer_{args.op}_samples_per_s", "value": value,
@@ -796,6 +809,8 @@ def main():
     ap.add_argument("--torch-loss", action="store_true", help="--config cfg5: torch.nn.MSELoss instead of the fused loss")
     ap.add_argument("--op", default="fwd", choices=["fwd", "dcoeff", "dx"],
                     help="time the forward (headline) or one backward kernel on the same shape")
+    ap.add_argument("--family", default="", choices=["", "jacobi", "hermite", "hermite_prob"],
+                    help="profiling runs: the layer kernel with this polynomial family's recurrence (Jacobi alpha 0.5, beta -0.3)")
     ap.add_argument("--shape", default="", help="B,in,out,deg override (profiling other layer shapes)")
     ap.add_argument("--config", default="cfg3", choices=["cfg1", "cfg2", "cfg3", "cfg4", "cfg5"],
                     help="cfg3 (default) is the headline forward; the others time that configuration's model step alone")
