@@ -358,6 +358,9 @@ def test_forward_host_pipelined(mode, tol):
     assert o.rel_l2(y, o.forward(x, c.bfloat16().float() if mode == "bf16" else c)) <= tol
     out = torch.empty(5000, 72).pin_memory()
     assert layer.forward_host(x, out=out, chunk_rows=100000) is out and same(out, y)
+    # the first and last blocks are shortened (1/8, 1/4, 1/2 of a block): a block size that 8 does not divide
+    out.fill_(float("nan"))
+    assert same(layer.forward_host(x, out=out, chunk_rows=1030), y)
     # pageable (not pinned) host memory and a block size that does not divide anything: still the same bits
     xp = x[:777].clone()
     assert not xp.is_pinned()
