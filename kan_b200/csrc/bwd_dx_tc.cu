@@ -9,9 +9,10 @@
 //   B (Wd):  packed coefficients Wd[(i,d)][out_pad] (slot = i*(deg+1)+d, outputs contiguous,
 //            rounded to tf32), K-major tile [256 slots][32 outputs], TMA, 128B swizzle.
 //   D (G):   128 x 256 fp32 in TMEM, two buffers: the epilogue of one tile overlaps the
-//            MMAs of the next.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
-//   warp 0 TMA, warp 1 MMA, warps 2-17 epilogue (four warps per TMEM lane quarter, each
-//   taking a quarter of the tile's inputs; a thread owns one batch row).
+//            MMAs of the other.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
+//   warp 0 TMA, warp 1 MMA, warps 2-17 epilogue (two groups of eight, one per accumulator; in a
+//   group two warps per TMEM lane quarter, each taking half of the tile's inputs, two inputs at a
+//   time; a thread owns one batch row).
 // With more than 128 rows the kernel runs as CTA pairs (cluster of 2, cta_group::2): the pair
 // covers 256 rows, each CTA loads the dY tile of its own 128 rows and half of the Wd tile, and
 // the even CTA issues M = 256 MMAs, so every coefficient byte is fetched once per 256 rows.
@@ -27,17 +28,24 @@ constexpr int DX_TMA_WARP = 0;
 constexpr int DX_MMA_WARP = 1;
 constexpr int DX_EPI_WARP0 = 2;
 constexpr int DX_EPI_WARPS = 16;
-constexpr int DX_EPI_PARTS = DX_EPI_WARPS / 4;      // warps per TMEM lane quarter: each takes a share of the inputs
+// The epilogue warps form one group per accumulator; group g folds the tiles that land in accumulator g, so the
+// groups work on different tiles at different points of their cycle: while one waits for its TMEM loads or its
+// MMAs another issues its FMAs.  With all sixteen warps on the same tile they moved through the phases in lock
+// step and every stall was exposed.  Inside a group, the warps of a TMEM lane quarter share the tile's inputs.
 constexpr int DX_THREADS = (2 + DX_EPI_WARPS) * 32;
-constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;
+constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;   // DX_BN: the widest tile (slots per accumulator)
 constexpr int DX_A_STAGE = DX_BM * 128;
-constexpr int DX_B_STAGE = DX_BN * 128;
+// BN slots per accumulator, 512 / BN accumulators, one epilogue group each.  256 is what runs: four accumulators
+// of 128 slots (four groups of four warps) measured slower on the narrow layers they were meant for (0.94 against
+// 0.81 ms at 1048576 x 64 -> 64, degree 32: 22 tiles per row block instead of 10, each with its own set-up, and a
+// wasted half round per tile of three inputs) and re-read dY twice as often on wide ones.
 // a CTA of a pair stages half of every Wd tile (a ring deeper than 4 stages measured no faster)
-template <int CG>
+template <int CG, int BN>
 struct DxSmem {
     static constexpr int NS = 4;
-    static constexpr int NUM_BARS = 2 * NS + 5;     // full, empty, acc_full[2], acc_empty[2], drain
-    static constexpr int B_STAGE = DX_B_STAGE / CG;
+    static constexpr int NACC = 512 / BN;
+    static constexpr int NUM_BARS = 2 * NS + 2 * NACC + 1;     // full, empty, acc_full[NACC], acc_empty[NACC], drain
+    static constexpr int B_STAGE = BN * 128 / CG;
     static constexpr int STAGE = DX_A_STAGE + B_STAGE;
     static constexpr int BAR_OFFSET = NS * STAGE;
     static constexpr int TOTAL = BAR_OFFSET + NUM_BARS * 8 + 16 + 1024;
@@ -107,15 +115,31 @@ dy_tail_kernel(const float* __restrict__ dy, float* __restrict__ lo, int64_t n) 
     }
 }
 
-template <int CG>
+// Running state of one input's fold: sum += U_{d-1}(t) G_d column by column, U advanced by its recurrence.
+struct DxFold {
+    float ua = 0.f, ub = -1.f, sum = 0.f, t2;
+    __device__ __forceinline__ explicit DxFold(float two_t) : t2(two_t) {}
+    // two columns: sum += U_{d-1} G_d, advance U, twice (ua / ub swap roles)
+    __device__ __forceinline__ void two(uint32_t g0, uint32_t g1) {
+        sum = fmaf(ua, __uint_as_float(g0), sum);
+        ub = fmaf(t2, ua, -ub);
+        sum = fmaf(ub, __uint_as_float(g1), sum);
+        ua = fmaf(t2, ub, -ua);
+    }
+    __device__ __forceinline__ void one(uint32_t g) { sum = fmaf(ua, __uint_as_float(g), sum); }
+};
+
+template <int CG, int BN>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
              const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
              int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh) {
-    using L = DxSmem<CG>;
-    constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS;
+    using L = DxSmem<CG, BN>;
+    constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS, NACC = L::NACC;
+    constexpr int GROUP_WARPS = DX_EPI_WARPS / NACC;     // epilogue warps per accumulator
+    constexpr int PARTS = GROUP_WARPS / 4;               // warps per TMEM lane quarter within a group
     constexpr int DX_STAGE = L::STAGE, DX_BAR_OFFSET = L::BAR_OFFSET;
-    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(DX_BN >> 3) << 17) |
+    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                ((uint32_t)((DX_BM * CG) >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -124,8 +148,8 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (NS + s); };
     auto acc_full_bar = [&](int a) { return bars + 8u * (2 * NS + a); };
-    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NS + 2 + a); };
-    const uint32_t drain_bar = bars + 8u * (2 * NS + 4);
+    auto acc_empty_bar = [&](int a) { return bars + 8u * (2 * NS + NACC + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * NS + 2 * NACC);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem_gen + DX_BAR_OFFSET + DX_NUM_BARS * 8);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DX_BAR_OFFSET + DX_NUM_BARS * 8 + 4);
 
@@ -135,10 +159,14 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
     const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
     const int64_t unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
     const int64_t nunits = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
+    // tile = row block * i_tiles + input tile.  The roles walk their tiles with (row block, input tile) counters:
+    // a 64-bit division per tile and warp costs about as many instructions as folding one input.
+    const int64_t rb_first = unit / i_tiles, rb_step = nunits / i_tiles;
+    const int it_first = (int)(unit % i_tiles), it_step = (int)(nunits % i_tiles);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), DX_EPI_WARPS * CG); }
+        for (int a = 0; a < NACC; ++a) { mbar_init(acc_full_bar(a), 1); mbar_init(acc_empty_bar(a), GROUP_WARPS * CG); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -164,9 +192,12 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
         if (lane == 0) {
             int s = 0; uint32_t ph = 0;
             bool alive = true;
+            int64_t rb = rb_first; int it = it_first;
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
-                const int m0 = (int)((tile / i_tiles) * (DX_BM * CG) + rank * DX_BM);
-                const int slot0 = (int)(tile % i_tiles) * TI * dp1;
+                const int m0 = (int)(rb * (DX_BM * CG) + rank * DX_BM);
+                const int slot0 = it * TI * dp1;
+                rb += rb_step; it += it_step;
+                if (it >= i_tiles) { it -= i_tiles; ++rb; }
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, status, XST_TMA)) { alive = false; break; }
                     const uint32_t st = smem_base + s * DX_STAGE;
@@ -175,7 +206,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                         if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * DX_STAGE);
                         const uint32_t bar0 = mapa_cluster(full_bar(s), 0);
                         tma_load_2d_pair(st, &tmap_dy, kb * DX_KB, m0, bar0);
-                        tma_load_2d_pair(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0 + (int)rank * (DX_BN / 2), bar0);
+                        tma_load_2d_pair(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0 + (int)rank * (BN / 2), bar0);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), DX_STAGE);
                         tma_load_2d(st, &tmap_dy, kb * DX_KB, m0, full_bar(s));
@@ -202,7 +233,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 if (!__all_sync(0xffffffffu, mbar_wait(acc_empty_bar(acc), acc_ph ^ 1u, abort_flag, status, XST_MMA_ACC))) { alive = false; break; }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * DX_BN);
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < nkb; ++kb) {
                     if (!__all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, abort_flag, status, XST_MMA_FULL))) { alive = false; break; }
                     tc_fence_after();
@@ -228,7 +259,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 }
                 if (alive && elected) { if (CG == 2) umma2_commit_both(acc_full_bar(acc)); else umma_commit(acc_full_bar(acc)); }
                 __syncwarp();
-                if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+                if (++acc == NACC) { acc = 0; acc_ph ^= 1u; }
             }
             if (!alive && elected) {
                 if (CG == 2) umma2_commit(drain_bar); else umma_commit(drain_bar);
@@ -240,74 +271,99 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
     } else {
         // ------------------------------ epilogue ------------------------------
         const int q = warp & 3;                          // TMEM lane quarter
-        const int part = (warp - DX_EPI_WARP0) >> 2;     // which share of the tile's inputs
-        int acc = 0; uint32_t acc_ph = 0;
+        const int group = (warp - DX_EPI_WARP0) / GROUP_WARPS;          // which accumulator's tiles
+        const int part = ((warp - DX_EPI_WARP0) % GROUP_WARPS) >> 2;     // which share of a tile's inputs
+        const int acc = group; uint32_t acc_ph = 0;
         bool alive = true;
-        for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
-            const int64_t row = (tile / i_tiles) * (DX_BM * CG) + rank * DX_BM + q * 32 + lane;
-            const int i0 = (int)(tile % i_tiles) * TI;
+        // this group's tiles: unit + group * nunits, then every NACC * nunits
+        const int64_t first = unit + group * nunits;
+        int64_t rb = first / i_tiles; int it = (int)(first % i_tiles);
+        const int64_t rb_step2 = (NACC * nunits) / i_tiles; const int it_step2 = (int)((NACC * nunits) % i_tiles);
+        for (int64_t tile = first; tile < num_tiles && alive; tile += NACC * nunits) {
+            const int64_t row = rb * (DX_BM * CG) + rank * DX_BM + q * 32 + lane;
+            const int i0 = it * TI;
+            rb += rb_step2; it += it_step2;
+            if (it >= i_tiles) { it -= i_tiles; ++rb; }
             const int ti = min(TI, in - i0);
-            const int per = (ti + DX_EPI_PARTS - 1) / DX_EPI_PARTS;
+            const int per = (ti + PARTS - 1) / PARTS;
             const int ii_begin = min(ti, part * per), ii_end = min(ti, ii_begin + per);
             const bool row_ok = row < B;
             const float* xrow = x + (row_ok ? row : 0) * in + i0;
             float* dxrow = dx + (row_ok ? row : 0) * in + i0;
-            // first x value in flight before the accumulator is awaited
-            float xnext = (row_ok && ii_begin < ii_end) ? __ldg(xrow + ii_begin) : 0.f;
+            // The warp folds its inputs two at a time (A and B): both inputs' TMEM loads are in flight together and
+            // their recurrences are four independent FMA chains instead of two.  One input at a time, a warp spent
+            // most of a tile waiting (a TMEM load, then 64 dependent FMAs, then the next load), and sixteen such
+            // warps, not the MMAs, set the kernel's time.
+            // x of the first pair in flight before the accumulator is awaited
+            float xa = (row_ok && ii_begin < ii_end) ? __ldg(xrow + ii_begin) : 0.f;
+            float xb = (row_ok && ii_begin + 1 < ii_end) ? __ldg(xrow + ii_begin + 1) : 0.f;
             const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, XST_EPILOGUE);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * DX_BN);
-            for (int ii = ii_begin; ii < ii_end; ++ii) {
-                const float t = exact_tanh ? tanhf(xnext) : tanh_fast(xnext);
-                if (row_ok && ii + 1 < ii_end) xnext = __ldg(xrow + ii + 1);
-                const float t2 = 2.f * t;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            for (int ii = ii_begin; ii < ii_end; ii += 2) {
+                const bool has_b = ii + 1 < ii_end;          // warp-uniform; without B the second lane of work repeats A
+                const float ta = exact_tanh ? tanhf(xa) : tanh_fast(xa);
+                const float tb = exact_tanh ? tanhf(xb) : tanh_fast(xb);
+                if (row_ok && ii + 2 < ii_end) xa = __ldg(xrow + ii + 2);
+                if (row_ok && ii + 3 < ii_end) xb = __ldg(xrow + ii + 3);
                 // ua / ub alternate as (U_{d-1}, U_{d-2}); U_{-1} = 0, U_{-2} = -1 make U_0 = 1 and
                 // give the d = 0 column (whose coefficients are 0 * C) weight zero without a branch
-                float ua = 0.f, ub = -1.f, sum = 0.f;
-                const uint32_t col0 = taddr + (uint32_t)(ii * dp1);
-                // two columns: sum += U_{d-1} G_d, advance U, twice (ua / ub swap roles)
-                auto fold2 = [&](uint32_t g0, uint32_t g1) {
-                    sum = fmaf(ua, __uint_as_float(g0), sum);
-                    ub = fmaf(t2, ua, -ub);
-                    sum = fmaf(ub, __uint_as_float(g1), sum);
-                    ua = fmaf(t2, ub, -ua);
-                };
+                DxFold fa(2.f * ta), fb(2.f * tb);
+                const uint32_t col_a = taddr + (uint32_t)(ii * dp1);
+                const uint32_t col_b = has_b ? col_a + (uint32_t)dp1 : col_a;
                 int c = 0;
                 for (; c + 32 <= dp1; c += 32) {
-                    uint32_t r[32];
-                    tmem_ld32(col0 + c, r);
+                    uint32_t ra[32], rb[32];
+                    tmem_ld32(col_a + c, ra);
+                    tmem_ld32(col_b + c, rb);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int e = 0; e < 32; e += 2) fold2(r[e], r[e + 1]);
+                    for (int e = 0; e < 32; e += 2) { fa.two(ra[e], ra[e + 1]); fb.two(rb[e], rb[e + 1]); }
                 }
-                // the last 1-31 columns: one load of 16, 8, 4, 2 and 1 columns each as the count's bits say
-                // (all issued before a single wait), so no lane touches a column of the next input
+                // the last 1-31 columns: loads of 16, 8, 4, 2 and 1 columns as the count's bits say, so that no lane
+                // touches a column past its input's last one; each size is loaded, awaited and folded in turn (few
+                // registers live at once; configurations whose time the epilogue sets have one or two bits set)
                 const int rem = dp1 - c;
-                if (rem > 0) {
-                    uint32_t r16[16], r8[8], r4[4], r2[2], r1 = 0u;
-                    int cc = c;
-                    if (rem & 16) { tmem_ld16(col0 + cc, r16); cc += 16; }
-                    if (rem & 8) { tmem_ld8(col0 + cc, r8); cc += 8; }
-                    if (rem & 4) { tmem_ld4(col0 + cc, r4); cc += 4; }
-                    if (rem & 2) { tmem_ld2(col0 + cc, r2); cc += 2; }
-                    if (rem & 1) tmem_ld1(col0 + cc, r1);
-                    tmem_ld_wait();
-                    if (rem & 16) {
+                int cc = c;
+                if (rem & 16) {
+                    uint32_t a[16], b[16];
+                    tmem_ld16(col_a + cc, a); tmem_ld16(col_b + cc, b); tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 16; e += 2) fold2(r16[e], r16[e + 1]);
-                    }
-                    if (rem & 8) {
+                    for (int e = 0; e < 16; e += 2) { fa.two(a[e], a[e + 1]); fb.two(b[e], b[e + 1]); }
+                    cc += 16;
+                }
+                if (rem & 8) {
+                    uint32_t a[8], b[8];
+                    tmem_ld8(col_a + cc, a); tmem_ld8(col_b + cc, b); tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 8; e += 2) fold2(r8[e], r8[e + 1]);
-                    }
-                    if (rem & 4) { fold2(r4[0], r4[1]); fold2(r4[2], r4[3]); }
-                    if (rem & 2) fold2(r2[0], r2[1]);
-                    if (rem & 1) sum = fmaf(ua, __uint_as_float(r1), sum);
+                    for (int e = 0; e < 8; e += 2) { fa.two(a[e], a[e + 1]); fb.two(b[e], b[e + 1]); }
+                    cc += 8;
+                }
+                if (rem & 4) {
+                    uint32_t a[4], b[4];
+                    tmem_ld4(col_a + cc, a); tmem_ld4(col_b + cc, b); tmem_ld_wait();
+                    fa.two(a[0], a[1]); fb.two(b[0], b[1]); fa.two(a[2], a[3]); fb.two(b[2], b[3]);
+                    cc += 4;
+                }
+                if (rem & 2) {
+                    uint32_t a[2], b[2];
+                    tmem_ld2(col_a + cc, a); tmem_ld2(col_b + cc, b); tmem_ld_wait();
+                    fa.two(a[0], a[1]); fb.two(b[0], b[1]);
+                    cc += 2;
+                }
+                if (rem & 1) {
+                    uint32_t a = 0u, b = 0u;
+                    tmem_ld1(col_a + cc, a); tmem_ld1(col_b + cc, b); tmem_ld_wait();
+                    fa.one(a); fb.one(b);
                 }
                 if (row_ok) {
-                    const float v = fmaf(-t, t, 1.f) * sum;
-                    dxrow[ii] = accumulate ? dxrow[ii] + v : v;
+                    const float va = fmaf(-ta, ta, 1.f) * fa.sum;
+                    dxrow[ii] = accumulate ? dxrow[ii] + va : va;
+                    if (has_b) {
+                        const float vb = fmaf(-tb, tb, 1.f) * fb.sum;
+                        dxrow[ii + 1] = accumulate ? dxrow[ii + 1] + vb : vb;
+                    }
                 }
             }
             tc_fence_before();
@@ -316,7 +372,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 if (CG == 2 && rank != 0) mbar_arrive_cluster(mapa_cluster(acc_empty_bar(acc), 0));
                 else mbar_arrive(acc_empty_bar(acc));
             }
-            if (++acc == 2) { acc = 0; acc_ph ^= 1u; }
+            acc_ph ^= 1u;
         }
     }
 
@@ -356,14 +412,14 @@ int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, i
 }
 
 namespace {
-template <int CG>
+template <int CG, int BN>
 int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
                      int in, int out, int dp1, int32_t* status, cudaStream_t s, int accumulate = 0, int exact_tanh = 0) {
-    using L = DxSmem<CG>;
+    using L = DxSmem<CG, BN>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dx_tc_kernel<CG>;
+    auto kernel = dx_tc_kernel<CG, BN>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -371,7 +427,7 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int TI = DX_BN / dp1;
+    int TI = BN / dp1;
     if (TI > in) TI = in;
     const int i_tiles = (int)ceil_div(in, TI);
     const int64_t num_tiles = ceil_div(B, DX_BM * CG) * i_tiles;
@@ -415,6 +471,7 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
         }
     }
     const int cg = B > DX_BM ? 2 : 1;
+    const int bn = DX_BN;
     const cuuint32_t estr[2] = {1, 1};
     auto map_dy = [&](CUtensorMap* m, const float* p) -> int {
         const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
@@ -429,7 +486,7 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     auto map_w = [&](CUtensorMap* m, void* p) -> int {
         const cuuint64_t dims[2] = {(cuuint64_t)out_pad, (cuuint64_t)slots};
         const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 4)};
-        const cuuint32_t box[2] = {DX_KB, (cuuint32_t)(DX_BN / cg)};
+        const cuuint32_t box[2] = {DX_KB, (cuuint32_t)(bn / cg)};
         const CUresult r = encode(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, p, dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -437,8 +494,8 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
         return CHEBYKAN_OK;
     };
     auto run = [&](const CUtensorMap& mdy, const CUtensorMap& mw, int accumulate) -> int {
-        if (cg == 2) return launch_dx_kernel<2>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
-        return launch_dx_kernel<1>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
+        if (cg == 2) return launch_dx_kernel<2, DX_BN>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
+        return launch_dx_kernel<1, DX_BN>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
     };
     CUtensorMap m_dy, m_w;
     int rc;
