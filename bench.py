@@ -620,8 +620,9 @@ def sub_train_cfg5(ctx: Ctx, mode: str, steps: int, warmup: int, peaks, tf32_pea
     return rec
 
 
-def sub_small_train(ctx: Ctx, name: str, graph: bool, steps: int, warmup: int):
-    """Launch-bound configurations 1 and 2 (single GPU): ms per training step, eager or replayed as one CUDA graph."""
+def sub_small_train(ctx: Ctx, name: str, graph: bool, steps: int, warmup: int, fused: bool = False):
+    """Launch-bound configurations 1 and 2 (single GPU): ms per training step, eager, replayed as one CUDA graph, or
+    (configuration 1: one layer, MSE) as the single-launch fused step."""
     import kan_b200
     from kan_b200 import dp, workloads
     cfg = workloads.CONFIGS[name]
@@ -629,7 +630,12 @@ def sub_small_train(ctx: Ctx, name: str, graph: bool, steps: int, warmup: int):
     x, tgt = workloads.make_inputs(cfg)
     x, tgt = x.to(ctx.dev), tgt.to(ctx.dev)
     loss_fn = workloads.loss_fn(cfg)
-    if graph:
+    if fused:
+        fused_step = kan_b200.small.FusedTrainStep(model[0], cfg.optimizer, lr=cfg.lr)
+
+        def step():
+            fused_step(x, tgt)
+    elif graph:
         opt = (kan_b200.optim.Adam(list(model.parameters()), lr=cfg.lr, capturable=True) if cfg.optimizer == "adam"
                else kan_b200.optim.SGD(list(model.parameters()), lr=cfg.lr))
         graphed = kan_b200.graph.GraphedTrainStep(model, loss_fn, opt, x, tgt)
@@ -646,7 +652,7 @@ def sub_small_train(ctx: Ctx, name: str, graph: bool, steps: int, warmup: int):
     ms, _ = ctx.time_steps(step, steps, warmup)
     rec = {"workload": f"{name}: layers {list(cfg.layers)}, batch {cfg.batch}, fwd+bwd+{cfg.optimizer}, fp32",
            "value": cfg.batch / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "cuda_graph": graph,
-           "roofline": {"bound": "launch latency"}}
+           "single_launch_step": fused, "roofline": {"bound": "launch latency"}}
     free_gpu()
     return rec
 
@@ -732,6 +738,7 @@ def run_ours(args):
             for name in ("cfg1", "cfg2"):
                 sub[name + "_train_eager"] = sub_small_train(ctx, name, False, 50, 5)
                 sub[name + "_train_graph"] = sub_small_train(ctx, name, True, 200, 5)
+            sub["cfg1_train_fused_step"] = sub_small_train(ctx, "cfg1", False, 200, 5, fused=True)
 
     if ctx.rank == 0:
         flops = 2.0 * B * n_in * (deg + 1) * n_out            # per GPU

@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 5
+#define CHEBYKAN_ABI_VERSION 6
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -298,6 +298,25 @@ int chebykan_adam_step_graph(float* param, const float* grad, float* exp_avg,
                              float* exp_avg_sq, int64_t n, float lr, float beta1,
                              float beta2, float eps, int64_t* step_dev,
                              float grad_scale, void* stream);
+
+/*
+ * One-launch training step of a single SMALL layer: forward, mean-squared-error loss, backward and the
+ * optimizer update as one kernel of one CTA.  Replaces one iteration of the reference's example loop
+ * (README.md:57-69: optimizer.zero_grad(); loss = MSELoss()(layer(x), target); loss.backward();
+ * optimizer.step()), whose dozen microsecond-scale kernels are bound by launch overhead when each stage
+ * is its own launch.  coeffs [in][out][deg+1] is updated in place; optimizer 0 = SGD (lr), 1 = Adam
+ * (lr, beta1, beta2, eps; exp_avg / exp_avg_sq like coeffs, *step_dev = steps taken so far, advanced
+ * by the kernel: bias corrections as torch.optim.Adam computes them).  *loss = mean((y - target)^2) of
+ * the step's forward (before the update); dcoeffs_out (may be NULL) receives the gradient that was
+ * applied.  fp32, tanh correctly rounded; gradient sums run over the rows in order, so a step is
+ * bitwise repeatable.  chebykan_small_train_step_supported: at most 2048 coefficients, 16 outputs and
+ * B * (in + out) <= 49152; other shapes return CHEBYKAN_EUNSUPPORTED.
+ */
+int chebykan_small_train_step_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
+int chebykan_small_train_step(const float* x, const float* target, float* coeffs, float* exp_avg,
+                              float* exp_avg_sq, int64_t* step_dev, float* loss, float* dcoeffs_out,
+                              int64_t B, int64_t in, int64_t out, int64_t deg, int optimizer, float lr,
+                              float beta1, float beta2, float eps, void* stream);
 
 /*
  * Self-test of the bounded device-side wait the tensor-core kernels use: one

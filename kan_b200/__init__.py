@@ -11,9 +11,9 @@ from .layer import ChebyKANLayer, ChebyshevBasis, KANLayer, chebykan_apply, inst
 from .poly import HermiteBasis, HermiteKANLayer, JacobiBasis, JacobiKANLayer
 from .stack import FusedChebyKANStack, fuse_layernorm
 from .loss import MSELoss, mse_loss
-from . import ops, optim, dp, workloads, graph, poly
+from . import ops, optim, dp, workloads, graph, poly, small
 
 __all__ = ["MSELoss", "mse_loss", "FusedChebyKANStack", "fuse_layernorm", "ChebyKANLayer", "ChebyshevBasis", "KANLayer",
            "JacobiKANLayer", "HermiteKANLayer", "JacobiBasis", "HermiteBasis", "chebykan_apply", "install_into_reference",
-           "ops", "optim", "dp", "workloads", "graph", "poly"]
+           "ops", "optim", "dp", "workloads", "graph", "poly", "small"]
 __version__ = "0.1.0"

@@ -66,6 +66,10 @@ SIGNATURES = {
                                    c_float, c_float, c_int64, c_float, c_void_p]),
     "chebykan_adam_step_graph": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_float,
                                          c_float, c_float, c_void_p, c_float, c_void_p]),
+    "chebykan_small_train_step_supported": (c_int, [c_int64, c_int64, c_int64, c_int64]),
+    "chebykan_small_train_step": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_int64, c_int64, c_int64, c_int64, c_int, c_float, c_float, c_float, c_float,
+                                          c_void_p]),
     "chebykan_selftest_bounded_wait": (c_int, [c_void_p, c_int64, c_int, c_void_p]),
     "chebykan_fwd_host_scratch_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int64, c_int]),
     "chebykan_fwd_host": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
@@ -92,7 +96,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 5:
+    if lib.chebykan_abi_version() != 6:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -350,6 +350,75 @@ def test_graphed_training_step_config1(golden):
                                         kan_b200.optim.Adam(layer.parameters(), lr=0.01), x, tgt)
 
 
+def test_fused_single_launch_step_config1(golden):
+    """The README loop with the whole step (forward, MSE, backward, Adam) as one kernel launch: the reference's loss
+    curve and final coefficients; one step equals the staged kernels' step; bitwise repeatable."""
+    layer = kan_b200.ChebyKANLayer(1, 1, 8)
+    with torch.no_grad():
+        layer.cheby_coeffs.copy_(torch.from_numpy(golden["cfg1_train"]["init_coeffs"]))
+    layer = layer.cuda()
+    x, tgt = workloads.make_inputs(workloads.CONFIGS["cfg1"])
+    x, tgt = x.cuda(), tgt.cuda()
+    step = kan_b200.small.FusedTrainStep(layer, "adam", lr=0.01)
+    got = []
+    for i in range(1000):
+        loss = step(x, tgt)
+        if i in (0, 99, 499, 999):
+            got.append(float(loss))
+    assert np.allclose(got, golden["cfg1_train"]["losses"], rtol=2e-3)
+    assert o.rel_l2(layer.cheby_coeffs.detach().cpu(), golden["cfg1_train"]["final_coeffs"]) <= 2e-3
+    assert int(step.step_count.item()) == 1000
+    # an eager forward after the fused steps sees the updated coefficients (the packed copy is refreshed)
+    assert o.rel_l2(layer(x).detach().cpu(), o.forward(x.cpu(), layer.cheby_coeffs.detach().cpu())) <= FP32_TOL
+
+
+@pytest.mark.parametrize("opt_name", ["adam", "sgd"])
+@pytest.mark.parametrize("shape", [(100, 1, 1, 8), (333, 5, 3, 4), (1, 2, 16, 0), (2000, 8, 16, 3), (64, 16, 4, 31)])
+def test_fused_single_launch_step_matches_oracle(opt_name, shape):
+    B, n_in, n_out, deg = shape
+    g = torch.Generator().manual_seed(B + deg)
+    x = torch.randn(B, n_in, generator=g)
+    tgt = torch.randn(B, n_out, generator=g)
+    torch.manual_seed(B)
+    layer = kan_b200.ChebyKANLayer(n_in, n_out, deg).cuda()
+    c0 = layer.cheby_coeffs.detach().cpu().clone()
+    step = kan_b200.small.FusedTrainStep(layer, opt_name, lr=0.05, keep_grad=True)
+    ref_p = c0.clone().requires_grad_(True)
+    ref_opt = (torch.optim.Adam([ref_p], lr=0.05) if opt_name == "adam" else torch.optim.SGD([ref_p], lr=0.05))
+    for _ in range(3):
+        loss = step(x.cuda(), tgt.cuda())
+        ref_opt.zero_grad()
+        ref_loss = torch.nn.functional.mse_loss(o.forward(x, ref_p), tgt)
+        ref_loss.backward()
+        assert abs(float(loss) - float(ref_loss)) <= 2e-5 * abs(float(ref_loss))
+        assert o.rel_l2(layer.cheby_coeffs.grad.cpu(), ref_p.grad) <= FP32_TOL
+        ref_opt.step()
+    # Adam divides by sqrt(v) + eps: where a gradient is almost zero the update direction is ill-conditioned
+    assert o.rel_l2(layer.cheby_coeffs.detach().cpu() - c0, ref_p.detach() - c0) <= (1e-3 if opt_name == "adam" else 1e-5)
+    # bitwise repeatable: the same three steps from the same start give the same bits
+    layer2 = kan_b200.ChebyKANLayer(n_in, n_out, deg).cuda()
+    with torch.no_grad():
+        layer2.cheby_coeffs.copy_(c0.cuda())
+    step2 = kan_b200.small.FusedTrainStep(layer2, opt_name, lr=0.05)
+    for _ in range(3):
+        step2(x.cuda(), tgt.cuda())
+    assert torch.equal(layer2.cheby_coeffs.detach(), layer.cheby_coeffs.detach())
+
+
+def test_fused_single_launch_step_limits():
+    assert kan_b200.small.supported(100, 1, 1, 8) and kan_b200.small.supported(3072, 8, 8, 3)
+    assert not kan_b200.small.supported(100, 64, 64, 8)          # 36864 coefficients
+    assert not kan_b200.small.supported(100, 4, 17, 2)           # more than 16 outputs
+    assert not kan_b200.small.supported(50000, 1, 1, 8)          # rows do not fit shared memory
+    layer = kan_b200.ChebyKANLayer(64, 64, 8).cuda()
+    with pytest.raises(RuntimeError, match="does not cover"):
+        kan_b200.small.FusedTrainStep(layer)(torch.randn(10, 64).cuda(), torch.randn(10, 64).cuda())
+    with pytest.raises(RuntimeError, match="CUDA"):
+        kan_b200.small.FusedTrainStep(kan_b200.ChebyKANLayer(1, 1, 2))
+    with pytest.raises(ValueError):
+        kan_b200.small.FusedTrainStep(layer, optimizer="lbfgs")
+
+
 def test_graphed_step_equals_eager_config2():
     cfg = workloads.CONFIGS["cfg2"]
     x, labels = workloads.make_inputs(cfg)
