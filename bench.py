@@ -434,7 +434,7 @@ def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg
 
             def step():
                 if fam is not None:
-                    ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, out=dc)      # always the fp32 kernel
+                    ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, mode, out=dc)
                 else:
                     ops.bwd_dcoeff(x, dy, n_in, n_out, deg, mode, out=dc)
         else:
@@ -442,7 +442,7 @@ def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg
 
             def step():
                 if fam is not None:
-                    ops.family_bwd_dx(fam, x, dy, cdev, out=dx)                       # always the fp32 kernel
+                    ops.family_bwd_dx(fam, x, dy, cdev, mode, out=dx)
                 else:
                     ops.bwd_dx(x, dy, cdev, mode, out=dx)
     flush = B * 4 * (n_in + n_out) < 2 * L2_BYTES
@@ -465,8 +465,9 @@ def layer_record(ctx, mode, op, B_rank, B_total, shape, ms, peaks, tf32_peak, ex
 
 
 def sub_family(ctx: Ctx, kind: str, B: int, n_in: int, n_out: int, deg: int, peaks, **family_kw):
-    """Forward (fp32 FFMA kernel and bf16 tensor-core kernel), dC and dx (fp32) of a Jacobi / Hermite layer, all with a
-    table-driven recurrence, on B resident rows of this rank; ms per launch and the rate of each against its pipe."""
+    """Forward (fp32 FFMA kernel and bf16 tensor-core kernel), dC and dx (fp32 FFMA kernels and tf32 tensor-core kernels)
+    of a Jacobi / Hermite layer, all with a table-driven recurrence, on B resident rows of this rank; ms per launch and
+    the rate of each against its pipe."""
     from kan_b200 import ops
     fam = ops.make_family(kind, **family_kw)
     g = torch.Generator().manual_seed(77 + ctx.rank)
@@ -478,15 +479,18 @@ def sub_family(ctx: Ctx, kind: str, B: int, n_in: int, n_out: int, deg: int, pea
     packed_bf16 = ops.pack_coeffs(coeffs, "bf16")
     steps = {"fwd": lambda: ops.family_forward(fam, x, packed, n_in, n_out, deg, "fp32", out=y),
              "fwd_bf16": lambda: ops.family_forward(fam, x, packed_bf16, n_in, n_out, deg, "bf16", out=y),
-             "dcoeff": lambda: ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, out=dc),
-             "dx": lambda: ops.family_bwd_dx(fam, x, dy, coeffs, out=dx)}
+             "dcoeff": lambda: ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, "fp32", out=dc),
+             "dx": lambda: ops.family_bwd_dx(fam, x, dy, coeffs, "fp32", out=dx),
+             "dcoeff_tf32": lambda: ops.family_bwd_dcoeff(fam, x, dy, n_in, n_out, deg, "tf32", out=dc),
+             "dx_tf32": lambda: ops.family_bwd_dx(fam, x, dy, coeffs, "tf32", out=dx)}
     flops = 2.0 * B * n_in * (deg + 1) * n_out
     rec = {"family": dict(family_kw, kind=kind), "rows_per_gpu": B, "shape": [n_in, n_out, deg], "dtype": "fp32"}
     for op, fn in steps.items():
         ms, _ = ctx.time_steps(fn, 3, 3, False, flush_l2=B * 4 * (n_in + n_out) < 2 * L2_BYTES)
-        peak, note = tensor_peak("bf16" if op == "fwd_bf16" else "fp32", "fwd", peaks, None)
+        tc_mode = {"fwd_bf16": "bf16", "dcoeff_tf32": "tf32", "dx_tf32": "tf32"}.get(op)
+        peak, note = tensor_peak(tc_mode or "fp32", "fwd", peaks, None)
         rec[op] = {"ms_per_step": ms, "value": B * ctx.world / (ms * 1e-3), "unit": UNIT,
-                   "roofline": {"bound": "tensor" if op == "fwd_bf16" else "ffma", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                   "roofline": {"bound": "tensor" if tc_mode else "ffma", "achieved": flops / (ms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                                 "frac": flops / (ms * 1e-3) / 1e12 / peak, "peak_note": note}}
     ops.check_status()
     del x, dy, coeffs, packed, packed_bf16, y, dc, dx

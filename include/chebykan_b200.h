@@ -27,7 +27,7 @@
 extern "C" {
 #endif
 
-#define CHEBYKAN_ABI_VERSION 6
+#define CHEBYKAN_ABI_VERSION 7
 
 /* error codes */
 #define CHEBYKAN_OK            0
@@ -212,17 +212,18 @@ int chebykan_basis_functions(const float* t, float* phi, int64_t n, int64_t deg,
  *                                them against the Chebyshev entry points above).
  * A family is described on the HOST by a chebykan_family; the library turns it into the recurrence
  * table the kernels take as a launch parameter, so there is nothing to upload or keep alive.
- * `packed` is chebykan_pack_coeffs' layout for `mode` (the packing does not depend on the family) and
- * the workspace of chebykan_family_bwd_dcoeff is chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DCOEFF, ...,
- * CHEBYKAN_MODE_FP32).  chebykan_family_fwd runs in CHEBYKAN_MODE_FP32 (FFMA pipe, correctly rounded
- * tanh; status may be NULL), CHEBYKAN_MODE_TF32 or CHEBYKAN_MODE_BF16 (the tcgen05 kernel of
- * chebykan_fwd with the family's recurrence in its producer warps; status as for chebykan_fwd);
- * CHEBYKAN_MODE_FP32X3 returns CHEBYKAN_EUNSUPPORTED.  The two bwd functions always compute in fp32 on
- * the FFMA pipe; the reference has no hand-written backward, they return what autograd derives from
- * the forward.  chebykan_family_normalize / chebykan_family_basis are the basis object's
+ * `packed` is chebykan_pack_coeffs' layout for `mode` (the packing does not depend on the family);
+ * the workspaces of the two bwd functions are sized by chebykan_family_workspace_bytes(op, ..., mode).
+ * Modes: CHEBYKAN_MODE_FP32 (FFMA pipe, correctly rounded tanh; status may be NULL), CHEBYKAN_MODE_TF32
+ * and CHEBYKAN_MODE_BF16 (the tcgen05 kernels of chebykan_fwd / chebykan_bwd_dcoeff / chebykan_bwd_dx
+ * with the family's recurrence - and, for dx, its derivative - in their producer and epilogue warps;
+ * the backward contracts in tf32 in both modes; status as for the Chebyshev functions);
+ * CHEBYKAN_MODE_FP32X3 returns CHEBYKAN_EUNSUPPORTED.  The reference has no hand-written backward: the
+ * two bwd functions return what autograd derives from the forward.  chebykan_family_normalize / chebykan_family_basis are the basis object's
  * normalize_input / basis_functions on flat arrays of n elements (phi has n*(deg+1) elements), and
  * chebykan_family_table copies the recurrence P_d = (a[d] u + b[d]) P_{d-1} - c[d] P_{d-2}
- * (d = 1..deg, P_0 = 1, P_{-1} = 0; deg+1 floats per HOST array, entry 0 unused) for inspection.
+ * (d = 1..deg, P_0 = 1, P_{-1} = 0; deg+1 floats per HOST array; entry 0 is a = 0, b = 1, c = 0)
+ * for inspection.
  */
 #define CHEBYKAN_FAMILY_CHEBYSHEV    0
 #define CHEBYKAN_FAMILY_JACOBI       1
@@ -242,12 +243,16 @@ int chebykan_family_table(const chebykan_family* family, int64_t deg, float* a_h
 int chebykan_family_fwd(const chebykan_family* family, const float* x, const void* packed, float* y,
                         int64_t B, int64_t in, int64_t out, int64_t deg, int mode, int32_t* status,
                         void* stream);
+int64_t chebykan_family_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int64_t deg,
+                                        int mode);
 int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, const float* dy,
                                float* dcoeffs, void* workspace, int64_t workspace_bytes, int64_t B,
-                               int64_t in, int64_t out, int64_t deg, int accumulate, void* stream);
+                               int64_t in, int64_t out, int64_t deg, int mode, int accumulate,
+                               int32_t* status, void* stream);
 int chebykan_family_bwd_dx(const chebykan_family* family, const float* x, const float* dy,
-                           const float* coeffs, float* dx, int64_t B, int64_t in, int64_t out,
-                           int64_t deg, void* stream);
+                           const float* coeffs, float* dx, void* workspace, int64_t workspace_bytes,
+                           int64_t B, int64_t in, int64_t out, int64_t deg, int mode, int32_t* status,
+                           void* stream);
 int chebykan_family_normalize(const chebykan_family* family, const float* x, float* u, int64_t n,
                               void* stream);
 int chebykan_family_basis(const chebykan_family* family, const float* u, float* phi, int64_t n,

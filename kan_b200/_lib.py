@@ -51,10 +51,11 @@ SIGNATURES = {
     "chebykan_family_table": (c_int, [_FAM, c_int64, c_void_p, c_void_p, c_void_p]),
     "chebykan_family_fwd": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int,
                                     c_void_p, c_void_p]),
+    "chebykan_family_workspace_bytes": (c_int64, [c_int, c_int64, c_int64, c_int64, c_int64, c_int]),
     "chebykan_family_bwd_dcoeff": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                           c_int64, c_int64, c_int, c_void_p]),
-    "chebykan_family_bwd_dx": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64,
-                                       c_int64, c_void_p]),
+                                           c_int64, c_int64, c_int, c_int, c_void_p, c_void_p]),
+    "chebykan_family_bwd_dx": (c_int, [_FAM, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64,
+                                       c_int64, c_int64, c_int64, c_int, c_void_p, c_void_p]),
     "chebykan_family_normalize": (c_int, [_FAM, c_void_p, c_void_p, c_int64, c_void_p]),
     "chebykan_family_basis": (c_int, [_FAM, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "chebykan_mse_workspace_bytes": (c_int64, []),
@@ -96,7 +97,7 @@ def load() -> ctypes.CDLL:
         fn = getattr(lib, name)
         fn.restype = res
         fn.argtypes = args
-    if lib.chebykan_abi_version() != 6:
+    if lib.chebykan_abi_version() != 7:
         raise RuntimeError("libchebykan_b200.so ABI version mismatch; rebuild it")
     _lib = lib
     return lib

@@ -77,13 +77,20 @@ __device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t addr) {
     return d;
 }
 
-template <int BN, int CG>
+// FAM: another polynomial family; its recurrence table arrives as one more by-value parameter (an empty struct
+// otherwise) and the producer warps run the table recurrence instead of the Chebyshev one.
+struct DcNoTable {};
+template <bool FAM> struct DcTable { using type = DcNoTable; };
+template <> struct DcTable<true> { using type = RecurrenceTable; };
+
+template <int BN, int CG, bool FAM>
 __global__ void __launch_bounds__(DC_THREADS, 1)
 dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
                  int use_x_tma, int x_box_w, int nxs, int x_slot_bytes, const float* __restrict__ x,
                  float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
                  int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
-                 int32_t* status, int part, int exact_tanh) {
+                 int32_t* status, int part, int exact_tanh,
+                 const __grid_constant__ typename DcTable<FAM>::type rec) {
     using L = DcSmem<BN, CG>;
     constexpr int NS = L::NS;
     // tf32 x tf32 -> f32, A K-major, B MN-major, M = 128 per CTA, N = BNI
@@ -220,10 +227,37 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     bool finite = true;           // a NaN input makes every degree NaN: no rounding add then
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float t = exact_tanh ? tanhf(xc[r][e]) : tanh_fast(xc[r][e]);
+                        float t = exact_tanh ? tanhf(xc[r][e]) : tanh_fast(xc[r][e]);
+                        if constexpr (FAM) {
+                            // the family's normalised input u; P_0 = 1, P_{-1} = 0
+                            t = rec.affine ? fmaf(rec.scale, xc[r][e] - rec.shift, rec.offset) : rec.scale * t;
+                            t2[e] = t; ta[e] = 1.f; tb[e] = 0.f;
+                        } else {
+                            t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
+                        }
                         finite = finite && (t == t);
-                        t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
                     }
+                    // degree d from the two before it: into tb from (ta, tb), or into ta from (tb, ta)
+                    auto next_b = [&](int d) {
+                        if constexpr (FAM) {
+                            const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) tb[e] = fmaf(fmaf(ra, t2[e], rb), ta[e], -(rc * tb[e]));
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
+                        }
+                    };
+                    auto next_a = [&](int d) {
+                        if constexpr (FAM) {
+                            const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(fmaf(ra, t2[e], rb), tb[e], -(rc * ta[e]));
+                        } else {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
+                        }
+                    };
                     const uint32_t inc = finite ? TF32_HALF_ULP : 0u;
                     // one 16-byte chunk (4 batch rows) per degree; ta / tb alternate as the newest value
                     // Slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart): its chunk c sits
@@ -252,21 +286,17 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     for (; d + 7 < dp1; d += 8) {
 #pragma unroll
                         for (int h = 0; h < 4; ++h) {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
+                            next_b(d + 2 * h);
                             store4(tb);
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
+                            next_a(d + 2 * h + 1);
                             store4(ta);
                         }
                     }
                     for (; d < dp1; d += 2) {
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) tb[e] = fmaf(t2[e], ta[e], -tb[e]);
+                        next_b(d);
                         store4(tb);
                         if (d + 1 < dp1) {
-#pragma unroll
-                            for (int e = 0; e < 4; ++e) ta[e] = fmaf(t2[e], tb[e], -ta[e]);
+                            next_a(d + 1);
                             store4(ta);
                         }
                     }
@@ -495,14 +525,15 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0)
     return p;
 }
 
-template <int BN, int CG = 1>
-int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
-              const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s, int part, int exact) {
+template <int BN, int CG, bool FAM>
+int launch_dc_fam(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
+                  const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s, int part, int exact,
+                  const typename DcTable<FAM>::type& rec) {
     using L = DcSmem<BN, CG>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dcoeff_tc_kernel<BN, CG>;
+    auto kernel = dcoeff_tc_kernel<BN, CG, FAM>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -522,7 +553,16 @@ int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma,
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in,
                                          out, dp1, p.TI, p.i_tiles, p.n_tiles, p.rows_per_split, split_stride, add,
-                                         status, part, exact));
+                                         status, part, exact, rec));
+}
+
+template <int BN, int CG = 1>
+int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, int x_box_w, const float* x, float* dst, int64_t B, int in, int out, int dp1,
+              const DcTcPlan& p, int64_t split_stride, int add, int32_t* status, cudaStream_t s, int part, int exact,
+              const RecurrenceTable* rec) {
+    if (rec != nullptr)
+        return launch_dc_fam<BN, CG, true>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, in, out, dp1, p, split_stride, add, status, s, part, exact, *rec);
+    return launch_dc_fam<BN, CG, false>(tmap, tmap_x, use_x_tma, x_box_w, x, dst, B, in, out, dp1, p, split_stride, add, status, s, part, exact, DcNoTable());
 }
 
 }  // namespace
@@ -544,8 +584,9 @@ static int64_t x3_group_rows(int64_t in, int64_t out, int64_t deg) {
     return slices * DC_X3_ROWS;
 }
 
-int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
-    if (!x3 && dcoeff_f16_supported(B, in, out, deg)) return dcoeff_f16_workspace_bytes(B, in, out, deg);
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3, int family) {
+    // (the fp16-operand kernel of narrow layers is for the Chebyshev basis only: its values stay in [-1, 1])
+    if (!x3 && !family && dcoeff_f16_supported(B, in, out, deg)) return dcoeff_f16_workspace_bytes(B, in, out, deg);
     if (x3 && B > x3_group_rows(in, out, deg)) B = x3_group_rows(in, out, deg);
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
     const int64_t partials = p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
@@ -556,8 +597,10 @@ int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t de
 int launch_dy_tail(const float* dy, float* lo, int64_t n, cudaStream_t s);
 
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
-                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3) {
-    if (!x3 && dcoeff_f16_supported(B, in, out, deg))
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3,
+                     const RecurrenceTable* rec) {
+    if (rec != nullptr && x3) return CHEBYKAN_EUNSUPPORTED;
+    if (!x3 && rec == nullptr && dcoeff_f16_supported(B, in, out, deg))
         return launch_dcoeff_f16(x, dy, dc, ws, ws_bytes, B, in, out, deg, accumulate, status, s);
     if (x3 && B > x3_group_rows(in, out, deg)) {
         // group after group of batch slices through the same workspace (stream order keeps them apart)
@@ -574,8 +617,8 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
     const int dp1 = (int)deg + 1;
     const int64_t n = in * out * dp1;
     const bool direct = p.splits == 1;
-    if (dcoeff_tc_workspace_bytes(B, in, out, deg, x3) > 0 &&
-        (ws == nullptr || ws_bytes < dcoeff_tc_workspace_bytes(B, in, out, deg, x3)))
+    if (dcoeff_tc_workspace_bytes(B, in, out, deg, x3, rec != nullptr) > 0 &&
+        (ws == nullptr || ws_bytes < dcoeff_tc_workspace_bytes(B, in, out, deg, x3, rec != nullptr)))
         return CHEBYKAN_EWORKSPACE;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
@@ -624,11 +667,11 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
         const int part = x3 ? (pass == 2 ? 2 : 1) : 0;
         const int acc = (pass == 0) ? accumulate : 1;
         const int add = direct && acc;
-        if (p.bn == 64) rc = launch_dc<64>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
-        else if (p.bn == 128) rc = launch_dc<128>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
-        else if (p.bn == 256) rc = launch_dc<256>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
-        else if (p.cg == 2) rc = launch_dc<512, 2>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
-        else rc = launch_dc<512>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3);
+        if (p.bn == 64) rc = launch_dc<64>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3, rec);
+        else if (p.bn == 128) rc = launch_dc<128>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3, rec);
+        else if (p.bn == 256) rc = launch_dc<256>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3, rec);
+        else if (p.cg == 2) rc = launch_dc<512, 2>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3, rec);
+        else rc = launch_dc<512>(m, tmap_x, use_x_tma, x_box_w, x, dst, B, (int)in, (int)out, dp1, p, n, add, status, s, part, x3, rec);
         if (rc) return rc;
         if (!direct && (rc = launch_dcoeff_reduce(partials, dc, n, p.splits, acc, s))) return rc;
     }

@@ -82,9 +82,11 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t& r) {
 // T_d' = d U_{d-1} is folded in here so that the epilogue only needs U_{d-1} * G per value.
 // PART 0: rounded to tf32 (the tf32 / bf16 modes).  PART 1: head = the value truncated to tf32, and the tail
 // (value - head, fp32) in a second matrix right behind the first (the fp32-grade three-product mode).
+// degree_factor = 0: plain C (other polynomial families: their P_d' comes whole from the differentiated recurrence).
 template <int PART>
 __global__ void __launch_bounds__(256)
-pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad) {
+pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad,
+               int degree_factor) {
     const int64_t total = (int64_t)in * dp1 * out_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
          e += (int64_t)gridDim.x * blockDim.x) {
@@ -93,7 +95,7 @@ pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, i
         const int64_t i = slot / dp1;
         const int d = (int)(slot % dp1);
         float v = 0.f;
-        if (o < out) v = (float)d * c[(i * out + o) * dp1 + d];
+        if (o < out) v = (degree_factor ? (float)d : 1.f) * c[(i * out + o) * dp1 + d];
         if (PART == 0) {
             uint32_t r;
             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -129,11 +131,31 @@ struct DxFold {
     __device__ __forceinline__ void one(uint32_t g) { sum = fmaf(ua, __uint_as_float(g), sum); }
 };
 
-template <int CG, int BN>
+// The same for a table-driven family: sum += P_d'(u) G_d with P and P' carried side by side through the recurrence
+// and its derivative.  Entry 0 of the table (A = 0, B = 1, C = 0) with the start state P_{-1} = 1 makes column 0
+// (P_0 = 1, P_0' = 0) an ordinary step.
+struct DxFoldTable {
+    float p1 = 1.f, p2 = 0.f, d1 = 0.f, d2 = 0.f, sum = 0.f, u;
+    __device__ __forceinline__ explicit DxFoldTable(float u_) : u(u_) {}
+    __device__ __forceinline__ void one(const RecurrenceTable& t, int d, uint32_t g) {
+        const float a = t.A[d], c = t.C[d];
+        const float k = fmaf(a, u, t.B[d]);
+        const float dp = fmaf(a, p1, fmaf(k, d1, -(c * d2)));
+        const float p = fmaf(k, p1, -(c * p2));
+        sum = fmaf(dp, __uint_as_float(g), sum);
+        p2 = p1; p1 = p; d2 = d1; d1 = dp;
+    }
+};
+struct DxNoTable {};
+template <bool FAM> struct DxTable { using type = DxNoTable; };
+template <> struct DxTable<true> { using type = RecurrenceTable; };
+
+template <int CG, int BN, bool FAM>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
              const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
-             int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh) {
+             int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh,
+             const __grid_constant__ typename DxTable<FAM>::type rec) {
     using L = DxSmem<CG, BN>;
     constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS, NACC = L::NACC;
     constexpr int GROUP_WARPS = DX_EPI_WARPS / NACC;     // epilogue warps per accumulator
@@ -301,6 +323,62 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(acc * BN);
+            if constexpr (FAM) {
+                // table-driven family: same pairing of inputs, one column per step (P and P' both advance)
+                for (int ii = ii_begin; ii < ii_end; ii += 2) {
+                    const bool has_b = ii + 1 < ii_end;
+                    const float tha = tanh_fast(xa), thb = tanh_fast(xb);
+                    const float ua = rec.affine ? fmaf(rec.scale, xa - rec.shift, rec.offset) : rec.scale * tha;
+                    const float ub = rec.affine ? fmaf(rec.scale, xb - rec.shift, rec.offset) : rec.scale * thb;
+                    const float dua = rec.affine ? rec.scale : rec.scale * fmaf(-tha, tha, 1.f);     // du/dx
+                    const float dub = rec.affine ? rec.scale : rec.scale * fmaf(-thb, thb, 1.f);
+                    if (row_ok && ii + 2 < ii_end) xa = __ldg(xrow + ii + 2);
+                    if (row_ok && ii + 3 < ii_end) xb = __ldg(xrow + ii + 3);
+                    DxFoldTable fa(ua), fb(ub);
+                    const uint32_t col_a = taddr + (uint32_t)(ii * dp1);
+                    const uint32_t col_b = has_b ? col_a + (uint32_t)dp1 : col_a;
+                    int c = 0;
+                    for (; c + 16 <= dp1; c += 16) {
+                        uint32_t ra[16], rb[16];
+                        tmem_ld16(col_a + c, ra); tmem_ld16(col_b + c, rb); tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                    }
+                    if ((dp1 - c) & 8) {
+                        uint32_t ra[8], rb[8];
+                        tmem_ld8(col_a + c, ra); tmem_ld8(col_b + c, rb); tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                        c += 8;
+                    }
+                    if ((dp1 - c) & 4) {
+                        uint32_t ra[4], rb[4];
+                        tmem_ld4(col_a + c, ra); tmem_ld4(col_b + c, rb); tmem_ld_wait();
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                        c += 4;
+                    }
+                    if ((dp1 - c) & 2) {
+                        uint32_t ra[2], rb[2];
+                        tmem_ld2(col_a + c, ra); tmem_ld2(col_b + c, rb); tmem_ld_wait();
+                        fa.one(rec, c, ra[0]); fb.one(rec, c, rb[0]); fa.one(rec, c + 1, ra[1]); fb.one(rec, c + 1, rb[1]);
+                        c += 2;
+                    }
+                    if ((dp1 - c) & 1) {
+                        uint32_t ra = 0u, rb = 0u;
+                        tmem_ld1(col_a + c, ra); tmem_ld1(col_b + c, rb); tmem_ld_wait();
+                        fa.one(rec, c, ra); fb.one(rec, c, rb);
+                    }
+                    if (row_ok) {
+                        const float va = dua * fa.sum;
+                        dxrow[ii] = accumulate ? dxrow[ii] + va : va;
+                        if (has_b) {
+                            const float vb = dub * fb.sum;
+                            dxrow[ii + 1] = accumulate ? dxrow[ii + 1] + vb : vb;
+                        }
+                    }
+                }
+            } else {
             for (int ii = ii_begin; ii < ii_end; ii += 2) {
                 const bool has_b = ii + 1 < ii_end;          // warp-uniform; without B the second lane of work repeats A
                 const float ta = exact_tanh ? tanhf(xa) : tanh_fast(xa);
@@ -366,6 +444,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     }
                 }
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -412,14 +491,15 @@ int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, i
 }
 
 namespace {
-template <int CG, int BN>
+template <int CG, int BN, bool FAM>
 int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
-                     int in, int out, int dp1, int32_t* status, cudaStream_t s, int accumulate = 0, int exact_tanh = 0) {
+                     int in, int out, int dp1, int32_t* status, cudaStream_t s, int accumulate, int exact_tanh,
+                     const typename DxTable<FAM>::type& rec) {
     using L = DxSmem<CG, BN>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dx_tc_kernel<CG, BN>;
+    auto kernel = dx_tc_kernel<CG, BN, FAM>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -440,12 +520,15 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, dp1, TI, i_tiles, num_tiles,
-                                         status, accumulate, exact_tanh));
+                                         status, accumulate, exact_tanh, rec));
 }
 }  // namespace
 
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
-                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3) {
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3,
+                 const RecurrenceTable* rec) {
+    if (rec != nullptr && x3) return CHEBYKAN_EUNSUPPORTED;
+    const int degree_factor = rec == nullptr;
     const int dp1 = (int)deg + 1;
     const int64_t out_pad = round_up(out, 32);
     const int64_t slots = in * dp1;
@@ -459,8 +542,8 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     {
         int64_t blocks = ceil_div(slots * out_pad, 256);
         if (blocks > 148 * 16) blocks = 148 * 16;
-        if (x3) pack_dx_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad);
-        else pack_dx_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad);
+        if (x3) pack_dx_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad, degree_factor);
+        else pack_dx_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad, degree_factor);
         int rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
         if (x3) {
@@ -494,8 +577,12 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
         return CHEBYKAN_OK;
     };
     auto run = [&](const CUtensorMap& mdy, const CUtensorMap& mw, int accumulate) -> int {
-        if (cg == 2) return launch_dx_kernel<2, DX_BN>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
-        return launch_dx_kernel<1, DX_BN>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3);
+        if (rec != nullptr) {
+            if (cg == 2) return launch_dx_kernel<2, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, 0, *rec);
+            return launch_dx_kernel<1, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, 0, *rec);
+        }
+        if (cg == 2) return launch_dx_kernel<2, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3, DxNoTable());
+        return launch_dx_kernel<1, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3, DxNoTable());
     };
     CUtensorMap m_dy, m_w;
     int rc;

@@ -171,15 +171,18 @@ bool dcoeff_f16_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
 int64_t dcoeff_f16_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg);
 int launch_dcoeff_f16(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B, int64_t in,
                       int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s);
-int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0);
+// `family` / `rec`: another polynomial family (tf32 kernel with the table recurrence; never the fp16-operand one)
+int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0, int family = 0);
 int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64_t ws_bytes, int64_t B,
-                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3 = 0);
+                     int64_t in, int64_t out, int64_t deg, int accumulate, int32_t* status, cudaStream_t s, int x3 = 0,
+                     const RecurrenceTable* rec = nullptr);
 int launch_dx_ffma(const float* x, const float* dy, const float* coeffs, float* dx, int64_t B,
                    int64_t in, int64_t out, int64_t deg, cudaStream_t s, const RecurrenceTable* rec = nullptr);
 bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg);
 int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3);
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
-                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3);
+                 int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3,
+                 const RecurrenceTable* rec = nullptr);
 int launch_sgd(float* p, const float* g, int64_t n, float lr, float gs, cudaStream_t s);
 int launch_adam(float* p, const float* g, float* m, float* v, int64_t n, float lr, float b1,
                 float b2, float eps, int64_t step, float gs, cudaStream_t s);

@@ -21,6 +21,7 @@ static int build_table(const chebykan_family* f, int64_t deg, RecurrenceTable* t
     t->shift = f->shift;
     t->offset = f->offset;
     for (int d = 0; d < 128; ++d) { t->A[d] = 0.f; t->B[d] = 0.f; t->C[d] = 0.f; }
+    t->B[0] = 1.f;      // entry 0: P_0 = (0 u + 1) P_{-1} with P_{-1} = 1, for kernels that treat degree 0 as a step
     switch (f->kind) {
         case CHEBYKAN_FAMILY_CHEBYSHEV:
             t->A[1] = 1.f;
@@ -119,11 +120,40 @@ int chebykan_family_fwd(const chebykan_family* family, const float* x, const voi
     return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream, LnFusion(), &t);
 }
 
+static bool family_mode_ok(int mode) {
+    return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16;
+}
+// tf32 / bf16 modes: the tcgen05 kind::tf32 kernels of the Chebyshev layer's backward with the table recurrence,
+// on the shapes those kernels cover; fp32 mode and every other shape: the FFMA kernels
+static bool family_dcoeff_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    return mode != CHEBYKAN_MODE_FP32 && B > 0 && dcoeff_tc_supported(B, in, out, deg);
+}
+static bool family_dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    return mode != CHEBYKAN_MODE_FP32 && B > 0 && dx_tc_supported(B, in, out, deg);
+}
+
+int64_t chebykan_family_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
+    if (!family_shape_ok(B, in, out, deg)) return CHEBYKAN_EINVAL;
+    if (!family_mode_ok(mode)) return mode == CHEBYKAN_MODE_FP32X3 ? CHEBYKAN_EUNSUPPORTED : CHEBYKAN_EINVAL;
+    switch (op) {
+        case CHEBYKAN_OP_FWD: return 0;
+        case CHEBYKAN_OP_BWD_DCOEFF:
+            if (B == 0) return 0;
+            return family_dcoeff_on_tensor_cores(B, in, out, deg, mode)
+                       ? dcoeff_tc_workspace_bytes(B, in, out, deg, 0, 1)
+                       : dcoeff_workspace_bytes(B, in, out, deg, CHEBYKAN_MODE_FP32);
+        case CHEBYKAN_OP_BWD_DX:
+            return family_dx_on_tensor_cores(B, in, out, deg, mode) ? dx_tc_workspace_bytes(B, in, out, deg, 0) : 0;
+        default: return CHEBYKAN_EINVAL;
+    }
+}
+
 int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, const float* dy, float* dcoeffs,
                                void* workspace, int64_t workspace_bytes, int64_t B, int64_t in, int64_t out,
-                               int64_t deg, int accumulate, void* stream) {
+                               int64_t deg, int mode, int accumulate, int32_t* status, void* stream) {
     RecurrenceTable t;
     if (!family_shape_ok(B, in, out, deg) || !dcoeffs) return CHEBYKAN_EINVAL;
+    if (!family_mode_ok(mode)) return mode == CHEBYKAN_MODE_FP32X3 ? CHEBYKAN_EUNSUPPORTED : CHEBYKAN_EINVAL;
     int rc = build_table(family, deg, &t);
     if (rc) return rc;
     if (!aligned16(dcoeffs) || !aligned16(workspace)) return CHEBYKAN_EALIGN;
@@ -135,19 +165,29 @@ int chebykan_family_bwd_dcoeff(const chebykan_family* family, const float* x, co
     }
     if (!x || !dy) return CHEBYKAN_EINVAL;
     if (!aligned16(x) || !aligned16(dy)) return CHEBYKAN_EALIGN;
+    if (family_dcoeff_on_tensor_cores(B, in, out, deg, mode)) {
+        if (!status) return CHEBYKAN_EINVAL;
+        return launch_dcoeff_tc(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate, status, s, 0, &t);
+    }
     return launch_dcoeff_ffma(x, dy, dcoeffs, workspace, workspace_bytes, B, in, out, deg, accumulate, s, &t);
 }
 
 int chebykan_family_bwd_dx(const chebykan_family* family, const float* x, const float* dy, const float* coeffs,
-                           float* dx, int64_t B, int64_t in, int64_t out, int64_t deg, void* stream) {
+                           float* dx, void* workspace, int64_t workspace_bytes, int64_t B, int64_t in, int64_t out,
+                           int64_t deg, int mode, int32_t* status, void* stream) {
     RecurrenceTable t;
     if (!family_shape_ok(B, in, out, deg) || !coeffs) return CHEBYKAN_EINVAL;
+    if (!family_mode_ok(mode)) return mode == CHEBYKAN_MODE_FP32X3 ? CHEBYKAN_EUNSUPPORTED : CHEBYKAN_EINVAL;
     int rc = build_table(family, deg, &t);
     if (rc) return rc;
     if (B == 0) return CHEBYKAN_OK;
     if (!x || !dy || !dx) return CHEBYKAN_EINVAL;
-    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(coeffs)) return CHEBYKAN_EALIGN;
+    if (!aligned16(x) || !aligned16(dy) || !aligned16(dx) || !aligned16(coeffs) || !aligned16(workspace)) return CHEBYKAN_EALIGN;
     if ((rc = check_device())) return rc;
+    if (family_dx_on_tensor_cores(B, in, out, deg, mode)) {
+        if (!status) return CHEBYKAN_EINVAL;
+        return launch_dx_tc(x, dy, coeffs, dx, workspace, workspace_bytes, B, in, out, deg, status, (cudaStream_t)stream, 0, &t);
+    }
     return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream, &t);
 }
 

@@ -295,33 +295,34 @@ def family_forward(family, x: torch.Tensor, packed: torch.Tensor, in_dim: int, o
 
 
 def family_bwd_dcoeff(family, x: torch.Tensor, dy: torch.Tensor, in_dim: int, out_dim: int, degree: int,
-                      out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
-    """dC[in,out,deg+1] = sum_b P_d(u(x[b,i])) dY[b,o]."""
+                      mode="fp32", out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
+    """dC[in,out,deg+1] = sum_b P_d(u(x[b,i])) dY[b,o]; 'tf32' / 'bf16' contract on the tensor cores in tf32."""
     _require(x, "x")
     _require(dy, "dy")
     B = x.shape[0]
     if x.shape != (B, in_dim) or dy.shape != (B, out_dim):
         raise RuntimeError("x must be [B, in] and dy [B, out]")
     lib = _lib.load()
+    m = _mode(mode)
     if out is None:
         out = torch.empty(in_dim, out_dim, degree + 1, dtype=torch.float32, device=x.device)
         accumulate = False
     else:
         _require(out, "out")
-    ws_bytes = lib.chebykan_workspace_bytes(OP_BWD_DCOEFF, B, in_dim, out_dim, degree, _lib.MODE_FP32)
-    _lib.check(ws_bytes, "chebykan_workspace_bytes")
+    ws_bytes = lib.chebykan_family_workspace_bytes(OP_BWD_DCOEFF, B, in_dim, out_dim, degree, m)
+    _lib.check(ws_bytes, "chebykan_family_workspace_bytes")
     ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     with _Range("chebykan.family_dcoeff"), torch.cuda.device(x.device):
         rc = lib.chebykan_family_bwd_dcoeff(ctypes.byref(family), x.data_ptr(), dy.data_ptr(), out.data_ptr(),
-                                            ws.data_ptr(), ws_bytes, B, in_dim, out_dim, degree, int(accumulate),
-                                            _stream(x))
+                                            ws.data_ptr(), ws_bytes, B, in_dim, out_dim, degree, m, int(accumulate),
+                                            status_tensor(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "chebykan_family_bwd_dcoeff")
     return out
 
 
-def family_bwd_dx(family, x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor,
+def family_bwd_dx(family, x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tensor, mode="fp32",
                   out: torch.Tensor | None = None) -> torch.Tensor:
-    """dx[B,in] = du/dx * sum_d P_d'(u) sum_o dY[b,o] C[i,o,d]."""
+    """dx[B,in] = du/dx * sum_d P_d'(u) sum_o dY[b,o] C[i,o,d]; 'tf32' / 'bf16' contract on the tensor cores in tf32."""
     _require(x, "x")
     _require(dy, "dy")
     _require(coeffs, "coeffs")
@@ -333,9 +334,15 @@ def family_bwd_dx(family, x: torch.Tensor, dy: torch.Tensor, coeffs: torch.Tenso
         out = torch.empty_like(x)
     else:
         _require(out, "out")
+    lib = _lib.load()
+    m = _mode(mode)
+    ws_bytes = lib.chebykan_family_workspace_bytes(OP_BWD_DX, B, n_in, n_out, dp1 - 1, m)
+    _lib.check(ws_bytes, "chebykan_family_workspace_bytes")
+    ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=x.device)
     with _Range("chebykan.family_dx"), torch.cuda.device(x.device):
-        rc = _lib.load().chebykan_family_bwd_dx(ctypes.byref(family), x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(),
-                                                out.data_ptr(), B, n_in, n_out, dp1 - 1, _stream(x))
+        rc = lib.chebykan_family_bwd_dx(ctypes.byref(family), x.data_ptr(), dy.data_ptr(), coeffs.data_ptr(),
+                                        out.data_ptr(), ws.data_ptr(), ws_bytes, B, n_in, n_out, dp1 - 1, m,
+                                        status_tensor(x.device).data_ptr(), _stream(x))
     _lib.check(rc, "chebykan_family_bwd_dx")
     return out
 

@@ -7,7 +7,8 @@ with the recurrence coefficients swapped (the library's ``chebykan_family_*`` en
 parameter names (``jacobi_coeffs`` / ``hermite_coeffs``), RNG consumption, ``state_dict``, ``forward``'s flatten
 rule, ``get_coefficients``, ``get_analytical_form`` and ``extra_repr`` mirror the reference.  ``math_mode='fp32'``
 (default) runs forward, dC and dx on the FFMA pipe with a correctly rounded tanh (rel-L2 <= 1e-5 to the reference);
-``'tf32'`` / ``'bf16'`` run the forward on the tcgen05 tensor cores (rel-L2 <= 2e-3) and keep the backward in fp32.
+``'tf32'`` / ``'bf16'`` run forward and backward on the tcgen05 tensor cores (rel-L2 <= 2e-3; the backward
+contracts in tf32 in both).
 There is no CPU path.
 """
 from __future__ import annotations
@@ -116,6 +117,7 @@ class _FamilyKANFunction(torch.autograd.Function):
         y = ops.family_forward(family, x, packed, n_in, n_out, dp1 - 1, mode)
         ctx.save_for_backward(x, coeffs)
         ctx.family = family
+        ctx.mode = mode
         return y
 
     @staticmethod
@@ -125,9 +127,9 @@ class _FamilyKANFunction(torch.autograd.Function):
         dy = _aligned(dy)
         dx = dc = None
         if ctx.needs_input_grad[1]:
-            dc = ops.family_bwd_dcoeff(ctx.family, x, dy, n_in, n_out, dp1 - 1)
+            dc = ops.family_bwd_dcoeff(ctx.family, x, dy, n_in, n_out, dp1 - 1, ctx.mode)
         if ctx.needs_input_grad[0]:
-            dx = ops.family_bwd_dx(ctx.family, x, dy, _aligned(coeffs.detach()))
+            dx = ops.family_bwd_dx(ctx.family, x, dy, _aligned(coeffs.detach()), ctx.mode)
         return dx, dc, None, None, None
 
 
@@ -160,7 +162,7 @@ def make_jacobikan_layer_class(base_cls, basis_cls, name: str = "JacobiKANLayer"
     class _Layer(base_cls):
         """KAN layer on Jacobi polynomials, computed by sm_100a CUDA kernels.
         Args as in the reference (kan/layers/jacobikan.py:20-33): input_dim, output_dim, degree, alpha, beta, init_scale;
-        keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor-core forward, fp32 backward)."""
+        keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor cores)."""
 
         def __init__(self, input_dim: int, output_dim: int, degree: int, alpha: float = 0.0, beta: float = 0.0,
                      init_scale: float = None, *, math_mode: str = "fp32"):
@@ -218,8 +220,7 @@ def make_hermitekan_layer_class(base_cls, basis_cls, name: str = "HermiteKANLaye
     class _Layer(base_cls):
         """KAN layer on Hermite polynomials, computed by sm_100a CUDA kernels.
         Args as in the reference (kan/layers/hermitekan.py:22-40): input_dim, output_dim, degree, scaling, domain,
-        normalize_domain, init_scale; keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor-core forward,
-        fp32 backward)."""
+        normalize_domain, init_scale; keyword-only math_mode: 'fp32' (default), 'tf32' or 'bf16' (tensor cores)."""
 
         def __init__(self, input_dim: int, output_dim: int, degree: int, scaling: str = 'physicist',
                      domain: Optional[Tuple[float, float]] = None, normalize_domain: bool = True,

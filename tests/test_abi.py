@@ -34,7 +34,7 @@ def test_binding_table_covers_header(built_lib):
 
 def test_pure_host_entry_points(built_lib):
     lib = _lib.load()
-    assert lib.chebykan_abi_version() == 6
+    assert lib.chebykan_abi_version() == 7
     assert _lib.strerror(0) == "ok"
     assert "aligned" in _lib.strerror(-2)
     # packed sizes: fp32 [K_pad][N_pad] with blocks of 8 inputs, outputs padded to 64

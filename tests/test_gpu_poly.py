@@ -121,8 +121,44 @@ def test_tensor_core_forward_matches_oracle(mode, fam, shape):
     assert o.rel_l2(y.cpu(), y_ref) <= TC_TOL
 
 
+# backward on the tensor cores (kind::tf32 in both modes): CTA pairs and single CTAs, ragged tiles, narrow and wide
+# outputs (narrow layers must not take the Chebyshev-only fp16-operand kernel), degree 0 and 1, one row
+TC_BWD_SHAPES = [(1000, 96, 520, 5), (300, 64, 256, 4), (4096, 64, 64, 12), (257, 40, 100, 8), (64, 72, 392, 1),
+                 (128, 256, 1024, 0), (1, 8, 600, 3), (5000, 33, 20, 6)]
+
+
+@pytest.mark.parametrize("fam", FAMILIES, ids=lambda f: "-".join(str(v) for v in f.values()))
+@pytest.mark.parametrize("shape", TC_BWD_SHAPES, ids=lambda s: "x".join(map(str, s)))
+def test_tensor_core_backward_matches_oracle(fam, shape):
+    B, n_in, n_out, deg = shape
+    g = torch.Generator().manual_seed(B + n_in + deg + 2)
+    x = torch.randn(B, n_in, generator=g)
+    if fam.get("domain"):
+        x = x.clamp(-4, 4)
+    coeffs = torch.randn(n_in, n_out, deg + 1, generator=g) / (n_in * (deg + 1))
+    dy = torch.randn(B, n_out, generator=g)
+    _, dC_ref, dx_ref = po.forward_backward(fam, x, coeffs, dy)
+    lf = lib_family(fam)
+    dC, dC_whole = guarded(tuple(coeffs.shape))
+    dx, dx_whole = guarded(tuple(x.shape))
+    ops.family_bwd_dcoeff(lf, x.cuda(), dy.cuda(), n_in, n_out, deg, "tf32", out=dC)
+    ops.family_bwd_dx(lf, x.cuda(), dy.cuda(), coeffs.cuda(), "tf32", out=dx)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dC, dC_whole)
+    assert_guards_intact(dx, dx_whole)
+    assert o.rel_l2(dC.cpu(), dC_ref) <= TC_TOL
+    if deg > 0:
+        assert o.rel_l2(dx.cpu(), dx_ref) <= TC_TOL
+    else:
+        assert not bool(dx.any())
+    # accumulate adds into what is there
+    acc = ops.family_bwd_dcoeff(lf, x.cuda(), dy.cuda(), n_in, n_out, deg, "bf16", out=dC.clone(), accumulate=True)
+    assert o.rel_l2(acc.cpu(), 2 * dC_ref) <= TC_TOL
+
+
 @pytest.mark.parametrize("mode", ["bf16", "tf32"])
-def test_tensor_core_layers_keep_an_fp32_backward(mode):
+def test_tensor_core_layers_train_on_the_tensor_cores(mode):
     torch.manual_seed(4)
     layer = kan_b200.JacobiKANLayer(48, 300, 6, alpha=0.5, beta=-0.3, math_mode=mode).cuda()
     coeffs = layer.jacobi_coeffs.detach().cpu()
@@ -135,12 +171,14 @@ def test_tensor_core_layers_keep_an_fp32_backward(mode):
     fam = {"kind": "jacobi", "alpha": 0.5, "beta": -0.3}
     y_ref, dC_ref, dx_ref = po.forward_backward(fam, x, coeffs, dy)
     assert o.rel_l2(y.detach().cpu(), po.forward(fam, x, coeffs.bfloat16().float() if mode == "bf16" else coeffs)) <= TC_TOL
-    assert o.rel_l2(layer.jacobi_coeffs.grad.cpu(), dC_ref) <= FP32_TOL
-    assert o.rel_l2(xd.grad.cpu(), dx_ref) <= FP32_TOL
+    assert o.rel_l2(layer.jacobi_coeffs.grad.cpu(), dC_ref) <= TC_TOL
+    assert o.rel_l2(xd.grad.cpu(), dx_ref) <= TC_TOL
     with pytest.raises(ValueError, match="math_mode"):
         kan_b200.HermiteKANLayer(3, 2, 4, math_mode="fp32x3")
     with pytest.raises(RuntimeError, match="not supported"):
         ops.family_forward(ops.make_family("hermite"), x.cuda(), ops.pack_coeffs(coeffs.cuda(), "fp32x3"), 48, 300, 6, "fp32x3")
+    with pytest.raises(RuntimeError, match="not supported"):
+        ops.family_bwd_dx(ops.make_family("hermite"), x.cuda(), dy.cuda(), coeffs.cuda(), "fp32x3")
 
 
 def test_chebyshev_through_the_table_equals_the_chebyshev_kernels():
