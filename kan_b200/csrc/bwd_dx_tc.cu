@@ -334,6 +334,8 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     const float dub = rec.affine ? rec.scale : rec.scale * fmaf(-thb, thb, 1.f);
                     if (row_ok && ii + 2 < ii_end) xa = __ldg(xrow + ii + 2);
                     if (row_ok && ii + 3 < ii_end) xb = __ldg(xrow + ii + 3);
+                    float old_a = 0.f, old_b = 0.f;
+                    if (accumulate && row_ok) { old_a = dxrow[ii]; if (has_b) old_b = dxrow[ii + 1]; }
                     DxFoldTable fa(ua), fb(ub);
                     const uint32_t col_a = taddr + (uint32_t)(ii * dp1);
                     const uint32_t col_b = has_b ? col_a + (uint32_t)dp1 : col_a;
@@ -371,10 +373,10 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     }
                     if (row_ok) {
                         const float va = dua * fa.sum;
-                        dxrow[ii] = accumulate ? dxrow[ii] + va : va;
+                        dxrow[ii] = accumulate ? old_a + va : va;
                         if (has_b) {
                             const float vb = dub * fb.sum;
-                            dxrow[ii + 1] = accumulate ? dxrow[ii + 1] + vb : vb;
+                            dxrow[ii + 1] = accumulate ? old_b + vb : vb;
                         }
                     }
                 }
@@ -385,6 +387,10 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 const float tb = exact_tanh ? tanhf(xb) : tanh_fast(xb);
                 if (row_ok && ii + 2 < ii_end) xa = __ldg(xrow + ii + 2);
                 if (row_ok && ii + 3 < ii_end) xb = __ldg(xrow + ii + 3);
+                // accumulating launches: what is in dx already, in flight while the columns are folded (one lane
+                // per row: each of these loads is its own sector, and its latency would end the round otherwise)
+                float old_a = 0.f, old_b = 0.f;
+                if (accumulate && row_ok) { old_a = dxrow[ii]; if (has_b) old_b = dxrow[ii + 1]; }
                 // ua / ub alternate as (U_{d-1}, U_{d-2}); U_{-1} = 0, U_{-2} = -1 make U_0 = 1 and
                 // give the d = 0 column (whose coefficients are 0 * C) weight zero without a branch
                 DxFold fa(2.f * ta), fb(2.f * tb);
@@ -437,10 +443,10 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 }
                 if (row_ok) {
                     const float va = fmaf(-ta, ta, 1.f) * fa.sum;
-                    dxrow[ii] = accumulate ? dxrow[ii] + va : va;
+                    dxrow[ii] = accumulate ? old_a + va : va;
                     if (has_b) {
                         const float vb = fmaf(-tb, tb, 1.f) * fb.sum;
-                        dxrow[ii + 1] = accumulate ? dxrow[ii + 1] + vb : vb;
+                        dxrow[ii + 1] = accumulate ? old_b + vb : vb;
                     }
                 }
             }
