@@ -42,7 +42,8 @@ extern "C" {
 
 /* arithmetic mode of the contraction */
 #define CHEBYKAN_MODE_FP32 0  /* fp32 FFMA on CUDA cores, correctly rounded tanh   */
-#define CHEBYKAN_MODE_TF32 1  /* tcgen05 kind::tf32, fp32 accumulate in TMEM       */
+#define CHEBYKAN_MODE_TF32 1  /* tcgen05 kind::tf32 (narrow layers: fp16 operands,   */
+                              /* the same 11 bits), fp32 accumulate in TMEM        */
 #define CHEBYKAN_MODE_BF16 2  /* tcgen05 kind::f16 (bf16 x bf16), fp32 accumulate  */
 /* fp32-grade forward on the tensor cores: basis values and coefficients are each
  * split into a tf32 head and a tf32 tail and three tcgen05 kind::tf32 products

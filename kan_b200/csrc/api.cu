@@ -91,6 +91,8 @@ int chebykan_last_cuda_error(void) { return g_last_cuda_error; }
 int64_t chebykan_packed_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
     if (!shape_ok(0, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
     const PackedDims p = packed_dims(in, out, deg, mode);
+    if (mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))     // narrow layers: the fp16 plane behind the tf32 matrix
+        return tf32_half_plane_offset(in, out, deg) + tf32_half_plane_bytes(in, out, deg);
     return p.k_pad * p.n_pad * p.elem * p.planes;
 }
 

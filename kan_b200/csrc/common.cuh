@@ -17,7 +17,8 @@ __host__ __device__ constexpr int64_t round_up(int64_t a, int64_t b) { return ce
 //   k = (i / 64) * (deg+1) * 64 + d * 64 + (i % 64), in padded to a multiple of
 //   64, out to a multiple of 128.  One 64-wide K block (= one 128-byte swizzle
 //   row) holds one degree of 64 consecutive inputs.
-// TF32 mode:  Wt[N_pad][K_pad] fp32 (rounded to tf32), blocks of 32 inputs.
+// TF32 mode:  Wt[N_pad][K_pad] fp32 (rounded to tf32), blocks of 32 inputs; narrow layers carry a second,
+//   fp16 plane behind it (see tf32_has_half_plane below).
 constexpr int FP32_IB = 8;
 constexpr int BF16_IB = 64;
 constexpr int TF32_IB = 32;
@@ -47,6 +48,29 @@ inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64
     p.in_pad = round_up(in, p.ib);
     p.k_pad = p.in_pad * (deg + 1);
     return p;
+}
+
+// TF32 mode, narrow layers (at most 128 outputs, in % 4 == 0): behind the tf32 matrix the packed buffer carries a
+// second plane for the tensor-memory forward kernel: a 256-byte header {bit pattern of max |C|, 1 / scale} and
+// the coefficients times a power-of-two scale as fp16 in the BF16 layout.
+constexpr int64_t HALF_PLANE_HEADER = 256;
+inline __host__ __device__ bool tf32_has_half_plane(int64_t in, int64_t out) { return out <= 128 && (in % 4) == 0; }
+inline __host__ __device__ int64_t tf32_half_plane_offset(int64_t in, int64_t out, int64_t deg) {
+    const PackedDims p = packed_dims(in, out, deg, CHEBYKAN_MODE_TF32);
+    return round_up(p.k_pad * p.n_pad * p.elem, 256);
+}
+inline __host__ __device__ int64_t tf32_half_plane_bytes(int64_t in, int64_t out, int64_t deg) {
+    const PackedDims p = packed_dims(in, out, deg, CHEBYKAN_MODE_BF16);
+    return HALF_PLANE_HEADER + p.k_pad * p.n_pad * 2;
+}
+// power of two that puts `maxbits` (a non-negative float's bit pattern) into [2^14, 2^15); 1 for zero, inf and NaN
+__device__ __forceinline__ float half_scale_for(uint32_t maxbits) {
+    const int e = (int)(maxbits >> 23);            // biased exponent; 0 = zero / subnormal, 255 = inf / NaN
+    if (e == 0 || e == 255) return 1.f;
+    int k = 14 - (e - 127);
+    if (k > 126) k = 126;                           // keep the scale a normal float
+    if (k < -126) k = -126;
+    return __uint_as_float((uint32_t)(k + 127) << 23);
 }
 
 // ---- tanh ------------------------------------------------------------------

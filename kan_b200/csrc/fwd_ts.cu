@@ -25,6 +25,9 @@
 // SM pulls from L2 per row (the whole packed matrix is re-read for every row tile).
 //
 // Every mbarrier wait is bounded; on expiry the kernel records a role code in *status, drains and frees its TMEM.
+#include <cuda_fp16.h>
+#include <stdlib.h>
+#include <string.h>
 #include "tc_common.cuh"
 
 namespace chebykan {
@@ -38,9 +41,13 @@ enum { TS_PRODUCER = 21, TS_TMA_W = 22, TS_MMA_A = 23, TS_MMA_B = 24, TS_MMA_ACC
 // NSUBM: row sub-tiles (of 128 rows) a CTA works on at once; KP: K blocks per stage; NACC: accumulator buffers.
 // The A ring takes the tensor-memory columns the accumulators leave: NSTG = (512 - NACC*NSUBM*BN) / (NSUBM*KP*32).
 #define TOTAL_CHECK(v) ((v) <= 232448)
+// Internal mode of this file: fp16 operands (basis values and a power-of-two scaled fp16 copy of the coefficients)
+// with the bf16 kernel's layouts.  fp16 carries tf32's 11 significant bits at half the tensor-memory columns, stores
+// and MMAs, and the basis values lie in [-1, 1]: this is what the TF32 math mode runs on narrow layers.
+constexpr int TS_MODE_F16 = 16;
 template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 struct TsCfg {
-    static constexpr bool BF16 = MODE == CHEBYKAN_MODE_BF16;
+    static constexpr bool BF16 = MODE == CHEBYKAN_MODE_BF16 || MODE == TS_MODE_F16;   // 16-bit operands
     static constexpr int NSUBM = NSUBM_;
     static constexpr int KP = KP_;
     static constexpr int NACC = NACC_;
@@ -88,7 +95,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 template <int MODE>
 __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    if (MODE == CHEBYKAN_MODE_BF16) {
+    if (MODE == CHEBYKAN_MODE_BF16 || MODE == TS_MODE_F16) {
         asm volatile(
             "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
@@ -104,11 +111,12 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
 template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 __global__ void __launch_bounds__(TsCfg<MODE, BN, NSUBM_, KP_, NACC_>::NUM_THREADS, 1)
 fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
-              float* __restrict__ y, int64_t B, int in, int out, int dp1, int64_t num_tiles, int32_t* status) {
+              float* __restrict__ y, int64_t B, int in, int out, int dp1, int64_t num_tiles, int32_t* status,
+              const float* __restrict__ out_scale) {
     using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     constexpr int NSUBM = C::NSUBM, KP = C::KP, NSTG = C::NSTG, NSB = C::NSB, NACC = C::NACC, NXS = C::NXS;
     constexpr int IB = C::IB, EPT = C::EPT;
-    constexpr uint32_t FMT = C::BF16 ? 1u : 2u;
+    constexpr uint32_t FMT = MODE == TS_MODE_F16 ? 0u : (C::BF16 ? 1u : 2u);      // f16, bf16, tf32
     constexpr uint32_t IDESC = (1u << 4) | (FMT << 7) | (FMT << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
     constexpr uint32_t D_COL0 = 0, A_COL0 = C::D_COLS;
 
@@ -173,8 +181,13 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
             if (C::BF16) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
-                    const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[(2 * c) % EPT], v[(2 * c + 1) % EPT]);
-                    w[c] = *reinterpret_cast<const uint32_t*>(&p2);
+                    if (MODE == TS_MODE_F16) {
+                        const __half2 p2 = __floats2half2_rn(v[(2 * c) % EPT], v[(2 * c + 1) % EPT]);
+                        w[c] = *reinterpret_cast<const uint32_t*>(&p2);
+                    } else {
+                        const __nv_bfloat162 p2 = __floats2bfloat162_rn(v[(2 * c) % EPT], v[(2 * c + 1) % EPT]);
+                        w[c] = *reinterpret_cast<const uint32_t*>(&p2);
+                    }
                 }
             } else {
 #pragma unroll
@@ -376,6 +389,8 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         int acc = 0; uint32_t acc_ph = 0;
         bool alive = true;
         const bool vec4 = (out & 3) == 0;
+        // fp16 operands: the coefficients were scaled by a power of two when they were packed; its inverse is exact
+        const float osc = (MODE == TS_MODE_F16) ? __ldg(out_scale) : 1.f;
         for (int64_t tile = blockIdx.x; tile < num_tiles && alive; tile += gridDim.x) {
             const bool ok = mbar_wait(acc_full_bar(acc), acc_ph, abort_flag, status, TS_EPILOGUE);
             if (!__all_sync(0xffffffffu, ok)) { alive = false; break; }
@@ -390,6 +405,10 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     uint32_t rg[16];
                     tmem_ld16(taddr + ch * 16, rg);
                     tmem_ld_wait();
+                    if (MODE == TS_MODE_F16) {
+#pragma unroll
+                        for (int e = 0; e < 16; ++e) rg[e] = __float_as_uint(__uint_as_float(rg[e]) * osc);
+                    }
                     if (row < B) {
                         float* dst = y + row * out + ch * 16;
 #pragma unroll
@@ -425,7 +444,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
 template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 int launch_ts(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, float* y, int64_t B, int in, int out, int dp1,
-              int32_t* status, cudaStream_t s) {
+              int32_t* status, cudaStream_t s, const float* out_scale = nullptr) {
     using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     static bool attr_set[64] = {false};
     static int sms[64] = {0};
@@ -443,11 +462,19 @@ int launch_ts(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, float* y, in
     }
     const int64_t num_tiles = ceil_div(B, 128 * C::NSUBM);
     const unsigned grid = (unsigned)(num_tiles < sms[dev] ? num_tiles : sms[dev]);
-    kernel<<<grid, C::NUM_THREADS, C::TOTAL, s>>>(tmap_w, tmap_x, y, B, in, out, dp1, num_tiles, status);
+    kernel<<<grid, C::NUM_THREADS, C::TOTAL, s>>>(tmap_w, tmap_x, y, B, in, out, dp1, num_tiles, status, out_scale);
     return check_cuda(cudaGetLastError());
 }
 
 }  // namespace
+
+static bool narrow_forward_tf32_operands() {
+    static const bool v = [] {
+        const char* e = getenv("CHEBYKAN_NARROW_FWD");
+        return e != nullptr && strcmp(e, "tf32") == 0;
+    }();
+    return v;
+}
 
 // narrow layers in the plain tf32 / bf16 modes whose x rows are TMA-addressable
 bool fwd_ts_supported(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
@@ -458,7 +485,13 @@ bool fwd_ts_supported(int64_t B, int64_t in, int64_t out, int64_t deg, int mode)
 
 int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out, int64_t deg, int mode,
                   int32_t* status, cudaStream_t s) {
-    const PackedDims p = packed_dims(in, out, deg, mode);
+    // TF32 mode: the fp16 plane behind the tf32 matrix (same layout as the bf16 matrix), unless the environment
+    // asks for tf32 operands (CHEBYKAN_NARROW_FWD=tf32, for A/B runs)
+    const bool half_plane = mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out) && !narrow_forward_tf32_operands();
+    const PackedDims p = packed_dims(in, out, deg, half_plane ? CHEBYKAN_MODE_BF16 : mode);
+    const char* plane = reinterpret_cast<const char*>(wt) + (half_plane ? tf32_half_plane_offset(in, out, deg) : 0);
+    const float* out_scale = half_plane ? reinterpret_cast<const float*>(plane) + 1 : nullptr;   // header: {max bits, 1/scale}
+    if (half_plane) plane += HALF_PLANE_HEADER;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
     const int bn = out <= 64 ? 64 : 128;
@@ -468,9 +501,10 @@ int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t i
         const cuuint64_t dims[2] = {(cuuint64_t)p.k_pad, (cuuint64_t)p.n_pad};
         const cuuint64_t strides[1] = {(cuuint64_t)(p.k_pad * p.elem)};
         const cuuint32_t box[2] = {(cuuint32_t)p.ib, (cuuint32_t)bn};
-        const CUtensorMapDataType dt = (mode == CHEBYKAN_MODE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                                    : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-        const CUresult r = encode(&tmap_w, dt, 2, const_cast<void*>(wt), dims, strides, box, estr,
+        const CUtensorMapDataType dt = half_plane ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                       : (mode == CHEBYKAN_MODE_BF16) ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                      : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        const CUresult r = encode(&tmap_w, dt, 2, const_cast<char*>(plane), dims, strides, box, estr,
                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
@@ -490,6 +524,10 @@ int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t i
 #ifdef TS_PROBE_VARIANTS
     TS_PROBE_VARIANTS
 #endif
+    if (half_plane) {
+        if (bn == 64) return launch_ts<TS_MODE_F16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, out_scale);
+        return launch_ts<TS_MODE_F16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, out_scale);
+    }
     if (mode == CHEBYKAN_MODE_BF16) {
         if (bn == 64) return launch_ts<CHEBYKAN_MODE_BF16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
         return launch_ts<CHEBYKAN_MODE_BF16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);

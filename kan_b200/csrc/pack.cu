@@ -2,6 +2,7 @@
 // operand layouts described in common.cuh.  Takes the place of the permute +
 // copy torch.einsum does before its bmm (reference kan/basis/chebyshev.py:101).
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "common.cuh"
 
 namespace chebykan {
@@ -40,6 +41,54 @@ pack_kernel(const float* __restrict__ c, void* __restrict__ packed, int in, int 
     }
 }
 
+// ---- the fp16 plane of the TF32 mode's narrow layers (layout in common.cuh) ----------------------------------
+__global__ void __launch_bounds__(256)
+coeff_absmax_kernel(const float* __restrict__ c, int64_t n, uint32_t* __restrict__ header) {
+    uint32_t m = 0u;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x)
+        m = max(m, __float_as_uint(fabsf(c[e])));      // a NaN's bit pattern beats every finite value: scaling is off then
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m != 0u) atomicMax(header, m);
+}
+
+__global__ void __launch_bounds__(256)
+pack_half_kernel(const float* __restrict__ c, uint32_t* __restrict__ header, __half* __restrict__ plane, int in, int out,
+                 int dp1, int ib, int64_t k_pad, int64_t n_pad) {
+    const float scale = half_scale_for(header[0]);
+    if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<float*>(header)[1] = 1.f / scale;
+    const int64_t total = k_pad * n_pad;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t n = e / k_pad, k = e % k_pad;
+        const int64_t blk = k / ((int64_t)ib * dp1);
+        const int64_t rem = k % ((int64_t)ib * dp1);
+        const int d = (int)(rem / ib);
+        const int64_t i = blk * ib + rem % ib;
+        float v = 0.f;
+        if (i < in && n < out) v = c[(i * out + n) * dp1 + d] * scale;
+        plane[e] = __float2half_rn(v);
+    }
+}
+
+static int launch_pack_half_plane(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, cudaStream_t s) {
+    const PackedDims p = packed_dims(in, out, deg, CHEBYKAN_MODE_BF16);
+    char* base = reinterpret_cast<char*>(packed) + tf32_half_plane_offset(in, out, deg);
+    uint32_t* header = reinterpret_cast<uint32_t*>(base);
+    int rc = check_cuda(cudaMemsetAsync(header, 0, HALF_PLANE_HEADER, s));
+    if (rc) return rc;
+    const int64_t n = in * out * (deg + 1);
+    int64_t blocks = ceil_div(n, 256);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    coeff_absmax_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, n, header);
+    if ((rc = check_cuda(cudaGetLastError()))) return rc;
+    const int64_t total = p.k_pad * p.n_pad;
+    blocks = ceil_div(total, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    pack_half_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, header, reinterpret_cast<__half*>(base + HALF_PLANE_HEADER),
+                                                    (int)in, (int)out, (int)deg + 1, (int)p.ib, p.k_pad, p.n_pad);
+    return check_cuda(cudaGetLastError());
+}
+
 int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, int mode,
                 cudaStream_t s) {
     const PackedDims p = packed_dims(in, out, deg, mode);
@@ -55,7 +104,10 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
         pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
     else
         pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
-    return check_cuda(cudaGetLastError());
+    int rc = check_cuda(cudaGetLastError());
+    if (rc == CHEBYKAN_OK && mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
+        rc = launch_pack_half_plane(coeffs, packed, in, out, deg, s);
+    return rc;
 }
 
 }  // namespace chebykan
