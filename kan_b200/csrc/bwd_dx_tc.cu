@@ -6,10 +6,11 @@
 // in TMEM and is folded with the derivative recurrence (T_d' = d U_{d-1}) by the epilogue.
 //
 //   A (dY):  K-major tile [128 rows][32 outputs] fp32 read as tf32, TMA, 128B swizzle.
-//   B (Wd):  packed coefficients Wd[(i,d)][out_pad] (slot = i*(deg+1)+d, outputs contiguous,
-//            rounded to tf32), K-major tile [256 slots][32 outputs], TMA, 128B swizzle.
+//   B (Wd):  packed coefficients Wd[(i,d)][out_pad], d = 1..deg (slot = i*deg + d-1: degree 0 has
+//            no derivative and takes no slot; outputs contiguous, rounded to tf32), K-major tile
+//            [256 slots][32 outputs], TMA, 128B swizzle.
 //   D (G):   128 x 256 fp32 in TMEM, two buffers: the epilogue of one tile overlaps the
-//            MMAs of the other.  A tile covers TI = 256/(deg+1) inputs with all their degrees.
+//            MMAs of the other.  A tile covers TI = 256/deg inputs with all their degrees.
 //   warp 0 TMA, warp 1 MMA, warps 2-17 epilogue (two groups of eight, one per accumulator; in a
 //   group two warps per TMEM lane quarter, each taking half of the tile's inputs, two inputs at a
 //   time; a thread owns one batch row).
@@ -85,17 +86,17 @@ __device__ __forceinline__ void tmem_ld1(uint32_t taddr, uint32_t& r) {
 // degree_factor = 0: plain C (other polynomial families: their P_d' comes whole from the differentiated recurrence).
 template <int PART>
 __global__ void __launch_bounds__(256)
-pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int dp1, int out_pad,
+pack_dx_kernel(const float* __restrict__ c, uint32_t* __restrict__ wd, int in, int out, int nd, int out_pad,
                int degree_factor) {
-    const int64_t total = (int64_t)in * dp1 * out_pad;
+    const int64_t total = (int64_t)in * nd * out_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
          e += (int64_t)gridDim.x * blockDim.x) {
         const int o = (int)(e % out_pad);
         const int64_t slot = e / out_pad;
-        const int64_t i = slot / dp1;
-        const int d = (int)(slot % dp1);
+        const int64_t i = slot / nd;
+        const int d = (int)(slot % nd) + 1;          // degree 0 has no slot: its derivative is zero
         float v = 0.f;
-        if (o < out) v = (degree_factor ? (float)d : 1.f) * c[(i * out + o) * dp1 + d];
+        if (o < out) v = (degree_factor ? (float)d : 1.f) * c[(i * out + o) * (nd + 1) + d];
         if (PART == 0) {
             uint32_t r;
             asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
@@ -119,7 +120,7 @@ dy_tail_kernel(const float* __restrict__ dy, float* __restrict__ lo, int64_t n) 
 
 // Running state of one input's fold: sum += U_{d-1}(t) G_d column by column, U advanced by its recurrence.
 struct DxFold {
-    float ua = 0.f, ub = -1.f, sum = 0.f, t2;
+    float ua = 1.f, ub = 0.f, sum = 0.f, t2;       // (U_0, U_{-1}): the first column is degree 1, weight U_0 = 1
     __device__ __forceinline__ explicit DxFold(float two_t) : t2(two_t) {}
     // two columns: sum += U_{d-1} G_d, advance U, twice (ua / ub swap roles)
     __device__ __forceinline__ void two(uint32_t g0, uint32_t g1) {
@@ -132,8 +133,7 @@ struct DxFold {
 };
 
 // The same for a table-driven family: sum += P_d'(u) G_d with P and P' carried side by side through the recurrence
-// and its derivative.  Entry 0 of the table (A = 0, B = 1, C = 0) with the start state P_{-1} = 1 makes column 0
-// (P_0 = 1, P_0' = 0) an ordinary step.
+// and its derivative, from degree 1 on (start state P_0 = 1, P_{-1} = 0, P_0' = 0).
 struct DxFoldTable {
     float p1 = 1.f, p2 = 0.f, d1 = 0.f, d2 = 0.f, sum = 0.f, u;
     __device__ __forceinline__ explicit DxFoldTable(float u_) : u(u_) {}
@@ -153,7 +153,7 @@ template <> struct DxTable<true> { using type = RecurrenceTable; };
 template <int CG, int BN, bool FAM>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
-             const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int dp1, int TI,
+             const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int nd, int TI,
              int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh,
              const __grid_constant__ typename DxTable<FAM>::type rec) {
     using L = DxSmem<CG, BN>;
@@ -217,7 +217,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             int64_t rb = rb_first; int it = it_first;
             for (int64_t tile = unit; tile < num_tiles && alive; tile += nunits) {
                 const int m0 = (int)(rb * (DX_BM * CG) + rank * DX_BM);
-                const int slot0 = it * TI * dp1;
+                const int slot0 = it * TI * nd;
                 rb += rb_step; it += it_step;
                 if (it >= i_tiles) { it -= i_tiles; ++rb; }
                 for (int kb = 0; kb < nkb; ++kb) {
@@ -337,39 +337,39 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     float old_a = 0.f, old_b = 0.f;
                     if (accumulate && row_ok) { old_a = dxrow[ii]; if (has_b) old_b = dxrow[ii + 1]; }
                     DxFoldTable fa(ua), fb(ub);
-                    const uint32_t col_a = taddr + (uint32_t)(ii * dp1);
-                    const uint32_t col_b = has_b ? col_a + (uint32_t)dp1 : col_a;
+                    const uint32_t col_a = taddr + (uint32_t)(ii * nd);
+                    const uint32_t col_b = has_b ? col_a + (uint32_t)nd : col_a;
                     int c = 0;
-                    for (; c + 16 <= dp1; c += 16) {
+                    for (; c + 16 <= nd; c += 16) {
                         uint32_t ra[16], rb[16];
                         tmem_ld16(col_a + c, ra); tmem_ld16(col_b + c, rb); tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                        for (int e = 0; e < 16; ++e) { fa.one(rec, c + e + 1, ra[e]); fb.one(rec, c + e + 1, rb[e]); }
                     }
-                    if ((dp1 - c) & 8) {
+                    if ((nd - c) & 8) {
                         uint32_t ra[8], rb[8];
                         tmem_ld8(col_a + c, ra); tmem_ld8(col_b + c, rb); tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                        for (int e = 0; e < 8; ++e) { fa.one(rec, c + e + 1, ra[e]); fb.one(rec, c + e + 1, rb[e]); }
                         c += 8;
                     }
-                    if ((dp1 - c) & 4) {
+                    if ((nd - c) & 4) {
                         uint32_t ra[4], rb[4];
                         tmem_ld4(col_a + c, ra); tmem_ld4(col_b + c, rb); tmem_ld_wait();
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) { fa.one(rec, c + e, ra[e]); fb.one(rec, c + e, rb[e]); }
+                        for (int e = 0; e < 4; ++e) { fa.one(rec, c + e + 1, ra[e]); fb.one(rec, c + e + 1, rb[e]); }
                         c += 4;
                     }
-                    if ((dp1 - c) & 2) {
+                    if ((nd - c) & 2) {
                         uint32_t ra[2], rb[2];
                         tmem_ld2(col_a + c, ra); tmem_ld2(col_b + c, rb); tmem_ld_wait();
-                        fa.one(rec, c, ra[0]); fb.one(rec, c, rb[0]); fa.one(rec, c + 1, ra[1]); fb.one(rec, c + 1, rb[1]);
+                        fa.one(rec, c + 1, ra[0]); fb.one(rec, c + 1, rb[0]); fa.one(rec, c + 2, ra[1]); fb.one(rec, c + 2, rb[1]);
                         c += 2;
                     }
-                    if ((dp1 - c) & 1) {
+                    if ((nd - c) & 1) {
                         uint32_t ra = 0u, rb = 0u;
                         tmem_ld1(col_a + c, ra); tmem_ld1(col_b + c, rb); tmem_ld_wait();
-                        fa.one(rec, c, ra); fb.one(rec, c, rb);
+                        fa.one(rec, c + 1, ra); fb.one(rec, c + 1, rb);
                     }
                     if (row_ok) {
                         const float va = dua * fa.sum;
@@ -391,13 +391,12 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 // per row: each of these loads is its own sector, and its latency would end the round otherwise)
                 float old_a = 0.f, old_b = 0.f;
                 if (accumulate && row_ok) { old_a = dxrow[ii]; if (has_b) old_b = dxrow[ii + 1]; }
-                // ua / ub alternate as (U_{d-1}, U_{d-2}); U_{-1} = 0, U_{-2} = -1 make U_0 = 1 and
-                // give the d = 0 column (whose coefficients are 0 * C) weight zero without a branch
+                // ua / ub alternate as (U_{d-1}, U_{d-2}), starting at degree 1
                 DxFold fa(2.f * ta), fb(2.f * tb);
-                const uint32_t col_a = taddr + (uint32_t)(ii * dp1);
-                const uint32_t col_b = has_b ? col_a + (uint32_t)dp1 : col_a;
+                const uint32_t col_a = taddr + (uint32_t)(ii * nd);
+                const uint32_t col_b = has_b ? col_a + (uint32_t)nd : col_a;
                 int c = 0;
-                for (; c + 32 <= dp1; c += 32) {
+                for (; c + 32 <= nd; c += 32) {
                     uint32_t ra[32], rb[32];
                     tmem_ld32(col_a + c, ra);
                     tmem_ld32(col_b + c, rb);
@@ -408,7 +407,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                 // the last 1-31 columns: loads of 16, 8, 4, 2 and 1 columns as the count's bits say, so that no lane
                 // touches a column past its input's last one; each size is loaded, awaited and folded in turn (few
                 // registers live at once; configurations whose time the epilogue sets have one or two bits set)
-                const int rem = dp1 - c;
+                const int rem = nd - c;
                 int cc = c;
                 if (rem & 16) {
                     uint32_t a[16], b[16];
@@ -499,7 +498,7 @@ int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, i
 namespace {
 template <int CG, int BN, bool FAM>
 int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
-                     int in, int out, int dp1, int32_t* status, cudaStream_t s, int accumulate, int exact_tanh,
+                     int in, int out, int nd, int32_t* status, cudaStream_t s, int accumulate, int exact_tanh,
                      const typename DxTable<FAM>::type& rec) {
     using L = DxSmem<CG, BN>;
     static bool attr_set[64] = {false};
@@ -513,7 +512,7 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     }
     int sms = 148;
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int TI = BN / dp1;
+    int TI = BN / nd;
     if (TI > in) TI = in;
     const int i_tiles = (int)ceil_div(in, TI);
     const int64_t num_tiles = ceil_div(B, DX_BM * CG) * i_tiles;
@@ -525,7 +524,7 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     attrs[0].id = cudaLaunchAttributeClusterDimension;
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
-    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, dp1, TI, i_tiles, num_tiles,
+    return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, nd, TI, i_tiles, num_tiles,
                                          status, accumulate, exact_tanh, rec));
 }
 }  // namespace
@@ -535,9 +534,12 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
                  const RecurrenceTable* rec) {
     if (rec != nullptr && x3) return CHEBYKAN_EUNSUPPORTED;
     const int degree_factor = rec == nullptr;
-    const int dp1 = (int)deg + 1;
+    // T_0' = 0 (P_0' = 0): degree 0 takes no slot of G.  A tile's 256 slots then hold 256 / deg inputs: 8 instead of
+    // 7 at degree 32 (one 32-column TMEM load per input, no remainder), 32 instead of 28 at degree 8.
+    const int nd = (int)deg;
+    if (nd == 0) return check_cuda(cudaMemsetAsync(dx, 0, B * in * 4, s));
     const int64_t out_pad = round_up(out, 32);
-    const int64_t slots = in * dp1;
+    const int64_t slots = in * nd;
     if (ws == nullptr || ws_bytes < dx_tc_workspace_bytes(B, in, out, deg, x3)) return CHEBYKAN_EWORKSPACE;
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
@@ -548,8 +550,8 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     {
         int64_t blocks = ceil_div(slots * out_pad, 256);
         if (blocks > 148 * 16) blocks = 148 * 16;
-        if (x3) pack_dx_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad, degree_factor);
-        else pack_dx_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, dp1, (int)out_pad, degree_factor);
+        if (x3) pack_dx_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, nd, (int)out_pad, degree_factor);
+        else pack_dx_kernel<0><<<(unsigned)blocks, 256, 0, s>>>(coeffs, wd_hi, (int)in, (int)out, nd, (int)out_pad, degree_factor);
         int rc = check_cuda(cudaGetLastError());
         if (rc) return rc;
         if (x3) {
@@ -584,11 +586,11 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     };
     auto run = [&](const CUtensorMap& mdy, const CUtensorMap& mw, int accumulate) -> int {
         if (rec != nullptr) {
-            if (cg == 2) return launch_dx_kernel<2, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, 0, *rec);
-            return launch_dx_kernel<1, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, 0, *rec);
+            if (cg == 2) return launch_dx_kernel<2, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, nd, status, s, accumulate, 0, *rec);
+            return launch_dx_kernel<1, DX_BN, true>(mdy, mw, x, dx, B, (int)in, (int)out, nd, status, s, accumulate, 0, *rec);
         }
-        if (cg == 2) return launch_dx_kernel<2, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3, DxNoTable());
-        return launch_dx_kernel<1, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, dp1, status, s, accumulate, x3, DxNoTable());
+        if (cg == 2) return launch_dx_kernel<2, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, nd, status, s, accumulate, x3, DxNoTable());
+        return launch_dx_kernel<1, DX_BN, false>(mdy, mw, x, dx, B, (int)in, (int)out, nd, status, s, accumulate, x3, DxNoTable());
     };
     CUtensorMap m_dy, m_w;
     int rc;
