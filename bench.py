@@ -763,7 +763,11 @@ def run_ours(args):
                          "unit": "TFLOP/s", "frac": achieved / peak,
                          "traffic": traffic["bytes"] if traffic else None, "traffic_source": traffic,
                          "algorithmic_bytes": B * 4.0 * (n_in + n_out) + n_in * n_out * (deg + 1) * (2 if mode == "bf16" else 4),
-                         "peak_note": peak_note, "flops_per_launch": flops, "per": "GPU"},
+                         "peak_note": peak_note, "flops_per_launch": flops, "per": "GPU",
+                         "flops_executed": flops if mode == "fp32" else flops * deg / (deg + 1),
+                         "flops_note": "achieved and frac count the layer's algorithmic FLOPs 2*B*in*(deg+1)*out; the "
+                                       "tensor-core kernels execute deg/(deg+1) of them: degree 0 of the basis is the "
+                                       "constant 1, so its term sum_i C[i,o,0] is a bias vector added in the epilogue"},
             "e2e": e2e if e2e else {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": args.steps,
             "clocks": clocks,

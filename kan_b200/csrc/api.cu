@@ -90,10 +90,7 @@ int chebykan_last_cuda_error(void) { return g_last_cuda_error; }
 
 int64_t chebykan_packed_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
     if (!shape_ok(0, in, out, deg) || !mode_ok(mode)) return CHEBYKAN_EINVAL;
-    const PackedDims p = packed_dims(in, out, deg, mode);
-    if (mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))     // narrow layers: the fp16 plane behind the tf32 matrix
-        return tf32_half_plane_offset(in, out, deg) + tf32_half_plane_bytes(in, out, deg);
-    return p.k_pad * p.n_pad * p.elem * p.planes;
+    return packed_total_bytes(in, out, deg, mode);
 }
 
 int chebykan_pack_coeffs(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg,
@@ -129,6 +126,8 @@ int chebykan_fwd(const float* x, const void* packed, float* y, int64_t B, int64_
         return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg,
                                (cudaStream_t)stream);
     if (!status) return CHEBYKAN_EINVAL;
+    // degree 0 in a tensor-core mode: y is the bias vector of the packed buffer in every row
+    if (deg == 0) return launch_bias_rows(packed, y, B, in, out, mode, (cudaStream_t)stream);
     if (fwd_ts_supported(B, in, out, deg, mode) && !narrow_forward_in_shared_memory())
         return launch_fwd_ts(x, reinterpret_cast<const void*>(packed), y, B, in, out, deg, mode, status, (cudaStream_t)stream);
     return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream);
@@ -139,6 +138,7 @@ int chebykan_fwd_ln(const float* x, const void* packed, float* y, int64_t B, int
                     const float* ln_beta, float ln_eps, float* ln_stats_out, int32_t* status, void* stream) {
     if (!shape_ok(B, in, out, deg) || !mode_ok(mode) || !packed || !status) return CHEBYKAN_EINVAL;
     if (fp32_backward(mode)) return CHEBYKAN_EUNSUPPORTED;   // fusion lives in the bf16 / tf32 tensor-core kernels
+    if (deg == 0) return CHEBYKAN_EUNSUPPORTED;               // a degree-0 layer is a constant: nothing to fuse into
     if (ln_stats_in && (!ln_gamma || !ln_beta)) return CHEBYKAN_EINVAL;
     if (B == 0) return CHEBYKAN_OK;
     if (!x || !y) return CHEBYKAN_EINVAL;

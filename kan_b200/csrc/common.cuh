@@ -28,12 +28,20 @@ constexpr int TC_NPAD = 128;
 struct PackedDims {
     int64_t ib;      // inputs per K block
     int64_t in_pad;  // inputs padded to a multiple of ib
-    int64_t k_pad;   // in_pad * (deg+1)
+    int64_t nd;      // degrees that take K slots (see below)
+    int64_t k_pad;   // in_pad * nd
     int64_t n_pad;   // padded outputs
     int64_t elem;    // bytes per element
     bool    k_major; // true: [N_pad][K_pad]; false: [K_pad][N_pad]
     int64_t planes;  // matrices stored back to back (FP32X3: tf32 head, then tf32 tail)
 };
+
+// Degree 0 of every basis here is the constant 1, so its part of y, sum_i C[i][o][0], does not depend on x.  The
+// tensor-core layouts leave it out of the GEMM (K covers degrees 1..deg: a ninth fewer MMAs at degree 8, a fifth
+// fewer at degree 4) and carry it as a bias vector bias[N_pad] behind the matrices, which the forward kernels'
+// epilogues add.  A layer of degree 0 is its bias alone (no matrix); the FP32 (FFMA) layout keeps all deg+1 degrees.
+inline __host__ __device__ bool packed_has_bias(int64_t deg, int mode) { (void)deg; return mode != CHEBYKAN_MODE_FP32; }
+inline __host__ __device__ int64_t packed_degrees(int64_t deg, int mode) { return packed_has_bias(deg, mode) ? deg : deg + 1; }
 
 inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64_t deg, int mode) {
     PackedDims p{};
@@ -46,7 +54,8 @@ inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64
     }
     p.planes = (mode == CHEBYKAN_MODE_FP32X3) ? 2 : 1;
     p.in_pad = round_up(in, p.ib);
-    p.k_pad = p.in_pad * (deg + 1);
+    p.nd = packed_degrees(deg, mode);
+    p.k_pad = p.in_pad * p.nd;
     return p;
 }
 
@@ -62,6 +71,20 @@ inline __host__ __device__ int64_t tf32_half_plane_offset(int64_t in, int64_t ou
 inline __host__ __device__ int64_t tf32_half_plane_bytes(int64_t in, int64_t out, int64_t deg) {
     const PackedDims p = packed_dims(in, out, deg, CHEBYKAN_MODE_BF16);
     return HALF_PLANE_HEADER + p.k_pad * p.n_pad * 2;
+}
+// whole packed buffer: matrices (TF32 narrow layers: tf32 matrix, then the fp16 plane), then the bias vector
+inline __host__ __device__ int64_t packed_matrix_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
+    const PackedDims p = packed_dims(in, out, deg, mode);
+    if (mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
+        return tf32_half_plane_offset(in, out, deg) + tf32_half_plane_bytes(in, out, deg);
+    return p.k_pad * p.n_pad * p.elem * p.planes;
+}
+inline __host__ __device__ int64_t packed_bias_offset(int64_t in, int64_t out, int64_t deg, int mode) {
+    return round_up(packed_matrix_bytes(in, out, deg, mode), 256);
+}
+inline __host__ __device__ int64_t packed_total_bytes(int64_t in, int64_t out, int64_t deg, int mode) {
+    if (!packed_has_bias(deg, mode)) return packed_matrix_bytes(in, out, deg, mode);
+    return packed_bias_offset(in, out, deg, mode) + packed_dims(in, out, deg, mode).n_pad * 4;
 }
 // power of two that puts `maxbits` (a non-negative float's bit pattern) into [2^14, 2^15); 1 for zero, inf and NaN
 __device__ __forceinline__ float half_scale_for(uint32_t maxbits) {
@@ -168,6 +191,8 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
 int launch_fwd_ffma(const float* x, const float* wf, float* y, int64_t B, int64_t in, int64_t out,
                     int64_t deg, cudaStream_t s, const RecurrenceTable* rec = nullptr);
 // `rec` != nullptr: another polynomial family (bf16 / tf32 modes, no LayerNorm fusion)
+// y[b][o] = bias[o] for every row: the whole forward of a degree-0 layer in the tensor-core modes
+int launch_bias_rows(const void* packed, float* y, int64_t B, int64_t in, int64_t out, int mode, cudaStream_t s);
 int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t in, int64_t out,
                   int64_t deg, int mode, int32_t* status, cudaStream_t s, const LnFusion& ln = LnFusion(),
                   const RecurrenceTable* rec = nullptr);

@@ -117,6 +117,7 @@ int chebykan_family_fwd(const chebykan_family* family, const float* x, const voi
         return launch_fwd_ffma(x, reinterpret_cast<const float*>(packed), y, B, in, out, deg, (cudaStream_t)stream, &t);
     // bf16 / tf32: the tcgen05 kernel of the Chebyshev layer with the table-driven recurrence in its producer warps
     if (!status) return CHEBYKAN_EINVAL;
+    if (deg == 0) return launch_bias_rows(packed, y, B, in, out, mode, (cudaStream_t)stream);     // P_0 = 1 in every family
     return launch_fwd_tc(x, packed, y, B, in, out, deg, mode, status, (cudaStream_t)stream, LnFusion(), &t);
 }
 

@@ -105,8 +105,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               int use_x_tma, const float* __restrict__ x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
-              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad,
+              int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad, const float* __restrict__ bias,
               const __grid_constant__ typename VariantTable<VAR>::type rec) {
+    // `dp1` counts the degrees that take K slots: degrees 1..deg.  Degree 0, the constant 1, is the bias vector the
+    // epilogue adds (a layer of degree 0 never gets here: its output is the bias alone).
     constexpr bool LN = VAR == VAR_LN;
     constexpr bool FAM = VAR == VAR_FAMILY;
     constexpr bool X3 = MODE == CHEBYKAN_MODE_FP32X3;
@@ -339,11 +341,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     for (int e = 0; e < CH; ++e) {
                         float t = X3 ? tanhf(v[e]) : tanh_fast(v[e]);
                         if constexpr (FAM) {
-                            // the family's normalised input u, P_0 = 1 and P_{-1} = 0
+                            // the family's normalised input u; first emitted degree in ta, the one before it in tb: (P_1, P_0)
                             t = rec.affine ? fmaf(rec.scale, v[e] - rec.shift, rec.offset) : rec.scale * t;
-                            tt[j][e] = t; ta[j][e] = 1.f; tb[j][e] = 0.f;
+                            tt[j][e] = t;
+                            ta[j][e] = fmaf(rec.A[1], t, rec.B[1]);
+                            tb[j][e] = 1.f;
                         } else {
-                            tt[j][e] = 2.f * t; ta[j][e] = 1.f; tb[j][e] = t;   // T_0 = 1, T_{-1} = T_1 = t
+                            tt[j][e] = 2.f * t; ta[j][e] = t; tb[j][e] = 1.f;      // (T_1, T_0)
                         }
                         finite = finite && (t == t);
                     }
@@ -358,12 +362,13 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     if (lane == 0) mbar_arrive(x_empty_bar);
                     x_held = false;
                 };
-                // degree 0: T_0 = 1 (ta); then degrees alternate between tb and ta
+                // degree 1 (ta); then degrees alternate between tb and ta.  K slot d holds degree d + 1.
+                constexpr int sh = 1;
                 if (!emit(ta)) { alive = false; break; }
-                if (x_held && dp1 == 1) release_x();      // degree 0 only: the tile's values are never used
+                if (x_held && dp1 == 1) release_x();      // a single degree: nothing else reads the tile
                 for (int d = 1; d < dp1; d += 2) {
                     if constexpr (FAM) {
-                        const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];   // P_d = (A u + B) P_{d-1} - C P_{d-2}
+                        const float ra = rec.A[d + sh], rb = rec.B[d + sh], rc = rec.C[d + sh];   // P_d = (A u + B) P_{d-1} - C P_{d-2}
 #pragma unroll
                         for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -379,7 +384,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     if (x_held) release_x();
                     if (d + 1 < dp1) {
                         if constexpr (FAM) {
-                            const float ra = rec.A[d + 1], rb = rec.B[d + 1], rc = rec.C[d + 1];
+                            const float ra = rec.A[d + 1 + sh], rb = rec.B[d + 1 + sh], rc = rec.C[d + 1 + sh];
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
 #pragma unroll
@@ -548,6 +553,14 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         // one row's 32 consecutive outputs from registers to y
         float ln_s1 = 0.f, ln_s2 = 0.f;    // this row's sum and sum of squares over the tile (fused LayerNorm)
         auto store32 = [&](uint32_t (&r)[32], int64_t row, int col0, bool add) {
+            if (!add) {
+                // degree 0's part of y, the same for every row: lane l fetches bias[col0 + l] (the vector is padded to
+                // the tile grid) and the warp passes the values round, one register instead of thirty-two
+                const float bl = __ldg(bias + col0 + lane);
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                    r[e] = __float_as_uint(__uint_as_float(r[e]) + __shfl_sync(0xffffffffu, bl, e));
+            }
             if (row >= B) return;
             if (X3 && add) {
                 // later chunk of the K range: y already holds the earlier chunks' sum
@@ -663,7 +676,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 template <int MODE, int BN, int NSUB, int VAR, int CG>
 int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
-               const typename VariantTable<VAR>::type& rec) {
+               const float* bias, const typename VariantTable<VAR>::type& rec) {
     using L = Smem<BN, NSUB, CG, (MODE == CHEBYKAN_MODE_FP32X3) ? 2 : 1>;
     static bool attr_set[64] = {false};
     static int max_units[64] = {0};       // CTAs (or CTA pairs) that can be resident at once
@@ -702,7 +715,7 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_tiles,
-                                         num_tiles, status, ln, n_pad, rec));
+                                         num_tiles, status, ln, n_pad, bias, rec));
 }
 
 // the LayerNorm-fused and the family variants are separate instantiations, so the plain kernel carries none of
@@ -710,25 +723,25 @@ int launch_one_ln(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
 template <int MODE, int BN, int NSUB, int CG = 1>
 int launch_one(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma, const float* x, float* y,
                int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
-               const RecurrenceTable* rec) {
+               const float* bias, const RecurrenceTable* rec) {
     if constexpr (MODE != CHEBYKAN_MODE_FP32X3) {   // neither LayerNorm fusion nor families in the FP32X3 mode (the entry points refuse)
         if (rec != nullptr)
-            return launch_one_ln<MODE, BN, NSUB, VAR_FAMILY, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, *rec);
+            return launch_one_ln<MODE, BN, NSUB, VAR_FAMILY, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, *rec);
         if (ln.stats_in != nullptr || ln.stats_out != nullptr)
-            return launch_one_ln<MODE, BN, NSUB, VAR_LN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, NoTable());
+            return launch_one_ln<MODE, BN, NSUB, VAR_LN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, NoTable());
     }
-    return launch_one_ln<MODE, BN, NSUB, VAR_PLAIN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, NoTable());
+    return launch_one_ln<MODE, BN, NSUB, VAR_PLAIN, CG>(tmap, tmap_x, use_x_tma, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, NoTable());
 }
 
 template <int MODE>
 int launch_mode(const CUtensorMap& tmap, const CUtensorMap& tmx, int xt, int bn, int nsub, int cg, const float* x, float* y,
                 int64_t B, int in, int out, int dp1, int n_pad, int32_t* status, cudaStream_t s, const LnFusion& ln,
-                const RecurrenceTable* rec) {
-    if (bn == 64) return launch_one<MODE, 64, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
-    if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
-    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
-    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
-    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, rec);
+                const float* bias, const RecurrenceTable* rec) {
+    if (bn == 64) return launch_one<MODE, 64, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, rec);
+    if (bn == 256 && nsub == 2 && cg == 2) return launch_one<MODE, 256, 2, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, rec);
+    if (bn == 256 && nsub == 2) return launch_one<MODE, 256, 2>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, rec);
+    if (bn == 256) return launch_one<MODE, 256, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, rec);
+    return launch_one<MODE, 128, 1>(tmap, tmx, xt, x, y, B, in, out, dp1, n_pad, status, s, ln, bias, rec);
 }
 
 }  // namespace
@@ -771,15 +784,18 @@ int launch_fwd_tc(const float* x, const void* wt, float* y, int64_t B, int64_t i
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (rx != CUDA_SUCCESS) { set_last_cuda_error((int)rx); return CHEBYKAN_ECUDA; }
     }
-    const int dp1 = (int)deg + 1;
+    // degrees that take K slots, and degree 0 as the bias vector behind the matrices (see packed_degrees)
+    const int dp1 = (int)p.nd;
+    const float* bias = reinterpret_cast<const float*>(reinterpret_cast<const char*>(wt) + packed_bias_offset(in, out, deg, mode));
+    if (deg == 0) return CHEBYKAN_EUNSUPPORTED;      // the bias alone: the entry points broadcast it (launch_bias_rows)
     if (mode == CHEBYKAN_MODE_FP32X3)
         return launch_mode<CHEBYKAN_MODE_FP32X3>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                                 (int)p.n_pad, status, s, ln, rec);
+                                                 (int)p.n_pad, status, s, ln, bias, rec);
     if (mode == CHEBYKAN_MODE_BF16)
         return launch_mode<CHEBYKAN_MODE_BF16>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                               (int)p.n_pad, status, s, ln, rec);
+                                               (int)p.n_pad, status, s, ln, bias, rec);
     return launch_mode<CHEBYKAN_MODE_TF32>(tmap, tmap_x, use_x_tma, bn, nsub, cg, x, y, B, (int)in, (int)out, dp1,
-                                           (int)p.n_pad, status, s, ln, rec);
+                                           (int)p.n_pad, status, s, ln, bias, rec);
 }
 
 }  // namespace chebykan

@@ -112,7 +112,9 @@ template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 __global__ void __launch_bounds__(TsCfg<MODE, BN, NSUBM_, KP_, NACC_>::NUM_THREADS, 1)
 fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int64_t num_tiles, int32_t* status,
-              const float* __restrict__ out_scale) {
+              const float* __restrict__ out_scale, const float* __restrict__ bias) {
+    // `dp1` counts the degrees that take K slots: degrees 1..deg (K slot d holds T_{d+1}).  Degree 0, the constant 1,
+    // is the bias vector the epilogue adds.
     using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     constexpr int NSUBM = C::NSUBM, KP = C::KP, NSTG = C::NSTG, NSB = C::NSB, NACC = C::NACC, NXS = C::NXS;
     constexpr int IB = C::IB, EPT = C::EPT;
@@ -224,7 +226,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     for (int e = 0; e < 4; ++e) {
                         const float t = tanh_fast(vv[e]);
                         finite = finite && (t == t);
-                        tt[4 * c + e] = 2.f * t; ta[4 * c + e] = 1.f; tb[4 * c + e] = t;   // T_0 = 1, T_1 = t
+                        tt[4 * c + e] = 2.f * t; ta[4 * c + e] = t; tb[4 * c + e] = fmaf(2.f * t, t, -1.f);   // T_1, T_2
                     }
                 }
                 inc = finite ? TF32_HALF_ULP : 0u;
@@ -237,12 +239,12 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     }
                     const uint32_t st0 = lane_addr + A_COL0 + (uint32_t)((sub * NSTG + s) * KP * 32 + h * 16);
                     if (d0 == 0) {
-                        emit(st0, ta);                                     // degree 0
+                        emit(st0, ta);                                     // the block's first degree (T_1)
                         // the x slot goes back after a store whose data derives from it has been issued (an mbarrier
                         // arrive does not wait for this thread's outstanding ld.shared, the store does)
                         __syncwarp();
                         if (lane == 0) mbar_arrive(x_empty(sub, xs));
-                        if (1 < np) emit(st0 + 32, tb);                    // degree 1
+                        if (1 < np) emit(st0 + 32, tb);                    // T_2
                     } else {
 #pragma unroll
                         for (int e = 0; e < EPT; ++e) ta[e] = fmaf(tt[e], tb[e], -ta[e]);
@@ -405,9 +407,15 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     uint32_t rg[16];
                     tmem_ld16(taddr + ch * 16, rg);
                     tmem_ld_wait();
-                    if (MODE == TS_MODE_F16) {
+                    {
+                        // degree 0's part of y: lane l fetches bias[16 ch + (l & 15)] (the vector is padded to 128
+                        // outputs) and the warp passes the values round
+                        const float bl = __ldg(bias + ch * 16 + (lane & 15));
 #pragma unroll
-                        for (int e = 0; e < 16; ++e) rg[e] = __float_as_uint(__uint_as_float(rg[e]) * osc);
+                        for (int e = 0; e < 16; ++e) {
+                            const float v = __uint_as_float(rg[e]);
+                            rg[e] = __float_as_uint(fmaf(v, osc, __shfl_sync(0xffffffffu, bl, e)));
+                        }
                     }
                     if (row < B) {
                         float* dst = y + row * out + ch * 16;
@@ -444,7 +452,7 @@ fwd_ts_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
 
 template <int MODE, int BN, int NSUBM_, int KP_, int NACC_>
 int launch_ts(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, float* y, int64_t B, int in, int out, int dp1,
-              int32_t* status, cudaStream_t s, const float* out_scale = nullptr) {
+              int32_t* status, cudaStream_t s, const float* bias, const float* out_scale = nullptr) {
     using C = TsCfg<MODE, BN, NSUBM_, KP_, NACC_>;
     static bool attr_set[64] = {false};
     static int sms[64] = {0};
@@ -462,7 +470,7 @@ int launch_ts(const CUtensorMap& tmap_w, const CUtensorMap& tmap_x, float* y, in
     }
     const int64_t num_tiles = ceil_div(B, 128 * C::NSUBM);
     const unsigned grid = (unsigned)(num_tiles < sms[dev] ? num_tiles : sms[dev]);
-    kernel<<<grid, C::NUM_THREADS, C::TOTAL, s>>>(tmap_w, tmap_x, y, B, in, out, dp1, num_tiles, status, out_scale);
+    kernel<<<grid, C::NUM_THREADS, C::TOTAL, s>>>(tmap_w, tmap_x, y, B, in, out, dp1, num_tiles, status, out_scale, bias);
     return check_cuda(cudaGetLastError());
 }
 
@@ -478,8 +486,7 @@ static bool narrow_forward_tf32_operands() {
 
 // narrow layers in the plain tf32 / bf16 modes whose x rows are TMA-addressable
 bool fwd_ts_supported(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
-    (void)deg;
-    return (mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16) && out <= 128 && (in % 4) == 0 && B >= 1 &&
+    return (mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16) && out <= 128 && (in % 4) == 0 && B >= 1 && deg >= 1 &&
            B <= (int64_t)0x7fffffff - 512;
 }
 
@@ -520,20 +527,21 @@ int launch_fwd_ts(const float* x, const void* wt, float* y, int64_t B, int64_t i
                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
     }
-    const int dp1 = (int)deg + 1;
+    const int dp1 = (int)p.nd;        // degrees 1..deg take K slots; degree 0 is the bias vector behind the matrices
+    const float* bias = reinterpret_cast<const float*>(reinterpret_cast<const char*>(wt) + packed_bias_offset(in, out, deg, mode));
 #ifdef TS_PROBE_VARIANTS
     TS_PROBE_VARIANTS
 #endif
     if (half_plane) {
-        if (bn == 64) return launch_ts<TS_MODE_F16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, out_scale);
-        return launch_ts<TS_MODE_F16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, out_scale);
+        if (bn == 64) return launch_ts<TS_MODE_F16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias, out_scale);
+        return launch_ts<TS_MODE_F16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias, out_scale);
     }
     if (mode == CHEBYKAN_MODE_BF16) {
-        if (bn == 64) return launch_ts<CHEBYKAN_MODE_BF16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
-        return launch_ts<CHEBYKAN_MODE_BF16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+        if (bn == 64) return launch_ts<CHEBYKAN_MODE_BF16, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias);
+        return launch_ts<CHEBYKAN_MODE_BF16, 128, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias);
     }
-    if (bn == 64) return launch_ts<CHEBYKAN_MODE_TF32, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
-    return launch_ts<CHEBYKAN_MODE_TF32, 128, 1, 4, 1>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s);
+    if (bn == 64) return launch_ts<CHEBYKAN_MODE_TF32, 64, 1, 4, 2>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias);
+    return launch_ts<CHEBYKAN_MODE_TF32, 128, 1, 4, 1>(tmap_w, tmap_x, y, B, (int)in, (int)out, dp1, status, s, bias);
 }
 
 }  // namespace chebykan

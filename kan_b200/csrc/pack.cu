@@ -10,16 +10,17 @@ namespace chebykan {
 template <int MODE>
 __global__ void __launch_bounds__(256)
 pack_kernel(const float* __restrict__ c, void* __restrict__ packed, int in, int out, int dp1,
-            int ib, int64_t k_pad, int64_t n_pad) {
+            int ib, int64_t k_pad, int64_t n_pad, int nd) {
     const int64_t total = k_pad * n_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
          e += (int64_t)gridDim.x * blockDim.x) {
         int64_t k, n;
         if (MODE == CHEBYKAN_MODE_FP32) { k = e / n_pad; n = e % n_pad; }
         else                            { n = e / k_pad; k = e % k_pad; }
-        const int64_t blk = k / ((int64_t)ib * dp1);
-        const int64_t rem = k % ((int64_t)ib * dp1);
-        const int d = (int)(rem / ib);
+        // nd degrees take K slots: all dp1 of them, or degrees 1..deg when degree 0 travels as the bias vector
+        const int64_t blk = k / ((int64_t)ib * nd);
+        const int64_t rem = k % ((int64_t)ib * nd);
+        const int d = (int)(rem / ib) + (dp1 - nd);
         const int64_t i = blk * ib + rem % ib;
         float v = 0.f;
         if (i < in && n < out) v = c[(i * out + n) * dp1 + d];
@@ -54,20 +55,42 @@ coeff_absmax_kernel(const float* __restrict__ c, int64_t n, uint32_t* __restrict
 
 __global__ void __launch_bounds__(256)
 pack_half_kernel(const float* __restrict__ c, uint32_t* __restrict__ header, __half* __restrict__ plane, int in, int out,
-                 int dp1, int ib, int64_t k_pad, int64_t n_pad) {
+                 int dp1, int ib, int64_t k_pad, int64_t n_pad, int nd) {
     const float scale = half_scale_for(header[0]);
     if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<float*>(header)[1] = 1.f / scale;
     const int64_t total = k_pad * n_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = e / k_pad, k = e % k_pad;
-        const int64_t blk = k / ((int64_t)ib * dp1);
-        const int64_t rem = k % ((int64_t)ib * dp1);
-        const int d = (int)(rem / ib);
+        const int64_t blk = k / ((int64_t)ib * nd);
+        const int64_t rem = k % ((int64_t)ib * nd);
+        const int d = (int)(rem / ib) + (dp1 - nd);
         const int64_t i = blk * ib + rem % ib;
         float v = 0.f;
         if (i < in && n < out) v = c[(i * out + n) * dp1 + d] * scale;
         plane[e] = __float2half_rn(v);
     }
+}
+
+// bias[n] = sum_i C[i][n][0], each term rounded as the mode stores coefficients (bf16 / tf32; exact in the
+// three-product mode); one warp per output, lanes stride over the inputs, fixed-order tree: bitwise repeatable.
+template <int MODE>
+__global__ void __launch_bounds__(256)
+pack_bias_kernel(const float* __restrict__ c, float* __restrict__ bias, int in, int out, int dp1, int64_t n_pad) {
+    const int64_t n = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (n >= n_pad) return;
+    float s = 0.f;
+    if (n < out) {
+        for (int i = lane; i < in; i += 32) {
+            float v = c[((int64_t)i * out + n) * dp1];
+            if (MODE == CHEBYKAN_MODE_BF16) v = __bfloat162float(__float2bfloat16_rn(v));
+            else if (MODE == CHEBYKAN_MODE_TF32) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v)); v = __uint_as_float(r); }
+            s += v;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) bias[n] = s;
 }
 
 static int launch_pack_half_plane(const float* coeffs, void* packed, int64_t in, int64_t out, int64_t deg, cudaStream_t s) {
@@ -85,7 +108,7 @@ static int launch_pack_half_plane(const float* coeffs, void* packed, int64_t in,
     blocks = ceil_div(total, 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     pack_half_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, header, reinterpret_cast<__half*>(base + HALF_PLANE_HEADER),
-                                                    (int)in, (int)out, (int)deg + 1, (int)p.ib, p.k_pad, p.n_pad);
+                                                    (int)in, (int)out, (int)deg + 1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
     return check_cuda(cudaGetLastError());
 }
 
@@ -96,18 +119,42 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
     int64_t blocks = ceil_div(total, 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     const int dp1 = (int)deg + 1;
-    if (mode == CHEBYKAN_MODE_FP32)
-        pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+    if (total == 0) { /* degree 0 in a tensor-core mode: the bias alone */ }
+    else if (mode == CHEBYKAN_MODE_FP32)
+        pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
     else if (mode == CHEBYKAN_MODE_FP32X3)
-        pack_kernel<CHEBYKAN_MODE_FP32X3><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+        pack_kernel<CHEBYKAN_MODE_FP32X3><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
     else if (mode == CHEBYKAN_MODE_TF32)
-        pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+        pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
     else
-        pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad);
+        pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
     int rc = check_cuda(cudaGetLastError());
-    if (rc == CHEBYKAN_OK && mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
+    if (rc == CHEBYKAN_OK && total > 0 && mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
         rc = launch_pack_half_plane(coeffs, packed, in, out, deg, s);
+    if (rc == CHEBYKAN_OK && packed_has_bias(deg, mode)) {
+        float* bias = reinterpret_cast<float*>(reinterpret_cast<char*>(packed) + packed_bias_offset(in, out, deg, mode));
+        const unsigned bb = (unsigned)ceil_div(p.n_pad * 32, 256);
+        if (mode == CHEBYKAN_MODE_BF16) pack_bias_kernel<CHEBYKAN_MODE_BF16><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
+        else if (mode == CHEBYKAN_MODE_TF32) pack_bias_kernel<CHEBYKAN_MODE_TF32><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
+        else pack_bias_kernel<CHEBYKAN_MODE_FP32X3><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
+        rc = check_cuda(cudaGetLastError());
+    }
     return rc;
+}
+
+__global__ void __launch_bounds__(256)
+bias_rows_kernel(const float* __restrict__ bias, float* __restrict__ y, int64_t B, int out) {
+    const int64_t n = B * out;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x)
+        y[e] = bias[e % out];
+}
+
+int launch_bias_rows(const void* packed, float* y, int64_t B, int64_t in, int64_t out, int mode, cudaStream_t s) {
+    const float* bias = reinterpret_cast<const float*>(reinterpret_cast<const char*>(packed) + packed_bias_offset(in, out, 0, mode));
+    int64_t blocks = ceil_div(B * out, 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    bias_rows_kernel<<<(unsigned)blocks, 256, 0, s>>>(bias, y, B, (int)out);
+    return check_cuda(cudaGetLastError());
 }
 
 }  // namespace chebykan
