@@ -87,7 +87,7 @@ template <int BN, int CG, bool FAM>
 __global__ void __launch_bounds__(DC_THREADS, 1)
 dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_x,
                  int use_x_tma, int x_box_w, int nxs, int x_slot_bytes, const float* __restrict__ x,
-                 float* __restrict__ dst, int64_t B, int in, int out, int dp1, int TI, int i_tiles,
+                 float* __restrict__ dst, int64_t B, int in, int out, int dp1, int nd, int TI, int i_tiles,
                  int n_tiles, int64_t rows_per_split, int64_t split_stride, int add_to_dst,
                  int32_t* status, int part, int exact_tanh,
                  const __grid_constant__ typename DcTable<FAM>::type rec) {
@@ -229,18 +229,18 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     for (int e = 0; e < 4; ++e) {
                         float t = exact_tanh ? tanhf(xc[r][e]) : tanh_fast(xc[r][e]);
                         if constexpr (FAM) {
-                            // the family's normalised input u; P_0 = 1, P_{-1} = 0
+                            // the family's normalised input u
                             t = rec.affine ? fmaf(rec.scale, xc[r][e] - rec.shift, rec.offset) : rec.scale * t;
-                            t2[e] = t; ta[e] = 1.f; tb[e] = 0.f;
+                            t2[e] = t; ta[e] = fmaf(rec.A[1], t, rec.B[1]); tb[e] = 1.f;       // (P_1, P_0)
                         } else {
-                            t2[e] = 2.f * t; ta[e] = 1.f; tb[e] = t;     // T_0 = 1, T_{-1} = T_1 = t
+                            t2[e] = 2.f * t; ta[e] = t; tb[e] = 1.f;     // (T_1, T_0): slots start at degree 1
                         }
                         finite = finite && (t == t);
                     }
-                    // degree d from the two before it: into tb from (ta, tb), or into ta from (tb, ta)
+                    // slot d (degree d + 1) from the two before it: into tb from (ta, tb), or into ta from (tb, ta)
                     auto next_b = [&](int d) {
                         if constexpr (FAM) {
-                            const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];
+                            const float ra = rec.A[d + 1], rb = rec.B[d + 1], rc = rec.C[d + 1];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) tb[e] = fmaf(fmaf(ra, t2[e], rb), ta[e], -(rc * tb[e]));
                         } else {
@@ -250,7 +250,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     };
                     auto next_a = [&](int d) {
                         if constexpr (FAM) {
-                            const float ra = rec.A[d], rb = rec.B[d], rc = rec.C[d];
+                            const float ra = rec.A[d + 1], rb = rec.B[d + 1], rc = rec.C[d + 1];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) ta[e] = fmaf(fmaf(ra, t2[e], rb), tb[e], -(rc * ta[e]));
                         } else {
@@ -263,7 +263,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                     // Slot `row` lives in M tile row / 128 at row % 128 (tiles are 16 KB apart): its chunk c sits
                     // at lin = a_stage + row * 128 + c * 16 with the 16-byte chunk index XORed by row % 8, and
                     // since a_stage is 1024-byte aligned, row % 8 is bits 7-9 of lin itself.
-                    uint32_t lin = a_stage + (uint32_t)(ii * dp1) * 128u + ((uint32_t)c << 4);
+                    uint32_t lin = a_stage + (uint32_t)(ii * nd) * 128u + ((uint32_t)c << 4);
                     auto store4 = [&](const float (&v)[4]) {
                         uint32_t w[4];
 #pragma unroll
@@ -279,11 +279,11 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                                      ::"r"(dsta), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
                         lin += 128u;
                     };
-                    store4(ta);                                        // degree 0
+                    store4(ta);                                        // degree 1
                     int d = 1;
                     // eight degrees per trip: the loop's branches, not its arithmetic, were what the
                     // producers waited on
-                    for (; d + 7 < dp1; d += 8) {
+                    for (; d + 7 < nd; d += 8) {
 #pragma unroll
                         for (int h = 0; h < 4; ++h) {
                             next_b(d + 2 * h);
@@ -292,10 +292,10 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                             store4(ta);
                         }
                     }
-                    for (; d < dp1; d += 2) {
+                    for (; d < nd; d += 2) {
                         next_b(d);
                         store4(tb);
-                        if (d + 1 < dp1) {
+                        if (d + 1 < nd) {
                             next_a(d + 1);
                             store4(ta);
                         }
@@ -371,7 +371,7 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
             const uint64_t b_desc0 = make_smem_desc_mn(smem_base + L::A_STAGE);
             const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
             // slots of the pair: the odd CTA's tile may hold fewer (or no) inputs, its MMAs run all the same
-            const int mt_used = (ti * dp1 + 127) / 128;       // M tiles past the CTA's last slot stay unused
+            const int mt_used = (ti * nd + 127) / 128;       // M tiles past the CTA's last slot stay unused
             int nsub_used = 1;                                // 256-wide halves that hold real outputs
             for (int sub = 1; sub < L::NSUB; ++sub)
                 if (n0 + sub * L::BNI < out) nsub_used = sub + 1;
@@ -432,10 +432,10 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
             tc_fence_after();
 #pragma unroll 1
             for (int mt = 0; mt < L::MT; ++mt) {
-                if (mt * 128 >= ti * dp1) break;
+                if (mt * 128 >= ti * nd) break;
                 const int kk = mt * 128 + warp * 32 + lane;      // slot: M tile mt, TMEM lane warp*32+lane
-                const bool valid = kk < ti * dp1;
-                const int ii = kk / dp1, d = kk % dp1;
+                const bool valid = kk < ti * nd;
+                const int ii = kk / nd, d = kk % nd + 1;         // slots are degrees 1..deg; degree 0 is dY's column sums
                 float* base = dst + (int64_t)split * split_stride + ((int64_t)(i0 + ii) * out) * dp1 + d;
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 32) {
@@ -456,6 +456,9 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
                                 float* q = base + (int64_t)col * dp1;
                                 const float v = __uint_as_float(r[e]);
                                 *q = add_to_dst ? (*q + v) : v;
+                                // the degree-0 entry next to degree 1: cleared unless the destination accumulates,
+                                // filled from the column sums of dY after the reduction
+                                if (d == 1 && !add_to_dst) q[-1] = 0.f;
                             }
                         }
                     }
@@ -477,11 +480,52 @@ dcoeff_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_const
     }
 }
 
+// ---- degree 0 ---------------------------------------------------------------------------------------------
+// T_0 = 1 (P_0 = 1), so dC[i][o][0] = sum_b dY[b][o] for every input i: no part of the GEMM.  Two small kernels:
+// partial column sums per block of DC_CS_ROWS rows (a thread per column group walks its rows in order), then one
+// warp per output adds the blocks' partials in a fixed order and writes the value to all inputs.
+constexpr int DC_CS_ROWS = 2048;
+__global__ void __launch_bounds__(256)
+dy_colsum_kernel(const float* __restrict__ dy, float* __restrict__ part, int64_t B, int out) {
+    // 32 columns x 8 row lanes per block; grid (column groups, row blocks)
+    __shared__ float red[8][33];
+    const int col = blockIdx.x * 32 + (threadIdx.x & 31), rl = threadIdx.x >> 5;
+    const int64_t b0 = (int64_t)blockIdx.y * DC_CS_ROWS;
+    const int64_t b1 = min(B, b0 + DC_CS_ROWS);
+    float s = 0.f;
+    if (col < out)
+        for (int64_t b = b0 + rl; b < b1; b += 8) s += dy[b * out + col];
+    red[rl][threadIdx.x & 31] = s;
+    __syncthreads();
+    if (rl == 0 && col < out) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += red[k][threadIdx.x & 31];
+        part[(int64_t)blockIdx.y * out + col] = t;
+    }
+}
+__global__ void __launch_bounds__(256)
+degree0_fill_kernel(const float* __restrict__ part, int64_t nblocks, float* __restrict__ dc, int in, int out, int dp1,
+                    int accumulate) {
+    const int o = (int)((blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5);
+    const int lane = threadIdx.x & 31;
+    if (o >= out) return;
+    float sum = 0.f;
+    for (int64_t k = lane; k < nblocks; k += 32) sum += part[k * out + o];
+#pragma unroll
+    for (int w = 16; w > 0; w >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+    for (int i = lane; i < in; i += 32) {
+        float* q = dc + ((int64_t)i * out + o) * dp1;
+        *q = accumulate ? *q + sum : sum;
+    }
+}
+static int64_t dc_colsum_bytes(int64_t B, int64_t out) { return round_up(ceil_div(B, DC_CS_ROWS) * out * 4, 256); }
+
 // inputs per CTA: as many as fit the CTA's MT*128 slots, the x tile buffer and the producers' registers
-int dc_tile_inputs(int64_t in, int dp1, int bn) {
+int dc_tile_inputs(int64_t in, int nd, int bn) {
     const int mt = bn == 64 ? 4 : (bn == 128 ? 2 : 1);
     const int g = (bn == 64 || bn == 512) ? 4 : 2;         // producer warps per stage (8 / NS)
-    int ti = mt * 128 / dp1;
+    int ti = mt * 128 / nd;               // slots: degrees 1..deg of TI inputs
     if (ti > DC_MAX_TI) ti = DC_MAX_TI;
     if (ti * 8 > 32 * g * DC_MAX_ROUNDS) ti = 4 * g * DC_MAX_ROUNDS;
     if (ti > in) ti = (int)in;
@@ -498,7 +542,7 @@ DcTcPlan dc_tc_plan(int64_t B, int64_t in, int64_t out, int64_t deg, int x3 = 0)
     DcTcPlan p{};
     const int dp1 = (int)deg + 1;
     p.bn = out <= 64 ? 64 : (out <= 128 ? 128 : (out <= 256 ? 256 : 512));
-    p.TI = dc_tile_inputs(in, dp1, p.bn);
+    p.TI = dc_tile_inputs(in, (int)deg, p.bn);
     p.i_tiles = (int)ceil_div(in, p.TI);
     // wide layers run as CTA pairs over neighbouring input tiles (an odd count gets one empty tile)
     p.cg = (p.bn == 512 && p.i_tiles >= 2) ? 2 : 1;
@@ -552,7 +596,7 @@ int launch_dc_fam(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap, tmap_x, use_x_tma, x_box_w, nxs, x_slot_bytes, x, dst, B, in,
-                                         out, dp1, p.TI, p.i_tiles, p.n_tiles, p.rows_per_split, split_stride, add,
+                                         out, dp1, dp1 - 1, p.TI, p.i_tiles, p.n_tiles, p.rows_per_split, split_stride, add,
                                          status, part, exact, rec));
 }
 
@@ -571,7 +615,7 @@ int launch_dc(const CUtensorMap& tmap, const CUtensorMap& tmap_x, int use_x_tma,
 // lane must hold its (input, chunk) pairs in registers (TI*8 <= 32*DC_MAX_ROUNDS)
 bool dcoeff_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
     const int dp1 = (int)deg + 1;
-    return B > 0 && (out % 4) == 0 && dp1 <= 128;
+    return B > 0 && (out % 4) == 0 && deg >= 1 && dp1 <= 128;
 }
 
 // FP32X3 keeps one partial result per DC_X3_ROWS batch rows.  So that the workspace does not grow with the batch
@@ -589,8 +633,9 @@ int64_t dcoeff_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t de
     if (!x3 && !family && dcoeff_f16_supported(B, in, out, deg)) return dcoeff_f16_workspace_bytes(B, in, out, deg);
     if (x3 && B > x3_group_rows(in, out, deg)) B = x3_group_rows(in, out, deg);
     const DcTcPlan p = dc_tc_plan(B, in, out, deg, x3);
-    const int64_t partials = p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0;
-    return x3 ? round_up(B * out * 4, 256) + partials : partials;     // x3: the tails of dY come first
+    const int64_t partials = round_up(p.splits > 1 ? (int64_t)p.splits * in * out * (deg + 1) * 4 : 0, 256);
+    // x3: the tails of dY come first; last, the partial column sums of dY (degree 0)
+    return (x3 ? round_up(B * out * 4, 256) : 0) + partials + dc_colsum_bytes(B, out);
 }
 
 // dY minus dY truncated to tf32 (defined next to the dx kernel, which needs the same split)
@@ -625,6 +670,8 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
     float* dy_lo = reinterpret_cast<float*>(ws);
     float* partials = x3 ? reinterpret_cast<float*>(reinterpret_cast<char*>(ws) + round_up(B * out * 4, 256))
                          : reinterpret_cast<float*>(ws);
+    float* colsum_part = reinterpret_cast<float*>(reinterpret_cast<char*>(partials) +
+                                                  round_up(p.splits > 1 ? (int64_t)p.splits * n * 4 : 0, 256));
     const cuuint32_t estr[2] = {1, 1};
     auto map_dy = [&](CUtensorMap* m, const float* ptr) -> int {
         const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
@@ -675,7 +722,12 @@ int launch_dcoeff_tc(const float* x, const float* dy, float* dc, void* ws, int64
         if (rc) return rc;
         if (!direct && (rc = launch_dcoeff_reduce(partials, dc, n, p.splits, acc, s))) return rc;
     }
-    return CHEBYKAN_OK;
+    // degree 0: the column sums of dY (exact fp32 sums in every mode), the same for every input
+    const int64_t nblk = ceil_div(B, DC_CS_ROWS);
+    dy_colsum_kernel<<<dim3((unsigned)ceil_div(out, 32), (unsigned)nblk), 256, 0, s>>>(dy, colsum_part, B, (int)out);
+    if ((rc = check_cuda(cudaGetLastError()))) return rc;
+    degree0_fill_kernel<<<(unsigned)ceil_div(out * 32, 256), 256, 0, s>>>(colsum_part, nblk, dc, (int)in, (int)out, dp1, accumulate);
+    return check_cuda(cudaGetLastError());
 }
 
 }  // namespace chebykan
