@@ -55,7 +55,9 @@ inline __host__ __device__ PackedDims packed_dims(int64_t in, int64_t out, int64
     p.planes = (mode == CHEBYKAN_MODE_FP32X3) ? 2 : 1;
     p.in_pad = round_up(in, p.ib);
     p.nd = packed_degrees(deg, mode);
-    p.k_pad = p.in_pad * p.nd;
+    // tensor-core layouts: one more K block behind the last input block, whose first slot holds the bias (the wide
+    // forward multiplies it with a block of ones, which costs one K block per tile and no epilogue work)
+    p.k_pad = p.in_pad * p.nd + (packed_has_bias(deg, mode) ? p.ib : 0);
     return p;
 }
 

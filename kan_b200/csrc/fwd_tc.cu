@@ -107,8 +107,9 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
               float* __restrict__ y, int64_t B, int in, int out, int dp1, int n_tiles,
               int64_t num_tiles, int32_t* status, LnFusion ln, int n_pad, const float* __restrict__ bias,
               const __grid_constant__ typename VariantTable<VAR>::type rec) {
-    // `dp1` counts the degrees that take K slots: degrees 1..deg.  Degree 0, the constant 1, is the bias vector the
-    // epilogue adds (a layer of degree 0 never gets here: its output is the bias alone).
+    // `dp1` counts the degrees that take K slots per input block: degrees 1..deg.  Degree 0, the constant 1, is one
+    // last K block of ones per tile, against the bias row of the packed matrix (a layer of degree 0 never gets
+    // here: its output is the bias alone).
     constexpr bool LN = VAR == VAR_LN;
     constexpr bool FAM = VAR == VAR_FAMILY;
     constexpr bool X3 = MODE == CHEBYKAN_MODE_FP32X3;
@@ -146,7 +147,7 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
     const int64_t unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
     const int64_t nunits = (CG == 2) ? (gridDim.x >> 1) : gridDim.x;
     const int n_iblk = (in + IB - 1) / IB;
-    const int nkb = n_iblk * dp1;
+    const int nkb = n_iblk * dp1 + 1;      // + the bias block: a K block of ones against the packed bias row
     // FP32X3: the tensor pipe's fp32 accumulation truncates, a bias that grows with the number of MMAs added
     // into one accumulator (6e-5 after 3456 of them).  So an accumulator takes only X3_CHUNK K blocks (192 MMAs);
     // the epilogue adds the chunks' partial sums into y with ordinary fp32 additions.
@@ -400,6 +401,16 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
                     }
                 }
             }
+            // the tile's last K block: ones (degree 0 of every input at once) against the packed bias row
+            if (alive) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    inc[j] = 0u;                       // 1.0 is exact in tf32: no rounding increment
+#pragma unroll
+                    for (int e = 0; e < CH; ++e) ta[j][e] = 1.f;
+                }
+                if (!emit(ta)) alive = false;
+            }
         }
     } else if (warp == TMA_WARP) {
         // ------------------------------ coefficient loads ------------------------------
@@ -553,14 +564,6 @@ fwd_tc_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant_
         // one row's 32 consecutive outputs from registers to y
         float ln_s1 = 0.f, ln_s2 = 0.f;    // this row's sum and sum of squares over the tile (fused LayerNorm)
         auto store32 = [&](uint32_t (&r)[32], int64_t row, int col0, bool add) {
-            if (!add) {
-                // degree 0's part of y, the same for every row: lane l fetches bias[col0 + l] (the vector is padded to
-                // the tile grid) and the warp passes the values round, one register instead of thirty-two
-                const float bl = __ldg(bias + col0 + lane);
-#pragma unroll
-                for (int e = 0; e < 32; ++e)
-                    r[e] = __float_as_uint(__uint_as_float(r[e]) + __shfl_sync(0xffffffffu, bl, e));
-            }
             if (row >= B) return;
             if (X3 && add) {
                 // later chunk of the K range: y already holds the earlier chunks' sum

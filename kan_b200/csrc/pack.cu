@@ -10,20 +10,32 @@ namespace chebykan {
 template <int MODE>
 __global__ void __launch_bounds__(256)
 pack_kernel(const float* __restrict__ c, void* __restrict__ packed, int in, int out, int dp1,
-            int ib, int64_t k_pad, int64_t n_pad, int nd) {
+            int ib, int64_t k_pad, int64_t n_pad, int nd, int64_t k_main, const float* __restrict__ bias) {
     const int64_t total = k_pad * n_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
          e += (int64_t)gridDim.x * blockDim.x) {
         int64_t k, n;
         if (MODE == CHEBYKAN_MODE_FP32) { k = e / n_pad; n = e % n_pad; }
         else                            { n = e / k_pad; k = e % k_pad; }
-        // nd degrees take K slots: all dp1 of them, or degrees 1..deg when degree 0 travels as the bias vector
-        const int64_t blk = k / ((int64_t)ib * nd);
-        const int64_t rem = k % ((int64_t)ib * nd);
-        const int d = (int)(rem / ib) + (dp1 - nd);
-        const int64_t i = blk * ib + rem % ib;
         float v = 0.f;
-        if (i < in && n < out) v = c[(i * out + n) * dp1 + d];
+        if (k >= k_main) {
+            // the bias block (tensor-core layouts): slot 0 holds the bias as the mode rounds it, slot 1 what that
+            // rounding dropped, so the kernel's block of ones adds the bias to about twice the mode's precision
+            if (n < out && k <= k_main + 1) {
+                const float b = bias[n];
+                float head = b;
+                if (MODE == CHEBYKAN_MODE_BF16) head = __bfloat162float(__float2bfloat16_rn(b));
+                else if (MODE == CHEBYKAN_MODE_TF32) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(b)); head = __uint_as_float(r); }
+                v = (k == k_main) ? b : b - head;
+            }
+        } else {
+            // nd degrees take K slots: all dp1 of them, or degrees 1..deg when degree 0 travels as the bias
+            const int64_t blk = k / ((int64_t)ib * nd);
+            const int64_t rem = k % ((int64_t)ib * nd);
+            const int d = (int)(rem / ib) + (dp1 - nd);
+            const int64_t i = blk * ib + rem % ib;
+            if (i < in && n < out) v = c[(i * out + n) * dp1 + d];
+        }
         if (MODE == CHEBYKAN_MODE_FP32) {
             reinterpret_cast<float*>(packed)[e] = v;
         } else if (MODE == CHEBYKAN_MODE_FP32X3) {
@@ -55,18 +67,20 @@ coeff_absmax_kernel(const float* __restrict__ c, int64_t n, uint32_t* __restrict
 
 __global__ void __launch_bounds__(256)
 pack_half_kernel(const float* __restrict__ c, uint32_t* __restrict__ header, __half* __restrict__ plane, int in, int out,
-                 int dp1, int ib, int64_t k_pad, int64_t n_pad, int nd) {
+                 int dp1, int ib, int64_t k_pad, int64_t n_pad, int nd, int64_t k_main) {
     const float scale = half_scale_for(header[0]);
     if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<float*>(header)[1] = 1.f / scale;
     const int64_t total = k_pad * n_pad;
     for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
         const int64_t n = e / k_pad, k = e % k_pad;
-        const int64_t blk = k / ((int64_t)ib * nd);
-        const int64_t rem = k % ((int64_t)ib * nd);
-        const int d = (int)(rem / ib) + (dp1 - nd);
-        const int64_t i = blk * ib + rem % ib;
         float v = 0.f;
-        if (i < in && n < out) v = c[(i * out + n) * dp1 + d] * scale;
+        if (k < k_main) {      // (the bias block stays zero: the narrow kernel adds the fp32 bias vector)
+            const int64_t blk = k / ((int64_t)ib * nd);
+            const int64_t rem = k % ((int64_t)ib * nd);
+            const int d = (int)(rem / ib) + (dp1 - nd);
+            const int64_t i = blk * ib + rem % ib;
+            if (i < in && n < out) v = c[(i * out + n) * dp1 + d] * scale;
+        }
         plane[e] = __float2half_rn(v);
     }
 }
@@ -108,7 +122,7 @@ static int launch_pack_half_plane(const float* coeffs, void* packed, int64_t in,
     blocks = ceil_div(total, 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     pack_half_kernel<<<(unsigned)blocks, 256, 0, s>>>(coeffs, header, reinterpret_cast<__half*>(base + HALF_PLANE_HEADER),
-                                                    (int)in, (int)out, (int)deg + 1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
+                                                    (int)in, (int)out, (int)deg + 1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd, p.in_pad * p.nd);
     return check_cuda(cudaGetLastError());
 }
 
@@ -116,29 +130,32 @@ int launch_pack(const float* coeffs, void* packed, int64_t in, int64_t out, int6
                 cudaStream_t s) {
     const PackedDims p = packed_dims(in, out, deg, mode);
     const int64_t total = p.k_pad * p.n_pad;
+    const int64_t k_main = p.in_pad * p.nd;        // K slots of the inputs; the bias block (if any) follows
     int64_t blocks = ceil_div(total, 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     const int dp1 = (int)deg + 1;
-    if (total == 0) { /* degree 0 in a tensor-core mode: the bias alone */ }
-    else if (mode == CHEBYKAN_MODE_FP32)
-        pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
-    else if (mode == CHEBYKAN_MODE_FP32X3)
-        pack_kernel<CHEBYKAN_MODE_FP32X3><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
-    else if (mode == CHEBYKAN_MODE_TF32)
-        pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
-    else
-        pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd);
-    int rc = check_cuda(cudaGetLastError());
-    if (rc == CHEBYKAN_OK && total > 0 && mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
-        rc = launch_pack_half_plane(coeffs, packed, in, out, deg, s);
-    if (rc == CHEBYKAN_OK && packed_has_bias(deg, mode)) {
-        float* bias = reinterpret_cast<float*>(reinterpret_cast<char*>(packed) + packed_bias_offset(in, out, deg, mode));
+    int rc = CHEBYKAN_OK;
+    float* bias = nullptr;
+    if (packed_has_bias(deg, mode)) {
+        // the bias vector first: the matrices' bias block is filled from it
+        bias = reinterpret_cast<float*>(reinterpret_cast<char*>(packed) + packed_bias_offset(in, out, deg, mode));
         const unsigned bb = (unsigned)ceil_div(p.n_pad * 32, 256);
         if (mode == CHEBYKAN_MODE_BF16) pack_bias_kernel<CHEBYKAN_MODE_BF16><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
         else if (mode == CHEBYKAN_MODE_TF32) pack_bias_kernel<CHEBYKAN_MODE_TF32><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
         else pack_bias_kernel<CHEBYKAN_MODE_FP32X3><<<bb, 256, 0, s>>>(coeffs, bias, (int)in, (int)out, dp1, p.n_pad);
-        rc = check_cuda(cudaGetLastError());
+        if ((rc = check_cuda(cudaGetLastError()))) return rc;
     }
+    if (mode == CHEBYKAN_MODE_FP32)
+        pack_kernel<CHEBYKAN_MODE_FP32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd, k_main, bias);
+    else if (mode == CHEBYKAN_MODE_FP32X3)
+        pack_kernel<CHEBYKAN_MODE_FP32X3><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd, k_main, bias);
+    else if (mode == CHEBYKAN_MODE_TF32)
+        pack_kernel<CHEBYKAN_MODE_TF32><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd, k_main, bias);
+    else
+        pack_kernel<CHEBYKAN_MODE_BF16><<<(unsigned)blocks, 256, 0, s>>>(coeffs, packed, (int)in, (int)out, dp1, (int)p.ib, p.k_pad, p.n_pad, (int)p.nd, k_main, bias);
+    if ((rc = check_cuda(cudaGetLastError()))) return rc;
+    if (deg >= 1 && mode == CHEBYKAN_MODE_TF32 && tf32_has_half_plane(in, out))
+        rc = launch_pack_half_plane(coeffs, packed, in, out, deg, s);
     return rc;
 }
 

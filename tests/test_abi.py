@@ -41,14 +41,15 @@ def test_pure_host_entry_points(built_lib):
     assert lib.chebykan_packed_bytes(1024, 1024, 8, _lib.MODE_FP32) == 1024 * 9 * 1024 * 4
     assert lib.chebykan_packed_bytes(1, 1, 8, _lib.MODE_FP32) == 8 * 9 * 64 * 4
     # bf16 [N_pad][K_pad]: inputs padded to 64, outputs to 128
-    # tensor-core modes: degrees 1..deg in the matrix, degree 0 as a bias vector of N_pad floats behind it
-    assert lib.chebykan_packed_bytes(1024, 1024, 8, _lib.MODE_BF16) == 1024 * 8 * 1024 * 2 + 1024 * 4
-    assert lib.chebykan_packed_bytes(784, 64, 4, _lib.MODE_BF16) == 832 * 4 * 128 * 2 + 128 * 4
-    assert lib.chebykan_packed_bytes(784, 64, 0, _lib.MODE_BF16) == 128 * 4         # degree 0: the bias alone
+    # tensor-core modes: degrees 1..deg in the matrix plus one K block whose first slot is the bias (degree 0), and the
+    # bias again as a vector of N_pad floats behind the matrices
+    assert lib.chebykan_packed_bytes(1024, 1024, 8, _lib.MODE_BF16) == (1024 * 8 + 64) * 1024 * 2 + 1024 * 4
+    assert lib.chebykan_packed_bytes(784, 64, 4, _lib.MODE_BF16) == (832 * 4 + 64) * 128 * 2 + 128 * 4
+    assert lib.chebykan_packed_bytes(784, 64, 0, _lib.MODE_BF16) == 64 * 128 * 2 + 128 * 4    # degree 0: the bias alone
     # TF32, narrow layer (<= 128 outputs, in % 4 == 0): the tf32 matrix, then a 256-byte header and an fp16 plane in the BF16 layout
-    assert lib.chebykan_packed_bytes(784, 64, 4, _lib.MODE_TF32) == 800 * 4 * 128 * 4 + 256 + 832 * 4 * 128 * 2 + 128 * 4
-    assert lib.chebykan_packed_bytes(1024, 1024, 8, _lib.MODE_TF32) == 1024 * 8 * 1024 * 4 + 1024 * 4
-    assert lib.chebykan_packed_bytes(783, 64, 4, _lib.MODE_TF32) == 800 * 4 * 128 * 4 + 128 * 4
+    assert lib.chebykan_packed_bytes(784, 64, 4, _lib.MODE_TF32) == (800 * 4 + 32) * 128 * 4 + 256 + (832 * 4 + 64) * 128 * 2 + 128 * 4
+    assert lib.chebykan_packed_bytes(1024, 1024, 8, _lib.MODE_TF32) == (1024 * 8 + 32) * 1024 * 4 + 1024 * 4
+    assert lib.chebykan_packed_bytes(783, 64, 4, _lib.MODE_TF32) == (800 * 4 + 32) * 128 * 4 + 128 * 4
     # invalid arguments come back as error codes, never exceptions or crashes
     assert lib.chebykan_packed_bytes(0, 4, 4, 0) == -1
     assert lib.chebykan_packed_bytes(4, 4, 200, 0) == -1
