@@ -557,9 +557,12 @@ def sub_stack_cfg4(ctx: Ctx, mode: str, fuse_ln: bool, steps: int, warmup: int, 
     return rec
 
 
-def sub_train_cfg5(ctx: Ctx, mode: str, steps: int, warmup: int, peaks, tf32_peak, batch: int = 0, torch_loss: bool = False):
+def sub_train_cfg5(ctx: Ctx, mode: str, steps: int, warmup: int, peaks, tf32_peak, batch: int = 0, torch_loss: bool = False,
+                   graph: bool = False):
     """Configuration 5: 64 -> 64 -> 64, degree 32, global batch 1048576 sharded over the ranks; forward, MSE loss
-    (mean over the GLOBAL batch), backward, NCCL all-reduce of the flat gradient buffer, SGD."""
+    (mean over the GLOBAL batch), backward, NCCL all-reduce of the flat gradient buffer, SGD.  With `graph` the
+    whole step, collective included, is recorded once and replayed as one CUDA graph per rank (the host needs
+    about 0.5 ms to issue the step's launches, more than the kernels take once the batch is split eight ways)."""
     import kan_b200
     from kan_b200 import dp, ops, workloads
     cfg = workloads.CONFIGS["cfg5"]
@@ -593,10 +596,17 @@ def sub_train_cfg5(ctx: Ctx, mode: str, steps: int, warmup: int, peaks, tf32_pea
         opt.step()
         last["loss"] = loss
         k[0] += 1
+    if graph:
+        graphed = kan_b200.graph.GraphedTrainStep(model, lambda y_, t_: kan_b200.mse_loss(y_, t_, n_mean=n_mean), opt,
+                                                  x, tgt)
+        buf = graphed.grads
+
+        def step():                                            # noqa: F811 - the replayed step replaces the eager one
+            last["loss"] = graphed()
     ms, _ = ctx.time_steps(step, steps, warmup)
     torch.cuda.synchronize()
     w = max(warmup, 3)
-    ar_ms = ctx.max_over_ranks(sum(ar0[w + i].elapsed_time(ar1[w + i]) for i in range(steps)) / steps)
+    ar_ms = None if graph else ctx.max_over_ranks(sum(ar0[w + i].elapsed_time(ar1[w + i]) for i in range(steps)) / steps)
     loss = last["loss"].detach().clone()
     if ctx.world > 1 and not torch_loss:
         ctx.dist.all_reduce(loss)          # per-rank partial sums of the global mean
@@ -613,12 +623,15 @@ def sub_train_cfg5(ctx: Ctx, mode: str, steps: int, warmup: int, peaks, tf32_pea
     rec = {"workload": f"cfg5: ChebyKAN 64->64->64 degree 32, global batch {Bg}, fwd + MSE + bwd + all-reduce(dC) + SGD",
            "value": Bg / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "rows_per_gpu": rows, "math_mode": mode,
            "loss": "torch.nn.MSELoss" if torch_loss else "kan_b200.mse_loss (loss and gradient in one pass)",
-           "scaling": "strong", "allreduce_ms": ar_ms if ctx.world > 1 else 0.0,
+           "scaling": "strong", "allreduce_ms": ar_ms if ctx.world > 1 else 0.0, "cuda_graph": bool(graph),
            "allreduce_bytes": buf.flat.numel() * 4, "final_loss": float(loss),
            "roofline": {"bound": "basis generation / stage hand-over (neither tensor- nor HBM-bound)",
                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                         "peak_note": "GEMM-equivalent FLOPs (fwd + dC per layer, dx for the second) against the " + note,
                         "hbm_gbs": hbm_bytes / (ms * 1e-3) / 1e9, "hbm_frac": hbm_bytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}
+    if graph:
+        graphed.close()                 # a graph with a captured collective must be gone before the process group is
+        del graphed, step
     del model, x, tgt, buf, opt
     free_gpu()
     return rec
@@ -734,6 +747,7 @@ def run_ours(args):
         sub["cfg4_stack_fwd_bf16_fused_ln"] = sub_stack_cfg4(ctx, "bf16", True, ks, kw, peaks, tf32_peak)
         sub["cfg5_train_tf32"] = sub_train_cfg5(ctx, "tf32", ks, kw, peaks, tf32_peak)
         sub["cfg5_train_bf16_fwd_tf32_bwd"] = sub_train_cfg5(ctx, "bf16", ks, kw, peaks, tf32_peak)
+        sub["cfg5_train_tf32_graph"] = sub_train_cfg5(ctx, "tf32", ks, kw, peaks, tf32_peak, graph=True)
         if ctx.world == 1:
             sub["cfg5_train_tf32_torch_loss"] = sub_train_cfg5(ctx, "tf32", ks, kw, peaks, tf32_peak, torch_loss=True)
             sub["cfg5_train_fp32x3"] = sub_train_cfg5(ctx, "fp32x3", 3, kw, peaks, tf32_peak)
@@ -766,8 +780,10 @@ def run_ours(args):
                          "peak_note": peak_note, "flops_per_launch": flops, "per": "GPU",
                          "flops_executed": flops if mode == "fp32" else flops * deg / (deg + 1),
                          "flops_note": "achieved and frac count the layer's algorithmic FLOPs 2*B*in*(deg+1)*out; the "
-                                       "tensor-core kernels execute deg/(deg+1) of them: degree 0 of the basis is the "
-                                       "constant 1, so its term sum_i C[i,o,0] is a bias vector added in the epilogue"},
+                                       "tensor-core kernels execute deg/(deg+1) of them (plus one K block per tile): "
+                                       "degree 0 of the basis is the constant 1, so its term sum_i C[i,o,0] is a bias "
+                                       "vector, multiplied by a K block of ones (wide layers) or added in the "
+                                       "epilogue (narrow layers)"},
             "e2e": e2e if e2e else {"value": None, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": args.steps,
             "clocks": clocks,
@@ -792,7 +808,7 @@ def run_model_config(args):
         rec = sub_stack_cfg4(ctx, args.mode, args.fuse_ln, args.steps, args.warmup, peaks, None, batch=args.batch)
     elif args.config == "cfg5":
         rec = sub_train_cfg5(ctx, args.mode, args.steps, args.warmup, peaks, None, batch=args.batch,
-                             torch_loss=args.torch_loss)
+                             torch_loss=args.torch_loss, graph=args.graph and not args.torch_loss)
     else:
         rec = sub_small_train(ctx, args.config, args.graph, args.steps, args.warmup)
     if ctx.rank == 0:
@@ -820,7 +836,7 @@ def main():
     ap.add_argument("--fuse-ln", action="store_true",
                     help="--config cfg4: fold the LayerNorms between layers into the ChebyKAN kernels")
     ap.add_argument("--graph", action="store_true",
-                    help="--config cfg1/cfg2: replay the whole step as one CUDA graph (single GPU)")
+                    help="--config cfg1/cfg2/cfg5: replay the whole step as one CUDA graph (cfg5: all-reduce included)")
     ap.add_argument("--torch-loss", action="store_true", help="--config cfg5: torch.nn.MSELoss instead of the fused loss")
     ap.add_argument("--op", default="fwd", choices=["fwd", "dcoeff", "dx"],
                     help="time the forward (headline) or one backward kernel on the same shape")

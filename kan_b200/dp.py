@@ -92,6 +92,13 @@ def world_info() -> Tuple[int, int]:
     return 0, 1
 
 
+def world_info_of(group=None) -> Tuple[int, int]:
+    """(rank, size) within `group` (the world when None); (0, 1) without an initialised process group."""
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_rank(group), dist.get_world_size(group)
+    return 0, 1
+
+
 # ---------------------------------------------------------------------------------------------------------------
 # sharding over the output dimension
 # ---------------------------------------------------------------------------------------------------------------

@@ -1,7 +1,9 @@
 """Data-parallel checks over NCCL on every GPU of the box (skipped on a single-GPU box): sharded inference
 reproduces the single-GPU rows bit for bit, the all-reduced coefficient gradient matches the full-batch
-gradient, one sharded training step leaves identical coefficients on every rank, and a layer sharded over its
-output columns gives the unsharded layer's y, dC and dx."""
+gradient, one sharded training step leaves identical coefficients on every rank (also when the step, collective
+included, is replayed as a CUDA graph), and a layer sharded over its output columns gives the unsharded layer's y,
+dC and dx."""
+import datetime
 import os
 
 import pytest
@@ -17,7 +19,9 @@ def _worker(rank, world, port, results):
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    # a short collective timeout: a rank that failed before a collective ends the others' wait with an error
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank),
+                            timeout=datetime.timedelta(seconds=120))
     try:
         import kan_b200
         from kan_b200 import dp, ops
@@ -78,6 +82,39 @@ def _worker(rank, world, port, results):
         torch.nn.functional.mse_loss(o.forward(xt, cr), tt).backward()
         expect = start - 0.5 * cr.grad
         ok = ok and o.rel_l2(mine.cpu() - start, expect - start) <= 2e-3
+        # --- the same kind of step replayed as one CUDA graph per rank, all-reduce inside the graph: three replays
+        # leave the coefficients that the eager data-parallel loop leaves, identical on every rank
+        torch.manual_seed(9)
+        mk = lambda: torch.nn.Sequential(kan_b200.ChebyKANLayer(64, 64, 8, math_mode="tf32"),
+                                         kan_b200.ChebyKANLayer(64, 32, 8, math_mode="tf32")).cuda()
+        m_e, m_g = mk(), mk()
+        m_g.load_state_dict(m_e.state_dict())
+        Bg = 2048 * world
+        gg = torch.Generator().manual_seed(13)
+        xg_, tg_ = torch.randn(Bg, 64, generator=gg), torch.randn(Bg, 32, generator=gg)
+        bg, eg = dp.shard_rows(Bg, rank, world)
+        xs, ts = xg_[bg:eg].cuda(), tg_[bg:eg].cuda()
+        loss_fn = lambda y_, t_: kan_b200.mse_loss(y_, t_, n_mean=Bg * 32)
+        gstep = kan_b200.graph.GraphedTrainStep(m_g, loss_fn, kan_b200.optim.SGD(list(m_g.parameters()), lr=0.1), xs, ts)
+        for _ in range(3):
+            gstep()
+        ebuf = dp.FlatGradBuffer(m_e.parameters())
+        eopt = kan_b200.optim.SGD(list(m_e.parameters()), lr=0.1)
+        for _ in range(3 + 3):                          # the graphed step ran three eager warm-up steps first
+            ebuf.zero()
+            loss_fn(m_e(xs), ts).backward()
+            ebuf.all_reduce()
+            eopt.step()
+        torch.cuda.synchronize()
+        ops.check_status()
+        gstep.close()                                   # destroy_process_group waits for graphs that hold a collective
+        with pytest.raises(RuntimeError):
+            gstep()
+        for pe, pg in zip(m_e.parameters(), m_g.parameters()):
+            ok = ok and o.rel_l2(pg.detach().cpu(), pe.detach().cpu()) <= 1e-6
+            allg = [torch.empty_like(pg.detach()) for _ in range(world)]
+            dist.all_gather(allg, pg.detach().contiguous())
+            ok = ok and all(torch.equal(allg[0], w) for w in allg)
         # --- the output dimension as a second sharding axis: every rank holds a block of output columns of one layer
         # (Chebyshev fp32 and a Jacobi layer), sees all rows, and dx is summed over the ranks
         from oracle import polykan_oracle as po
@@ -117,5 +154,10 @@ def test_data_parallel_on_all_gpus():
             p.start()
         for p in procs:
             p.join(timeout=600)
-            assert p.exitcode == 0
+        stuck = [p for p in procs if p.exitcode is None]
+        for p in stuck:                                  # never leave a child behind on the GPU
+            p.terminate()
+            p.join(timeout=30)
+        assert not stuck
+        assert all(p.exitcode == 0 for p in procs)
         assert dict(results) == {r: True for r in range(world)}

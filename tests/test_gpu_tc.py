@@ -555,3 +555,37 @@ def test_cta_pair_kernels_replay_from_a_cuda_graph():
     ops.check_status()
     assert torch.equal(y_g, y_e) and torch.equal(dc_g, dc_e) and torch.equal(dx_g, dx_e)
 
+
+
+@pytest.mark.parametrize("mode", ["tf32", "bf16"])
+def test_graphed_training_step_narrow_layers_equals_eager(mode):
+    """Configuration 5's model shape (64 -> 64 -> 64, degree 32) at a small batch: the whole step (narrow-layer
+    tensor-memory forward, fp16-operand dC with its pre-pass, dx, fused MSE, SGD) replayed as one CUDA graph leaves
+    the coefficients an eager loop leaves, bit for bit."""
+    torch.manual_seed(17)
+    make = lambda: torch.nn.Sequential(kan_b200.ChebyKANLayer(64, 64, 32, math_mode=mode),
+                                       kan_b200.ChebyKANLayer(64, 64, 32, math_mode=mode)).cuda()
+    eager, graphed = make(), make()
+    graphed.load_state_dict(eager.state_dict())
+    B = 4096 + 64
+    x = (torch.rand(B, 64, generator=torch.Generator().manual_seed(18)) * 6 - 3).cuda()
+    tgt = torch.sin(x).sum(1, keepdim=True).expand(-1, 64).contiguous()
+    loss_fn = lambda y, t: kan_b200.mse_loss(y, t, n_mean=B * 64)
+    step = kan_b200.graph.GraphedTrainStep(graphed, loss_fn, kan_b200.optim.SGD(list(graphed.parameters()), lr=1e-2),
+                                           x, tgt)
+    n_done = 3                                           # the constructor's eager warm-up steps
+    for _ in range(4):
+        step()
+        n_done += 1
+    buf = kan_b200.dp.FlatGradBuffer(eager.parameters())
+    opt = kan_b200.optim.SGD(list(eager.parameters()), lr=1e-2)
+    for _ in range(n_done):
+        buf.zero()
+        loss = loss_fn(eager(x), tgt)
+        loss.backward()
+        opt.step()
+    torch.cuda.synchronize()
+    ops.check_status()
+    for a, b in zip(eager.parameters(), graphed.parameters()):
+        assert torch.equal(a.detach(), b.detach())
+    assert torch.equal(step.loss.detach(), loss.detach())
