@@ -95,6 +95,7 @@ def test_install_into_reference_registry():
 
 
 def test_shard_rows_partition():
+    assert dp.world_info_of(None) == (0, 1)              # no process group in this process
     for n, w in [(65536, 8), (100, 3), (7, 8), (0, 2)]:
         spans = [dp.shard_rows(n, r, w) for r in range(w)]
         assert spans[0][0] == 0 and spans[-1][1] == n
@@ -141,6 +142,7 @@ def _dp_worker(rank, world, port, results):
         _, dC_full, _ = o.forward_backward(x, coeffs, dy, need_dx=False)
         ok = o.rel_l2(p1.grad, dC_full) < 1e-6 and torch.allclose(p2.grad, torch.full((5,), 3.0))
         assert dp.world_info() == (rank, world)
+        assert dp.world_info_of(None) == (rank, world)
         # zero_grad(set_to_none=True) drops the aliases; backward then installs fresh tensors: the next
         # all_reduce must still cover them
         p1.grad = None
