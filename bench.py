@@ -330,8 +330,10 @@ def free_gpu():
     torch.cuda.empty_cache()
 
 
-def tensor_peak(mode: str, op: str, peaks: dict, tf32_peak):
-    """(peak TFLOP/s, note) a kernel of this mode is quoted against."""
+def tensor_peak(mode: str, op: str, peaks: dict, tf32_peak, n_out: int = 0):
+    """(peak TFLOP/s, note) a kernel of this mode is quoted against.  dC contracts tf32 (or, on narrow layers, fp16)
+    operands in both tensor-core modes; dx does too, except in bf16 mode on layers of 512 outputs or more, where it
+    contracts fp16 operands and is quoted against the 16-bit peak."""
     if mode == "fp32":
         return FFMA_PEAK_TFLOPS, "nominal FFMA peak (148 SM x 128 lanes x 2 x 1.965 GHz)"
     tf32 = tf32_peak["tflops"] if tf32_peak else peaks["bf16_tflops"] / 2
@@ -339,6 +341,8 @@ def tensor_peak(mode: str, op: str, peaks: dict, tf32_peak):
                  else f"half of the {peaks['source']} bf16 burst peak (no tf32 measurement in this run)")
     if mode == "fp32x3":
         return tf32 / 3, "a third of the " + tf32_note + ": three tf32 products per multiply"
+    if op == "dx" and mode == "bf16" and n_out >= 512:
+        return peaks["bf16_tflops"], f"{peaks['source']} cuBLAS bf16 burst peak (fp16 operands)"
     if mode == "tf32" or op in ("dcoeff", "dx"):
         return tf32, tf32_note
     return peaks["bf16_tflops"], f"{peaks['source']} cuBLAS bf16 burst peak"
@@ -454,9 +458,9 @@ def layer_record(ctx, mode, op, B_rank, B_total, shape, ms, peaks, tf32_peak, ex
     n_in, n_out, deg = shape
     flops_rank = 2.0 * B_rank * n_in * (deg + 1) * n_out
     achieved = flops_rank / (ms * 1e-3) / 1e12
-    peak, note = tensor_peak(mode, op, peaks, tf32_peak)
+    peak, note = tensor_peak(mode, op, peaks, tf32_peak, n_out)
     rec = {"value": B_total / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "rows_per_gpu": B_rank,
-           "dtype": DTYPE_NAME[mode],
+           "dtype": "f16" if (op == "dx" and mode == "bf16" and n_out >= 512) else DTYPE_NAME[mode],
            "roofline": {"bound": "tensor" if mode != "fp32" else "ffma", "achieved": achieved, "peak": peak,
                         "unit": "TFLOP/s", "frac": achieved / peak, "peak_note": note}}
     if extra:
@@ -738,7 +742,7 @@ def run_ours(args):
                 tf32_peak, {"scaling": "weak", "workload": "a full 65536-row batch on every GPU"})
         else:
             for m, op in (("tf32", "fwd"), ("fp32x3", "fwd"), ("fp32", "fwd"), ("tf32", "dcoeff"), ("tf32", "dx"),
-                          ("fp32x3", "dcoeff"), ("fp32x3", "dx")):
+                          ("bf16", "dx"), ("fp32x3", "dcoeff"), ("fp32x3", "dx")):
                 ms, _, st = bench_layer(ctx, m, op, Bg, n_in, n_out, deg, ks if m != "fp32" else 3, kw)
                 del st
                 free_gpu()
@@ -761,7 +765,7 @@ def run_ours(args):
     if ctx.rank == 0:
         flops = 2.0 * B * n_in * (deg + 1) * n_out            # per GPU
         achieved = flops / (ms_step * 1e-3) / 1e12
-        peak, peak_note = tensor_peak(mode, args.op, peaks, tf32_peak)
+        peak, peak_note = tensor_peak(mode, args.op, peaks, tf32_peak, n_out)
         traffic = measured_traffic(f"{args.op}_{mode}_cfg3", B) if not (args.shape or args.family) else None
         cfg = headline_config(ctx.world)
         if single:

@@ -166,6 +166,12 @@ int chebykan_bwd_dcoeff_static(const float* x, const float* dy, float* dcoeffs,
  * Reads the coefficients in their own [in][out][deg+1] layout.  The tensor-core
  * modes repack them into `workspace` on every call
  * (chebykan_workspace_bytes(CHEBYKAN_OP_BWD_DX, ...) bytes; 0 in FP32 mode).
+ * TF32 mode contracts in tcgen05 kind::tf32.  BF16 mode does the same on layers
+ * of fewer than 512 outputs and contracts fp16 operands (tf32's 11 significant
+ * bits, half the MMAs) on wider ones: the workspace then also holds a copy of dY
+ * as fp16, every row scaled by a power of two taken from its largest element,
+ * and the coefficients are scaled likewise; both scales are exact and undone
+ * before dx is written.
  */
 int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs,
                     float* dx, void* workspace, int64_t workspace_bytes,

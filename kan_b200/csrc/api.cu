@@ -46,6 +46,22 @@ static bool mode_ok(int mode) {
     return mode == CHEBYKAN_MODE_FP32 || mode == CHEBYKAN_MODE_TF32 || mode == CHEBYKAN_MODE_BF16 ||
            mode == CHEBYKAN_MODE_FP32X3;
 }
+// CHEBYKAN_DX_WIDE=tf32 in the environment keeps the bf16 mode's wide layers on tf32 operands (A/B timing; read once)
+static bool wide_dx_in_tf32() {
+    static const bool v = [] {
+        const char* e = getenv("CHEBYKAN_DX_WIDE");
+        return e != nullptr && strcmp(e, "tf32") == 0;
+    }();
+    return v;
+}
+// operand variant of the tensor-core dx kernel: 1 = three tf32 products (FP32X3), 2 = fp16 operands (the bf16 mode on
+// wide layers, where the kernel is bound by the tensor pipe: half the MMAs at tf32's 11 significant bits; narrow
+// layers are bound by the fold, and the scaled fp16 copy of dY would only cost), 0 = tf32 operands
+static int dx_variant(int64_t out, int64_t deg, int mode) {
+    if (mode == CHEBYKAN_MODE_FP32X3) return 1;
+    if (mode == CHEBYKAN_MODE_BF16 && out >= 512 && deg >= 1 && !wide_dx_in_tf32()) return 2;
+    return 0;
+}
 static bool dx_on_tensor_cores(int64_t B, int64_t in, int64_t out, int64_t deg, int mode) {
     if (mode == CHEBYKAN_MODE_FP32 || !dx_tc_supported(B, in, out, deg)) return false;
     return mode != CHEBYKAN_MODE_FP32X3 || x3_dx_on_tensor_cores(B, in, out, deg);
@@ -109,7 +125,7 @@ int64_t chebykan_workspace_bytes(int op, int64_t B, int64_t in, int64_t out, int
         case CHEBYKAN_OP_BWD_DCOEFF: return B == 0 ? 0 : dcoeff_workspace_bytes(B, in, out, deg, mode);
         case CHEBYKAN_OP_BWD_DX:
             return dx_on_tensor_cores(B, in, out, deg, mode)
-                       ? dx_tc_workspace_bytes(B, in, out, deg, mode == CHEBYKAN_MODE_FP32X3) : 0;
+                       ? dx_tc_workspace_bytes(B, in, out, deg, dx_variant(out, deg, mode)) : 0;
         default: return CHEBYKAN_EINVAL;
     }
 }
@@ -192,12 +208,13 @@ int chebykan_bwd_dx(const float* x, const float* dy, const float* coeffs, float*
         return CHEBYKAN_EALIGN;
     int rc = check_device();
     if (rc) return rc;
-    // tf32 and bf16 modes: tcgen05 kind::tf32 with the coefficients repacked into the workspace
+    // tf32 mode (and narrow layers in the bf16 mode): tcgen05 kind::tf32 with the coefficients repacked into the
+    // workspace; bf16 mode on wide layers: kind::f16 on scaled fp16 copies of dY and the coefficients
     // FP32X3: the same kernel three times on tf32 heads and tails of dY and of the coefficients
     if (dx_on_tensor_cores(B, in, out, deg, mode)) {
         if (!status) return CHEBYKAN_EINVAL;
         return launch_dx_tc(x, dy, coeffs, dx, workspace, workspace_bytes, B, in, out, deg, status,
-                            (cudaStream_t)stream, mode == CHEBYKAN_MODE_FP32X3);
+                            (cudaStream_t)stream, dx_variant(out, deg, mode));
     }
     return launch_dx_ffma(x, dy, coeffs, dx, B, in, out, deg, (cudaStream_t)stream);
 }

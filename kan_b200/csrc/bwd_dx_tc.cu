@@ -18,6 +18,15 @@
 // covers 256 rows, each CTA loads the dY tile of its own 128 rows and half of the Wd tile, and
 // the even CTA issues M = 256 MMAs, so every coefficient byte is fetched once per 256 rows.
 // Every mbarrier wait is bounded, as in the forward kernel.
+//
+// fp16-operand variant (template flag H; wide layers in the bf16 mode): the same kernel with kind::f16 MMAs on
+// K blocks of 64 outputs, i.e. twice the contraction per 128-byte row and half the MMAs.  fp16 carries the 11
+// significant bits of tf32, so the accuracy is that of the tf32 variant; what fp16 lacks is range, and exact
+// power-of-two scales supply it: one pass over dY scales every batch row by the power of two that puts the row's
+// largest element into [2^14, 2^15) and writes it as fp16 (dx is linear in a row of dY, and an epilogue thread owns one
+// row), the coefficient repack writes d * C * s_W with max |C| * s_W in [2^14, 2^15) / 2^ceil(log2 deg), so that the
+// degree factor cannot overflow, and the epilogue multiplies each dx by its row's 1/s_b and by 1/s_W.
+#include <cuda_fp16.h>
 #include "tc_common.cuh"
 
 namespace chebykan {
@@ -36,6 +45,8 @@ constexpr int DX_EPI_WARPS = 16;
 constexpr int DX_THREADS = (2 + DX_EPI_WARPS) * 32;
 constexpr int DX_BM = 128, DX_BN = 256, DX_KB = 32;   // DX_BN: the widest tile (slots per accumulator)
 constexpr int DX_A_STAGE = DX_BM * 128;
+constexpr int DX_KB_HALF = 64;            // outputs per K block with fp16 operands (128 bytes all the same)
+constexpr int DX_HEADER = 256;            // fp16 variant's workspace header: [0] max |C| as bits, [1] 1 / s_W (float)
 // BN slots per accumulator, 512 / BN accumulators, one epilogue group each.  256 is what runs: four accumulators
 // of 128 slots (four groups of four warps) measured slower on the narrow layers they were meant for (0.94 against
 // 0.81 ms at 1048576 x 64 -> 64, degree 32: 22 tiles per row block instead of 10, each with its own set-up, and a
@@ -118,6 +129,84 @@ dy_tail_kernel(const float* __restrict__ dy, float* __restrict__ lo, int64_t n) 
     }
 }
 
+// ---- pre-pass of the fp16-operand variant ----------------------------------------------------------------------
+// max |v| as the bit pattern of a non-negative float (integer max then is float max; a NaN beats every finite value
+// and turns the scaling off)
+__global__ void __launch_bounds__(256)
+dx_absmax_kernel(const float* __restrict__ v, int64_t n, uint32_t* __restrict__ out_bits) {
+    uint32_t m = 0u;
+    const int64_t n4 = n >> 2;
+    const float4* v4 = reinterpret_cast<const float4*>(v);
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < n4; e += (int64_t)gridDim.x * blockDim.x) {
+        const float4 a = v4[e];
+        m = max(m, __float_as_uint(fabsf(a.x))); m = max(m, __float_as_uint(fabsf(a.y)));
+        m = max(m, __float_as_uint(fabsf(a.z))); m = max(m, __float_as_uint(fabsf(a.w)));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) m = max(m, __float_as_uint(fabsf(v[(n4 << 2) + threadIdx.x])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0 && m != 0u) atomicMax(out_bits, m);
+}
+
+// s_W: max |C| * s_W lies in [2^14, 2^15) / 2^ceil(log2 max_factor), so max_factor * |C| * s_W stays below 2^15
+__device__ __forceinline__ float dx_w_scale(uint32_t maxbits, int max_factor) {
+    int sh = 0;
+    while ((1 << sh) < max_factor) ++sh;
+    return half_scale_for(maxbits) * __uint_as_float((uint32_t)(127 - sh) << 23);
+}
+
+// Wd[(i,d)][out_pad] <- fp16(d * C[i][o][d] * s_W); also writes the inverse scale the epilogue applies
+__global__ void __launch_bounds__(256)
+pack_dx_half_kernel(const float* __restrict__ c, uint32_t* __restrict__ header, __half* __restrict__ wd, int in, int out,
+                    int nd, int out_pad, int degree_factor) {
+    const float s_w = dx_w_scale(header[0], degree_factor ? nd : 1);
+    if (blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<float*>(header)[1] = 1.f / s_w;
+    const int64_t total = (int64_t)in * nd * out_pad;
+    for (int64_t e = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; e < total;
+         e += (int64_t)gridDim.x * blockDim.x) {
+        const int o = (int)(e % out_pad);
+        const int64_t slot = e / out_pad;
+        const int64_t i = slot / nd;
+        const int d = (int)(slot % nd) + 1;
+        float v = 0.f;
+        if (o < out) v = (degree_factor ? (float)d : 1.f) * c[(i * out + o) * (nd + 1) + d] * s_w;
+        wd[e] = __float2half_rn(v);
+    }
+}
+
+// dYh[b][pitch] <- fp16(dY[b][o] * s_b) for o < out, s_b the power of two that puts the row's largest |element| into
+// [2^14, 2^15) (1 for a row of zeros, and for a row with an inf or a NaN, which then reaches the tensor pipe as it
+// is); row_inv[b] = 1 / s_b.  One warp per row, the row read twice (the second time from L1).  `out` is a multiple
+// of 4; the pad columns are never read: the tensor map ends at `out`.
+__global__ void __launch_bounds__(256)
+dy_half_rows_kernel(const float* __restrict__ dy, __half* __restrict__ dyh, float* __restrict__ row_inv, int64_t B,
+                    int out, int64_t pitch) {
+    const int lane = threadIdx.x & 31;
+    const int q = out >> 2;
+    for (int64_t b = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) >> 5; b < B;
+         b += ((int64_t)gridDim.x * blockDim.x) >> 5) {
+        const float4* row = reinterpret_cast<const float4*>(dy + b * out);
+        uint32_t m = 0u;
+        for (int c4 = lane; c4 < q; c4 += 32) {
+            const float4 v = row[c4];
+            m = max(m, __float_as_uint(fabsf(v.x))); m = max(m, __float_as_uint(fabsf(v.y)));
+            m = max(m, __float_as_uint(fabsf(v.z))); m = max(m, __float_as_uint(fabsf(v.w)));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+        const float s = half_scale_for(m);
+        if (lane == 0) row_inv[b] = 1.f / s;
+        __half* dst = dyh + b * pitch;
+        for (int c4 = lane; c4 < q; c4 += 32) {
+            const float4 v = row[c4];
+            const __half2 h0 = __floats2half2_rn(v.x * s, v.y * s), h1 = __floats2half2_rn(v.z * s, v.w * s);
+            uint2 w;
+            w.x = *reinterpret_cast<const uint32_t*>(&h0); w.y = *reinterpret_cast<const uint32_t*>(&h1);
+            *reinterpret_cast<uint2*>(dst + 4 * c4) = w;
+        }
+    }
+}
+
 // Running state of one input's fold: sum += U_{d-1}(t) G_d column by column, U advanced by its recurrence.
 struct DxFold {
     float ua = 1.f, ub = 0.f, sum = 0.f, t2;       // (U_0, U_{-1}): the first column is degree 1, weight U_0 = 1
@@ -150,18 +239,23 @@ struct DxNoTable {};
 template <bool FAM> struct DxTable { using type = DxNoTable; };
 template <> struct DxTable<true> { using type = RecurrenceTable; };
 
-template <int CG, int BN, bool FAM>
+template <int CG, int BN, bool FAM, bool H = false>
 __global__ void __launch_bounds__(DX_THREADS, 1)
 dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant__ CUtensorMap tmap_w,
              const float* __restrict__ x, float* __restrict__ dx, int64_t B, int in, int out, int nd, int TI,
              int i_tiles, int64_t num_tiles, int32_t* status, int accumulate, int exact_tanh,
-             const __grid_constant__ typename DxTable<FAM>::type rec) {
+             const __grid_constant__ typename DxTable<FAM>::type rec, const float* __restrict__ w_inv_scale,
+             const float* __restrict__ row_inv_scale) {
+    static_assert(!(H && FAM), "the fp16-operand variant exists for the Chebyshev fold only");
+    constexpr int KB = H ? DX_KB_HALF : DX_KB;           // outputs per K block (one 128-byte row of either operand)
+    constexpr int OPMODE = H ? CHEBYKAN_MODE_BF16 : CHEBYKAN_MODE_TF32;   // kind::f16 / kind::tf32
     using L = DxSmem<CG, BN>;
     constexpr int NS = L::NS, DX_NUM_BARS = L::NUM_BARS, NACC = L::NACC;
     constexpr int GROUP_WARPS = DX_EPI_WARPS / NACC;     // epilogue warps per accumulator
     constexpr int PARTS = GROUP_WARPS / 4;               // warps per TMEM lane quarter within a group
     constexpr int DX_STAGE = L::STAGE, DX_BAR_OFFSET = L::BAR_OFFSET;
-    constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(BN >> 3) << 17) |
+    // fp32 accumulate; operand formats tf32 (2) or fp16 (0); both operands K-major
+    constexpr uint32_t IDESC = (1u << 4) | (H ? 0u : ((2u << 7) | (2u << 10))) | ((uint32_t)(BN >> 3) << 17) |
                                ((uint32_t)((DX_BM * CG) >> 4) << 24);
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -176,7 +270,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + DX_BAR_OFFSET + DX_NUM_BARS * 8 + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int nkb = (out + DX_KB - 1) / DX_KB;
+    const int nkb = (out + KB - 1) / KB;
     // CTA pair: a tile is 256 rows, this CTA owns rows [128 rank, 128 rank + 128) of it
     const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
     const int64_t unit = (CG == 2) ? (blockIdx.x >> 1) : blockIdx.x;
@@ -227,12 +321,12 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                         // both CTAs' bytes count on the even CTA's barrier
                         if (rank == 0) mbar_arrive_expect_tx(full_bar(s), 2 * DX_STAGE);
                         const uint32_t bar0 = mapa_cluster(full_bar(s), 0);
-                        tma_load_2d_pair(st, &tmap_dy, kb * DX_KB, m0, bar0);
-                        tma_load_2d_pair(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0 + (int)rank * (BN / 2), bar0);
+                        tma_load_2d_pair(st, &tmap_dy, kb * KB, m0, bar0);
+                        tma_load_2d_pair(st + DX_A_STAGE, &tmap_w, kb * KB, slot0 + (int)rank * (BN / 2), bar0);
                     } else {
                         mbar_arrive_expect_tx(full_bar(s), DX_STAGE);
-                        tma_load_2d(st, &tmap_dy, kb * DX_KB, m0, full_bar(s));
-                        tma_load_2d(st + DX_A_STAGE, &tmap_w, kb * DX_KB, slot0, full_bar(s));
+                        tma_load_2d(st, &tmap_dy, kb * KB, m0, full_bar(s));
+                        tma_load_2d(st + DX_A_STAGE, &tmap_w, kb * KB, slot0, full_bar(s));
                     }
                     if (++s == NS) { s = 0; ph ^= 1u; }
                 }
@@ -267,11 +361,11 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                         const uint64_t ad = desc_from_words(a_lo + 2u * k, a_hi), bd = desc_from_words(b_lo + 2u * k, b_hi);
                         if (elected) {
                             if (CG == 2) {
-                                if (k != 0) umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
-                                else umma2<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, later);
+                                if (k != 0) umma2<OPMODE>(d_tmem, ad, bd, IDESC, 1u);
+                                else umma2<OPMODE>(d_tmem, ad, bd, IDESC, later);
                             } else {
-                                if (k != 0) umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, 1u);
-                                else umma<CHEBYKAN_MODE_TF32>(d_tmem, ad, bd, IDESC, later);
+                                if (k != 0) umma<OPMODE>(d_tmem, ad, bd, IDESC, 1u);
+                                else umma<OPMODE>(d_tmem, ad, bd, IDESC, later);
                             }
                         }
                     }
@@ -297,6 +391,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
         const int part = ((warp - DX_EPI_WARP0) % GROUP_WARPS) >> 2;     // which share of a tile's inputs
         const int acc = group; uint32_t acc_ph = 0;
         bool alive = true;
+        const float osc_w = H ? __ldg(w_inv_scale) : 1.f;
         // this group's tiles: unit + group * nunits, then every NACC * nunits
         const int64_t first = unit + group * nunits;
         int64_t rb = first / i_tiles; int it = (int)(first % i_tiles);
@@ -310,6 +405,7 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
             const int per = (ti + PARTS - 1) / PARTS;
             const int ii_begin = min(ti, part * per), ii_end = min(ti, ii_begin + per);
             const bool row_ok = row < B;
+            const float osc_dy = (H && row_ok) ? __ldg(row_inv_scale + row) : 1.f;
             const float* xrow = x + (row_ok ? row : 0) * in + i0;
             float* dxrow = dx + (row_ok ? row : 0) * in + i0;
             // The warp folds its inputs two at a time (A and B): both inputs' TMEM loads are in flight together and
@@ -441,10 +537,12 @@ dx_tc_kernel(const __grid_constant__ CUtensorMap tmap_dy, const __grid_constant_
                     fa.one(a); fb.one(b);
                 }
                 if (row_ok) {
-                    const float va = fmaf(-ta, ta, 1.f) * fa.sum;
-                    dxrow[ii] = accumulate ? old_a + va : va;
+                    float va = fmaf(-ta, ta, 1.f) * fa.sum;
+                    if (H) va = va * osc_dy * osc_w;       // undo the operands' power-of-two scales (one after the other:
+                    dxrow[ii] = accumulate ? old_a + va : va;       // their product may leave the float range)
                     if (has_b) {
-                        const float vb = fmaf(-tb, tb, 1.f) * fb.sum;
+                        float vb = fmaf(-tb, tb, 1.f) * fb.sum;
+                        if (H) vb = vb * osc_dy * osc_w;
                         dxrow[ii + 1] = accumulate ? old_b + vb : vb;
                     }
                 }
@@ -490,21 +588,28 @@ bool dx_tc_supported(int64_t B, int64_t in, int64_t out, int64_t deg) {
 
 // tf32 / bf16 modes: the repacked coefficients.  Three-product (fp32-grade) mode: their heads and tails, and the
 // tails of dY.
+// fp16-operand variant (x3 == 2): a header, the fp16 coefficients and the scaled fp16 copy of dY.
 int64_t dx_tc_workspace_bytes(int64_t B, int64_t in, int64_t out, int64_t deg, int x3) {
+    if (x3 == 2) {
+        const int64_t out_pad = round_up(out, DX_KB_HALF);
+        return DX_HEADER + round_up(in * (deg > 0 ? deg : 1) * out_pad * 2, 256) + round_up(B * out_pad * 2, 256) +
+               round_up(B * 4, 256);
+    }
     const int64_t wd = round_up(in * (deg + 1) * round_up(out, 32) * 4, 256);
     return x3 ? 2 * wd + round_up(B * out * 4, 256) : wd;
 }
 
 namespace {
-template <int CG, int BN, bool FAM>
+template <int CG, int BN, bool FAM, bool H = false>
 int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, const float* x, float* dx, int64_t B,
                      int in, int out, int nd, int32_t* status, cudaStream_t s, int accumulate, int exact_tanh,
-                     const typename DxTable<FAM>::type& rec) {
+                     const typename DxTable<FAM>::type& rec, const float* w_inv_scale = nullptr,
+                     const float* row_inv_scale = nullptr) {
     using L = DxSmem<CG, BN>;
     static bool attr_set[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
-    auto kernel = dx_tc_kernel<CG, BN, FAM>;
+    auto kernel = dx_tc_kernel<CG, BN, FAM, H>;
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         int rc = check_cuda(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         if (rc) return rc;
@@ -525,13 +630,63 @@ int launch_dx_kernel(const CUtensorMap& tmap_dy, const CUtensorMap& tmap_w, cons
     attrs[0].val.clusterDim.x = CG; attrs[0].val.clusterDim.y = 1; attrs[0].val.clusterDim.z = 1;
     cfg.attrs = attrs; cfg.numAttrs = 1;
     return check_cuda(cudaLaunchKernelEx(&cfg, kernel, tmap_dy, tmap_w, x, dx, B, in, out, nd, TI, i_tiles, num_tiles,
-                                         status, accumulate, exact_tanh, rec));
+                                         status, accumulate, exact_tanh, rec, w_inv_scale, row_inv_scale));
+}
+
+// The fp16-operand variant: row-scaled fp16 copy of dY, absmax and scaled fp16 repack of the coefficients, the kernel.
+int launch_dx_half(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t B, int64_t in,
+                   int64_t out, int nd, int32_t* status, cudaStream_t s) {
+    EncodeTiledFn encode = get_encode_fn();
+    if (!encode) return CHEBYKAN_ECUDA;
+    const int64_t out_pad = round_up(out, DX_KB_HALF);
+    const int64_t slots = in * nd;
+    uint32_t* header = reinterpret_cast<uint32_t*>(ws);
+    __half* wd = reinterpret_cast<__half*>(reinterpret_cast<char*>(ws) + DX_HEADER);
+    __half* dyh = reinterpret_cast<__half*>(reinterpret_cast<char*>(ws) + DX_HEADER + round_up(slots * out_pad * 2, 256));
+    float* row_inv = reinterpret_cast<float*>(reinterpret_cast<char*>(dyh) + round_up(B * out_pad * 2, 256));
+    int rc;
+    if ((rc = check_cuda(cudaMemsetAsync(header, 0, 16, s)))) return rc;
+    auto grid_for = [](int64_t work) {
+        int64_t blocks = ceil_div(work, 256);
+        if (blocks > 148 * 8) blocks = 148 * 8;
+        return (unsigned)(blocks < 1 ? 1 : blocks);
+    };
+    dx_absmax_kernel<<<grid_for(ceil_div(in * out * (nd + 1), 4)), 256, 0, s>>>(coeffs, in * out * (nd + 1), header);
+    pack_dx_half_kernel<<<grid_for(slots * out_pad), 256, 0, s>>>(coeffs, header, wd, (int)in, (int)out, nd, (int)out_pad, 1);
+    dy_half_rows_kernel<<<grid_for(B * 32), 256, 0, s>>>(dy, dyh, row_inv, B, (int)out, out_pad);
+    if ((rc = check_cuda(cudaGetLastError()))) return rc;
+    const int cg = B > DX_BM ? 2 : 1;
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m_dy, m_w;
+    {
+        // dYh[B][out_pad] fp16, valid columns [0, out): boxes of 64 outputs (128 bytes) x 128 rows
+        const cuuint64_t dims[2] = {(cuuint64_t)out, (cuuint64_t)B};
+        const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 2)};
+        const cuuint32_t box[2] = {DX_KB_HALF, DX_BM};
+        const CUresult r = encode(&m_dy, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, dyh, dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    }
+    {
+        const cuuint64_t dims[2] = {(cuuint64_t)out_pad, (cuuint64_t)slots};
+        const cuuint64_t strides[1] = {(cuuint64_t)(out_pad * 2)};
+        const cuuint32_t box[2] = {DX_KB_HALF, (cuuint32_t)(DX_BN / cg)};
+        const CUresult r = encode(&m_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, wd, dims, strides, box, estr,
+                                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) { set_last_cuda_error((int)r); return CHEBYKAN_ECUDA; }
+    }
+    const float* w_inv = reinterpret_cast<const float*>(header) + 1;
+    if (cg == 2) return launch_dx_kernel<2, DX_BN, false, true>(m_dy, m_w, x, dx, B, (int)in, (int)out, nd, status, s, 0, 0, DxNoTable(), w_inv, row_inv);
+    return launch_dx_kernel<1, DX_BN, false, true>(m_dy, m_w, x, dx, B, (int)in, (int)out, nd, status, s, 0, 0, DxNoTable(), w_inv, row_inv);
 }
 }  // namespace
 
 int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx, void* ws, int64_t ws_bytes,
                  int64_t B, int64_t in, int64_t out, int64_t deg, int32_t* status, cudaStream_t s, int x3,
                  const RecurrenceTable* rec) {
+    // x3: 0 = tf32 operands, 1 = three tf32 products of heads and tails (the fp32 tolerance), 2 = fp16 operands
     if (rec != nullptr && x3) return CHEBYKAN_EUNSUPPORTED;
     const int degree_factor = rec == nullptr;
     // T_0' = 0 (P_0' = 0): degree 0 takes no slot of G.  A tile's 256 slots then hold 256 / deg inputs: 8 instead of
@@ -541,6 +696,7 @@ int launch_dx_tc(const float* x, const float* dy, const float* coeffs, float* dx
     const int64_t out_pad = round_up(out, 32);
     const int64_t slots = in * nd;
     if (ws == nullptr || ws_bytes < dx_tc_workspace_bytes(B, in, out, deg, x3)) return CHEBYKAN_EWORKSPACE;
+    if (x3 == 2) return launch_dx_half(x, dy, coeffs, dx, ws, B, in, out, nd, status, s);
     EncodeTiledFn encode = get_encode_fn();
     if (!encode) return CHEBYKAN_ECUDA;
     const int64_t wd_bytes = round_up(slots * out_pad * 4, 256);

@@ -304,6 +304,44 @@ def test_tc_dx_vs_oracle(mode, B, n_in, n_out, deg, dist):
         assert float(dx.abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("dy_scale,c_scale", [(1.0, 1.0), (1e-9, 1.0), (3e5, 1e-6), (1.0, 4e4)])
+@pytest.mark.parametrize("B,n_in,n_out,deg", [
+    (700, 40, 512, 8),        # narrowest layer that takes the fp16 operands; ragged rows, eight K blocks of 64 outputs
+    (129, 24, 516, 5),        # outputs not a multiple of 64: the last K block ends in zero fill; a CTA pair's second half nearly empty
+    (100, 16, 1000, 31),      # one CTA (no pair), 16 K blocks, eight inputs per tile
+    (5000, 96, 512, 3),       # more tiles than one wave of pairs
+])
+def test_wide_dx_fp16_operands(B, n_in, n_out, deg, dy_scale, c_scale):
+    """bf16 mode on layers of 512 outputs or more: dY and d * C go to the tensor cores as fp16, each scaled by a power
+    of two found from its largest element; the result holds the tensor-core tolerance whatever the magnitudes, and the
+    tf32 kernel (same 11 significant bits) lands within the same distance of the oracle."""
+    x, coeffs, dy = make_case(B, n_in, n_out, deg, seed=B + n_out + deg)
+    dy = dy * dy_scale
+    coeffs = coeffs * c_scale
+    _, _, dx_ref = o.forward_backward(x, coeffs, dy)
+    dx, dxw = guarded((B, n_in))
+    ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "bf16", out=dx)
+    torch.cuda.synchronize()
+    ops.check_status()
+    assert_guards_intact(dx, dxw)
+    err = o.rel_l2(dx.cpu(), dx_ref)
+    err_tf32 = o.rel_l2(ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "tf32").cpu(), dx_ref)
+    assert 1e-6 < err <= TC_TOL, err
+    assert err <= 2.0 * err_tf32 + 1e-5, (err, err_tf32)
+    assert torch.equal(dx, ops.bwd_dx(x.cuda(), dy.cuda(), coeffs.cuda(), "bf16"))     # bitwise repeatable
+
+
+def test_wide_dx_fp16_operands_zero_and_nan():
+    x, coeffs, dy = make_case(300, 8, 512, 4, seed=77)
+    zero = ops.bwd_dx(x.cuda(), torch.zeros_like(dy).cuda(), coeffs.cuda(), "bf16")
+    assert float(zero.abs().max()) == 0.0
+    dy_nan = dy.clone()
+    dy_nan[17, 3] = float("nan")
+    got = ops.bwd_dx(x.cuda(), dy_nan.cuda(), coeffs.cuda(), "bf16").cpu()
+    assert torch.isnan(got[17]).all()                    # the NaN reaches every input of its row
+    ops.check_status()
+
+
 def test_tc_dx_repeatable_and_fallback():
     x, coeffs, dy = make_case(3000, 24, 64, 8, seed=41)
     xd, dyd, cd = x.cuda(), dy.cuda(), coeffs.cuda()
