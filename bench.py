@@ -454,6 +454,33 @@ def bench_layer(ctx: Ctx, mode: str, op: str, B: int, n_in: int, n_out: int, deg
     return ms, clocks, dict(layer=layer, x_host=x_host, step=step, flushed=flush)
 
 
+def sub_layer_fwd_bwd(ctx: Ctx, mode: str, B: int, n_in: int, n_out: int, deg: int, steps: int, warmup: int):
+    """Forward and backward of ONE layer through the drop-in module and autograd (y = layer(x); y.backward(dY) with
+    x requiring a gradient, so that both dC and dx are computed), B resident rows per rank: the 'fwd+bwd ms/step' of a
+    wide layer.  FLOPs counted as three products of 2*B*in*(deg+1)*out."""
+    import kan_b200
+    torch.manual_seed(1003)
+    layer = kan_b200.ChebyKANLayer(n_in, n_out, deg, math_mode=mode).to(ctx.dev)
+    g = torch.Generator().manual_seed(1004 + ctx.rank)
+    x = torch.randn(B, n_in, generator=g).to(ctx.dev).requires_grad_(True)
+    dy = torch.randn(B, n_out, generator=g).to(ctx.dev)
+
+    def step():
+        x.grad = None
+        layer.cheby_coeffs.grad = None
+        layer(x).backward(dy)
+    ms, _ = ctx.time_steps(step, steps, warmup)
+    flops = 3 * 2.0 * B * n_in * (deg + 1) * n_out
+    rec = {"workload": f"one ChebyKANLayer {n_in}->{n_out} degree {deg}, {B} rows per GPU: forward + backward (dC and dx) "
+                       "through torch autograd",
+           "value": B * ctx.world / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "rows_per_gpu": B, "math_mode": mode,
+           "operands": {"fwd": mode, "dcoeff": "tf32", "dx": "f16" if (mode == "bf16" and n_out >= 512) else "tf32"},
+           "achieved_tflops": flops / (ms * 1e-3) / 1e12}
+    del layer, x, dy
+    free_gpu()
+    return rec
+
+
 def layer_record(ctx, mode, op, B_rank, B_total, shape, ms, peaks, tf32_peak, extra=None):
     n_in, n_out, deg = shape
     flops_rank = 2.0 * B_rank * n_in * (deg + 1) * n_out
@@ -747,6 +774,9 @@ def run_ours(args):
                 del st
                 free_gpu()
                 sub[f"cfg3_{op}_{m}"] = layer_record(ctx, m, op, Bg, Bg, (n_in, n_out, deg), ms, peaks, tf32_peak)
+        if ctx.world == 1:
+            sub["cfg3_fwd_bwd_bf16"] = sub_layer_fwd_bwd(ctx, "bf16", Bg, n_in, n_out, deg, ks, kw)
+            sub["cfg3_fwd_bwd_tf32"] = sub_layer_fwd_bwd(ctx, "tf32", Bg, n_in, n_out, deg, ks, kw)
         sub["cfg4_stack_fwd_bf16"] = sub_stack_cfg4(ctx, "bf16", False, ks, kw, peaks, tf32_peak)
         sub["cfg4_stack_fwd_bf16_fused_ln"] = sub_stack_cfg4(ctx, "bf16", True, ks, kw, peaks, tf32_peak)
         sub["cfg5_train_tf32"] = sub_train_cfg5(ctx, "tf32", ks, kw, peaks, tf32_peak)
