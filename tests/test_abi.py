@@ -58,4 +58,12 @@ def test_pure_host_entry_points(built_lib):
     assert lib.chebykan_workspace_bytes(99, 128, 8, 8, 4, 0) == -1
     ws = lib.chebykan_workspace_bytes(_lib.OP_BWD_DCOEFF, 1 << 20, 64, 64, 32, 0)
     assert ws > 0 and ws % (64 * 64 * 33 * 4) == 0
+    # dx workspace: the repacked tf32 coefficients (degrees 0..deg counted, 32-output pitch); in bf16 mode from 512
+    # outputs on a header, fp16 coefficients (degrees 1..deg, 64-output pitch), the fp16 copy of dY and a scale per row
+    assert lib.chebykan_workspace_bytes(_lib.OP_BWD_DX, 4096, 64, 64, 32, _lib.MODE_TF32) == 64 * 33 * 64 * 4
+    assert lib.chebykan_workspace_bytes(_lib.OP_BWD_DX, 4096, 64, 64, 32, _lib.MODE_BF16) == 64 * 33 * 64 * 4
+    assert lib.chebykan_workspace_bytes(_lib.OP_BWD_DX, 4096, 128, 1000, 8, _lib.MODE_TF32) == 128 * 9 * 1024 * 4
+    assert (lib.chebykan_workspace_bytes(_lib.OP_BWD_DX, 4096, 128, 1000, 8, _lib.MODE_BF16)
+            == 256 + 128 * 8 * 1024 * 2 + 4096 * 1024 * 2 + 4096 * 4)
+    assert lib.chebykan_workspace_bytes(_lib.OP_BWD_DX, 4096, 128, 1000, 8, _lib.MODE_FP32) == 0
     assert lib.chebykan_fwd_host_scratch_bytes(100, 4, 4, 3, 0) > 100 * 4 * 4 * 2
