@@ -70,10 +70,16 @@ class GraphedTrainStep:
         """Destroy the recorded graph (replaying afterwards raises).  A graph that holds a captured collective keeps
         the NCCL communicator busy: ``torch.distributed.destroy_process_group`` blocks until the graph is gone,
         so a data-parallel job calls this (or drops the object) before it shuts the process group down."""
-        if self.graph is not None:
+        if getattr(self, "graph", None) is not None:
             torch.cuda.synchronize(self.x.device)
             self.graph.reset()
             self.graph = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:        # interpreter shutdown: the CUDA context may be gone already
+            pass
 
     def __call__(self) -> torch.Tensor:
         """Replay one step; returns the (device) loss tensor of that step.
